@@ -1,0 +1,333 @@
+// Decode attention, scalar kernel for any head_dim <= 256, any row count and
+// any of bf16 / fp32 / int8 caches, plus the split-K merge, the two-partial
+// merge and the jpt_flash_decode dispatcher.  The tensor-core kernel for
+// head_dim 128 lives in attention_mma.cu; this one covers every other shape.
+#include <math.h>
+
+#include "attention_common.cuh"
+
+namespace jpt {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kRowTile = 4;   // query rows per block
+constexpr int kMaxDPL = 8;    // head_dim <= 32 * kMaxDPL
+
+template <typename TQ, typename TKV>
+__global__ void __launch_bounds__(kWarps * 32) flash_decode_generic_kernel(AttnArgs a) {
+  extern __shared__ float smem[];
+  const int split = blockIdx.x;
+  const int rc = blockIdx.y % ((a.R + kRowTile - 1) / kRowTile);
+  const int h = blockIdx.y / ((a.R + kRowTile - 1) / kRowTile);
+  const int b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r0 = rc * kRowTile;
+  const int nrows = min(kRowTile, a.R - r0);
+  const int D = a.D;
+
+  float* q_s = smem;                         // [kRowTile][D], pre-scaled by sm_scale
+  float* red = smem + kRowTile * D;          // [kWarps][kRowTile][D + 2]
+
+  const int64_t row_base = ((int64_t)b * a.Hkv + h) * a.R + r0;
+  const TQ* q = static_cast<const TQ*>(a.q) + row_base * D;
+  for (int i = threadIdx.x; i < kRowTile * D; i += blockDim.x) {
+    const int r = i / D;
+    q_s[i] = r < nrows ? to_f32<TQ>(q[i]) * a.sm_scale : 0.f;
+  }
+  __syncthreads();
+
+  const SeqRange rg = seq_range(a, b);
+  const int chunk = (rg.n + a.nsplit - 1) / a.nsplit;
+  const int j0 = split * chunk;
+  const int j1 = min(rg.n, j0 + chunk);
+
+  float m[kRowTile], l[kRowTile], o[kRowTile][kMaxDPL];
+#pragma unroll
+  for (int r = 0; r < kRowTile; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxDPL; ++i) o[r][i] = 0.f;
+  }
+
+  const TKV* kbase = static_cast<const TKV*>(a.k);
+  const TKV* vbase = static_cast<const TKV*>(a.v);
+  const TQ* mask = static_cast<const TQ*>(a.mask);
+
+  for (int j = j0 + warp; j < j1; j += kWarps) {
+    const int p = physical_pos(a, rg, j);
+    int64_t sidx;
+    const int64_t off = kv_row_offset(a, b, h, p, &sidx);
+    float kk[kMaxDPL], vv[kMaxDPL];
+#pragma unroll
+    for (int i = 0; i < kMaxDPL; ++i) {
+      const int d = lane + 32 * i;
+      kk[i] = d < D ? to_f32<TKV>(kbase[off + d]) : 0.f;
+      vv[i] = d < D ? to_f32<TKV>(vbase[off + d]) : 0.f;
+    }
+    float ks = 1.f, vs = 1.f;
+    if (a.k_scale) {
+      ks = load_scale(a.k_scale, sidx, a.scale_is_f32);
+      vs = load_scale(a.v_scale, sidx, a.scale_is_f32);
+    }
+#pragma unroll
+    for (int r = 0; r < kRowTile; ++r) {
+      if (r >= nrows) break;
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < kMaxDPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) s += q_s[r * D + d] * kk[i];
+      }
+      s = warp_sum(s) * ks;
+      if (a.mask_mode == JPT_MASK_ADD) {
+        s += to_f32<TQ>(mask[(int64_t)b * a.mk_b + (int64_t)(r0 + r) * a.mk_r + p]);
+      }
+      if (s == -INFINITY) continue;  // fully masked position
+      const float mn = fmaxf(m[r], s);
+      const float corr = expf(m[r] - mn);  // exp(-inf) = 0 on the first token
+      const float pr = expf(s - mn);
+      l[r] = l[r] * corr + pr;
+      const float pv = pr * vs;
+#pragma unroll
+      for (int i = 0; i < kMaxDPL; ++i) o[r][i] = o[r][i] * corr + pv * vv[i];
+      m[r] = mn;
+    }
+  }
+
+  // combine the warps of the block
+  const int stride = D + 2;
+  for (int r = 0; r < nrows; ++r) {
+    float* dst = red + ((int64_t)warp * kRowTile + r) * stride;
+#pragma unroll
+    for (int i = 0; i < kMaxDPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) dst[d] = o[r][i];
+    }
+    if (lane == 0) {
+      dst[D] = m[r];
+      dst[D + 1] = l[r];
+    }
+  }
+  __syncthreads();
+  for (int r = 0; r < nrows; ++r) {
+    float M = -INFINITY;
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, red[((int64_t)w * kRowTile + r) * stride + D]);
+    float L = 0.f;
+    float wgt[kWarps];
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = red[((int64_t)w * kRowTile + r) * stride + D];
+      wgt[w] = mw == -INFINITY ? 0.f : expf(mw - M);
+      L += wgt[w] * red[((int64_t)w * kRowTile + r) * stride + D + 1];
+    }
+    const int64_t row = row_base + r;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float acc = 0.f;
+      for (int w = 0; w < kWarps; ++w) acc += wgt[w] * red[((int64_t)w * kRowTile + r) * stride + d];
+      if (a.nsplit == 1) {
+        const float out = L > 0.f ? acc / L : 0.f;
+        static_cast<TQ*>(a.o)[row * D + d] = from_f32<TQ>(out);
+      } else {
+        a.ws_o[(row * a.nsplit + split) * D + d] = acc;
+      }
+    }
+    if (threadIdx.x == 0) {
+      if (a.nsplit == 1) {
+        if (a.m) a.m[row] = M;
+        if (a.l) a.l[row] = L;
+      } else {
+        a.ws_m[row * a.nsplit + split] = M;
+        a.ws_l[row * a.nsplit + split] = L;
+      }
+    }
+  }
+}
+
+// One block per output row: combine the nsplit partials.
+template <typename TQ>
+__global__ void splitk_merge_kernel(AttnArgs a) {
+  const int64_t row = blockIdx.x;
+  const int D = a.D;
+  float M = -INFINITY;
+  for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, a.ws_m[row * a.nsplit + s]);
+  float L = 0.f;
+  for (int s = 0; s < a.nsplit; ++s) {
+    const float ms = a.ws_m[row * a.nsplit + s];
+    if (ms != -INFINITY) L += expf(ms - M) * a.ws_l[row * a.nsplit + s];
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < a.nsplit; ++s) {
+      const float ms = a.ws_m[row * a.nsplit + s];
+      if (ms != -INFINITY) acc += expf(ms - M) * a.ws_o[(row * a.nsplit + s) * D + d];
+    }
+    static_cast<TQ*>(a.o)[row * D + d] = from_f32<TQ>(L > 0.f ? acc / L : 0.f);
+  }
+  if (threadIdx.x == 0) {
+    if (a.m) a.m[row] = M;
+    if (a.l) a.l[row] = L;
+  }
+}
+
+template <typename TI, typename TO>
+__global__ void merge_partials_kernel(const TI* o1, const float* m1, const float* l1, const TI* o2,
+                                      const float* m2, const float* l2, TO* o, int64_t rows, int D) {
+  const int64_t total = rows * D;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / D;
+    const float a1 = m1[r], a2 = m2[r];
+    const float g = fmaxf(a1, a2);
+    // An empty side has m = -inf and l = 0; its weight is zero (the reference
+    // formula would produce exp(-inf - -inf) only when both sides are empty).
+    const float alpha = a1 == -INFINITY ? 0.f : expf(a1 - g);
+    const float beta = a2 == -INFINITY ? 0.f : expf(a2 - g);
+    const float denom = alpha * l1[r] + beta * l2[r];
+    const float num = l1[r] * alpha * to_f32<TI>(o1[i]) + beta * to_f32<TI>(o2[i]) * l2[r];
+    o[i] = from_f32<TO>(num / denom);
+  }
+}
+
+template <typename TQ>
+int launch_generic_kv(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st) {
+  const int rcs = (a.R + kRowTile - 1) / kRowTile;
+  dim3 grid(a.nsplit, a.Hkv * rcs, a.B);
+  const size_t smem = sizeof(float) * (kRowTile * a.D + kWarps * kRowTile * (a.D + 2));
+  switch (p.kv_dtype) {
+    case JPT_BF16:
+      flash_decode_generic_kernel<TQ, __nv_bfloat16><<<grid, kWarps * 32, smem, st>>>(a);
+      break;
+    case JPT_F32:
+      flash_decode_generic_kernel<TQ, float><<<grid, kWarps * 32, smem, st>>>(a);
+      break;
+    case JPT_INT8:
+      flash_decode_generic_kernel<TQ, int8_t><<<grid, kWarps * 32, smem, st>>>(a);
+      break;
+    default:
+      return fail(JPT_EINVAL, "flash_decode: bad kv dtype %d", p.kv_dtype);
+  }
+  return check_launch("flash_decode_generic_kernel");
+}
+
+}  // namespace
+
+int launch_attention_generic(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st) {
+  JPT_REQUIRE(a.D <= 32 * kMaxDPL, JPT_ERANGE, "flash_decode: head_dim %d > %d unsupported", a.D, 32 * kMaxDPL);
+  return p.q_dtype == JPT_BF16 ? launch_generic_kv<__nv_bfloat16>(p, a, st) : launch_generic_kv<float>(p, a, st);
+}
+
+int launch_splitk_merge(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st) {
+  const int64_t rows = (int64_t)a.B * a.Hkv * a.R;
+  const int threads = a.D >= 128 ? 128 : (a.D > 32 ? 64 : 32);
+  if (p.q_dtype == JPT_BF16) {
+    splitk_merge_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, st>>>(a);
+  } else {
+    splitk_merge_kernel<float><<<(unsigned)rows, threads, 0, st>>>(a);
+  }
+  return check_launch("splitk_merge_kernel");
+}
+
+static int auto_splits_generic(const jpt_attn_params& p, int R) {
+  const int rcs = (R + kRowTile - 1) / kRowTile;
+  const long base = (long)p.B * p.Hkv * rcs;
+  int want = (int)((2L * 148 + base - 1) / base);
+  int maxs = (p.S + 127) / 128;
+  if (want > maxs) want = maxs;
+  if (want > 64) want = 64;
+  return want < 1 ? 1 : want;
+}
+
+static int resolve_splits(const jpt_attn_params& p, bool use_mma, int R) {
+  if (p.num_splits > 0) return p.num_splits;
+  return use_mma ? attention_mma_pick_splits(p) : auto_splits_generic(p, R);
+}
+
+static int validate(const jpt_attn_params& p) {
+  JPT_REQUIRE(p.q && p.k && p.v && p.o, JPT_EINVAL, "flash_decode: null tensor");
+  JPT_REQUIRE(p.q_dtype == JPT_BF16 || p.q_dtype == JPT_F32, JPT_EINVAL, "flash_decode: q dtype must be bf16 or f32");
+  JPT_REQUIRE(p.B > 0 && p.Hq > 0 && p.Hkv > 0 && p.Tq > 0 && p.D > 0 && p.S > 0, JPT_EINVAL,
+              "flash_decode: bad shape");
+  JPT_REQUIRE(p.Hq % p.Hkv == 0, JPT_EINVAL, "flash_decode: Hq (%d) not a multiple of Hkv (%d)", p.Hq, p.Hkv);
+  JPT_REQUIRE((p.k_scale == nullptr) == (p.v_scale == nullptr), JPT_EINVAL, "flash_decode: need both scales or none");
+  if (p.mask_mode == JPT_MASK_LENGTH) JPT_REQUIRE(p.end, JPT_EINVAL, "flash_decode: JPT_MASK_LENGTH needs end");
+  if (p.mask_mode == JPT_MASK_RING) JPT_REQUIRE(p.start && p.end, JPT_EINVAL, "flash_decode: JPT_MASK_RING needs start and end");
+  if (p.mask_mode == JPT_MASK_ADD) JPT_REQUIRE(p.mask, JPT_EINVAL, "flash_decode: JPT_MASK_ADD needs mask");
+  JPT_REQUIRE(p.mask_mode >= 0 && p.mask_mode <= 3, JPT_EINVAL, "flash_decode: bad mask mode");
+  if (p.paged) {
+    JPT_REQUIRE(p.page_table && p.page_size > 0 && p.max_pages > 0, JPT_EINVAL, "flash_decode: paged needs a page table");
+    JPT_REQUIRE(p.S == p.page_size * p.max_pages, JPT_EINVAL, "flash_decode: paged S must be max_pages*page_size");
+    JPT_REQUIRE(p.mask_mode == JPT_MASK_LENGTH, JPT_EINVAL, "flash_decode: paged caches use JPT_MASK_LENGTH");
+  }
+  return 0;
+}
+
+}  // namespace jpt
+
+using namespace jpt;
+
+extern "C" size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p) {
+  if (!p || validate(*p) != 0) return 0;
+  const int R = (p->Hq / p->Hkv) * p->Tq;
+  const bool use_mma = !p->force_generic && attention_mma_eligible(*p);
+  const int ns = resolve_splits(*p, use_mma, R);
+  if (ns <= 1) return 0;
+  const size_t rows = (size_t)p->B * p->Hkv * R;
+  return rows * ns * (p->D + 2) * sizeof(float);
+}
+
+extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
+  JPT_REQUIRE(pp, JPT_EINVAL, "flash_decode: null params");
+  const jpt_attn_params& p = *pp;
+  if (int rc = validate(p)) return rc;
+  const int R = (p.Hq / p.Hkv) * p.Tq;
+  const bool use_mma = !p.force_generic && attention_mma_eligible(p);
+  AttnArgs a{};
+  a.q = p.q; a.k = p.k; a.v = p.v; a.k_scale = p.k_scale; a.v_scale = p.v_scale;
+  a.page_table = p.page_table; a.start = p.start; a.end = p.end; a.mask = p.mask;
+  a.o = p.o; a.m = p.m; a.l = p.l;
+  a.B = p.B; a.Hq = p.Hq; a.Hkv = p.Hkv; a.Tq = p.Tq; a.D = p.D; a.R = R;
+  a.S = p.S; a.paged = p.paged; a.page_size = p.page_size; a.max_pages = p.max_pages;
+  a.kv_b = p.kv_b; a.kv_h = p.kv_h; a.kv_s = p.kv_s; a.kv_page = p.kv_page;
+  a.sc_b = p.sc_b; a.sc_s = p.sc_s; a.mk_b = p.mk_b; a.mk_r = p.mk_r;
+  a.mask_mode = p.mask_mode; a.scale_is_f32 = p.scale_dtype == JPT_F32;
+  a.sm_scale = p.sm_scale;
+  a.nsplit = resolve_splits(p, use_mma, R);
+  if (a.nsplit > 1) {
+    const size_t rows = (size_t)p.B * p.Hkv * R;
+    const size_t need = rows * a.nsplit * (p.D + 2) * sizeof(float);
+    JPT_REQUIRE(p.workspace && p.workspace_bytes >= need, JPT_EWORKSPACE,
+                "flash_decode: workspace of %zu bytes needed, %zu given", need, p.workspace_bytes);
+    JPT_REQUIRE(aligned(p.workspace, 16), JPT_EALIGN, "flash_decode: workspace must be 16-byte aligned");
+    a.ws_o = static_cast<float*>(p.workspace);
+    a.ws_m = a.ws_o + rows * a.nsplit * p.D;
+    a.ws_l = a.ws_m + rows * a.nsplit;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = use_mma ? launch_attention_mma(p, a, st) : launch_attention_generic(p, a, st);
+  if (rc) return rc;
+  if (a.nsplit > 1) return launch_splitk_merge(p, a, st);
+  return 0;
+}
+
+extern "C" int jpt_merge_partials(const void* o1, const float* m1, const float* l1, const void* o2,
+                                  const float* m2, const float* l2, int in_dtype, void* o, int out_dtype,
+                                  int64_t rows, int D, void* stream) {
+  JPT_REQUIRE(o1 && m1 && l1 && o2 && m2 && l2 && o, JPT_EINVAL, "merge_partials: null tensor");
+  JPT_REQUIRE(rows >= 0 && D > 0, JPT_EINVAL, "merge_partials: bad shape");
+  if (rows == 0) return 0;
+  const int64_t total = rows * D;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define JPT_MERGE(TI, TO)                                                                     \
+  merge_partials_kernel<TI, TO><<<blocks, 256, 0, st>>>(static_cast<const TI*>(o1), m1, l1,   \
+                                                        static_cast<const TI*>(o2), m2, l2,   \
+                                                        static_cast<TO*>(o), rows, D)
+  if (in_dtype == JPT_BF16 && out_dtype == JPT_BF16) JPT_MERGE(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == JPT_BF16 && out_dtype == JPT_F32) JPT_MERGE(__nv_bfloat16, float);
+  else if (in_dtype == JPT_F32 && out_dtype == JPT_F32) JPT_MERGE(float, float);
+  else if (in_dtype == JPT_F32 && out_dtype == JPT_BF16) JPT_MERGE(float, __nv_bfloat16);
+  else return fail(JPT_EINVAL, "merge_partials: bad dtypes");
+#undef JPT_MERGE
+  return check_launch("merge_partials_kernel");
+}
