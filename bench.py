@@ -120,8 +120,6 @@ class ClockSampler(threading.Thread):
 
 
 def cpu_layer_inputs(seed):
-  from oracle.quant import quantize_insert
-
   g = torch.Generator().manual_seed(seed)
   ck = torch.randint(-127, 128, (B, HKV, S, D), generator=g, dtype=torch.int8)
   cv = torch.randint(-127, 128, (B, HKV, S, D), generator=g, dtype=torch.int8)
@@ -130,7 +128,6 @@ def cpu_layer_inputs(seed):
   q = torch.randn(B, HQ, 1, D, generator=g).to(torch.bfloat16)
   xk = torch.randn(B, HKV, 1, D, generator=g).to(torch.bfloat16)
   xv = torch.randn(B, HKV, 1, D, generator=g).to(torch.bfloat16)
-  del quantize_insert
   return ck, cv, ks, vs, q, xk, xv
 
 
@@ -358,7 +355,7 @@ def run_cuda(args):
     for ci, c0 in enumerate(range(0, nl, chunk)):
       compute.wait_event(in_evt[ci])
       for i in range(c0, min(nl, c0 + chunk)):
-        o_s[i].copy_(layer_step(i, q_s[i], k_s[i], v_s[i]))
+        o_s[i].copy_(layer_step(i, q_s[i], k_s[i], v_s[i]).reshape(B, hq, 1, D))
       e = torch.cuda.Event()
       e.record(compute)
       copy_out.wait_event(e)
