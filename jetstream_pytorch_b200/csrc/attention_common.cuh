@@ -83,7 +83,9 @@ __device__ __forceinline__ float load_scale(const void* base, int64_t idx, int i
 // Host-side launchers implemented by the individual kernels.
 int launch_attention_generic(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
 bool attention_mma_eligible(const jpt_attn_params& p);
-int attention_mma_pick_splits(const jpt_attn_params& p);
+size_t attention_mma_workspace_bytes(const jpt_attn_params& p);
+// Launches the persistent kernel and its merge (and the mask pre-pass when the
+// mask is additive); uses p.workspace for its scratch.
 int launch_attention_mma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
 int launch_splitk_merge(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
 

@@ -237,9 +237,9 @@ static int auto_splits_generic(const jpt_attn_params& p, int R) {
   return want < 1 ? 1 : want;
 }
 
-static int resolve_splits(const jpt_attn_params& p, bool use_mma, int R) {
+static int resolve_splits(const jpt_attn_params& p, int R) {
   if (p.num_splits > 0) return p.num_splits;
-  return use_mma ? attention_mma_pick_splits(p) : auto_splits_generic(p, R);
+  return auto_splits_generic(p, R);
 }
 
 static int validate(const jpt_attn_params& p) {
@@ -268,8 +268,8 @@ using namespace jpt;
 extern "C" size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p) {
   if (!p || validate(*p) != 0) return 0;
   const int R = (p->Hq / p->Hkv) * p->Tq;
-  const bool use_mma = !p->force_generic && attention_mma_eligible(*p);
-  const int ns = resolve_splits(*p, use_mma, R);
+  if (!p->force_generic && attention_mma_eligible(*p)) return attention_mma_workspace_bytes(*p);
+  const int ns = resolve_splits(*p, R);
   if (ns <= 1) return 0;
   const size_t rows = (size_t)p->B * p->Hkv * R;
   return rows * ns * (p->D + 2) * sizeof(float);
@@ -291,7 +291,12 @@ extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
   a.sc_b = p.sc_b; a.sc_s = p.sc_s; a.mk_b = p.mk_b; a.mk_r = p.mk_r;
   a.mask_mode = p.mask_mode; a.scale_is_f32 = p.scale_dtype == JPT_F32;
   a.sm_scale = p.sm_scale;
-  a.nsplit = resolve_splits(p, use_mma, R);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_mma) {
+    a.nsplit = 1;
+    return launch_attention_mma(p, a, st);
+  }
+  a.nsplit = resolve_splits(p, R);
   if (a.nsplit > 1) {
     const size_t rows = (size_t)p.B * p.Hkv * R;
     const size_t need = rows * a.nsplit * (p.D + 2) * sizeof(float);
@@ -302,9 +307,7 @@ extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
     a.ws_m = a.ws_o + rows * a.nsplit * p.D;
     a.ws_l = a.ws_m + rows * a.nsplit;
   }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = use_mma ? launch_attention_mma(p, a, st) : launch_attention_generic(p, a, st);
-  if (rc) return rc;
+  if (int rc = launch_attention_generic(p, a, st)) return rc;
   if (a.nsplit > 1) return launch_splitk_merge(p, a, st);
   return 0;
 }
