@@ -245,7 +245,8 @@ typedef struct jpt_attn_params {
   void* o;              /* [B,Hq,Tq,D] q_dtype */
   float* m;             /* [B,Hq,Tq] running max of the logits, or NULL */
   float* l;             /* [B,Hq,Tq] softmax denominator (v scale not included), or NULL */
-  /* split-K scratch, at least jpt_flash_decode_workspace_bytes(p) bytes, 256-byte aligned */
+  /* scratch for split sequences: at least jpt_flash_decode_workspace_bytes(p) bytes,
+   * 256-byte aligned, cleared once with jpt_flash_decode_workspace_init() */
   void* workspace;
   size_t workspace_bytes;
   int num_splits;       /* split-K factor; 0 = choose automatically */
@@ -264,6 +265,15 @@ typedef struct jpt_attn_params {
  */
 int jpt_flash_decode(const jpt_attn_params* p, void* stream);
 size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p);
+/*
+ * Zero-fills a workspace (stream-ordered memset).  Call it once after
+ * allocating the buffer, and again after a launch that returned an error: the
+ * kernel keeps per-sequence arrival counters at the start of the workspace that
+ * it leaves at zero after every completed launch and expects at zero on entry.
+ * One workspace may serve calls of any shape, but never two calls that can
+ * overlap on the GPU.  (No counterpart in the reference.)
+ */
+int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, void* stream);
 
 /*
  * Merge two softmax partials: g = max(m1,m2); o = (l1 e^{m1-g} o1 + l2 e^{m2-g}

@@ -23,10 +23,12 @@ _workspaces = {}
 
 
 def _workspace(device, nbytes):
-  """Grow-only split-K scratch per device (allocated by torch, owned here)."""
+  """Grow-only attention scratch per device (allocated by torch, owned here),
+  cleared once when it is created as the kernel's arrival counters require."""
   ws = _workspaces.get(device)
   if ws is None or ws.numel() < nbytes:
-    ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+    ws = torch.empty(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
+    _lib.check(_lib.lib().jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), _lib.stream()))
     _workspaces[device] = ws
   return ws
 

@@ -54,7 +54,7 @@ def build_library(force=False, verbose=False):
   procs = []
   for src in SOURCES:
     obj = os.path.join(build_dir, src.replace(".cu", ".o"))
-    cmd = [nvcc, *NVCC_FLAGS, *EXTRA_FLAGS.get(src, []), "-I", INCLUDE, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+    cmd = [nvcc, *NVCC_FLAGS, *EXTRA_FLAGS.get(src, []), *os.environ.get("JPT_NVCC_FLAGS", "").split(), "-I", INCLUDE, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
     if verbose:
       cmd += ["-Xptxas", "-v"]
     procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

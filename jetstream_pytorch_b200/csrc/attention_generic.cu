@@ -272,7 +272,7 @@ extern "C" size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p) {
   const int ns = resolve_splits(*p, R);
   if (ns <= 1) return 0;
   const size_t rows = (size_t)p->B * p->Hkv * R;
-  return rows * ns * (p->D + 2) * sizeof(float);
+  return kWorkspaceCounterBytes + rows * ns * (p->D + 2) * sizeof(float);
 }
 
 extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
@@ -299,16 +299,25 @@ extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
   a.nsplit = resolve_splits(p, R);
   if (a.nsplit > 1) {
     const size_t rows = (size_t)p.B * p.Hkv * R;
-    const size_t need = rows * a.nsplit * (p.D + 2) * sizeof(float);
+    const size_t need = kWorkspaceCounterBytes + rows * a.nsplit * (p.D + 2) * sizeof(float);
     JPT_REQUIRE(p.workspace && p.workspace_bytes >= need, JPT_EWORKSPACE,
                 "flash_decode: workspace of %zu bytes needed, %zu given", need, p.workspace_bytes);
     JPT_REQUIRE(aligned(p.workspace, 16), JPT_EALIGN, "flash_decode: workspace must be 16-byte aligned");
-    a.ws_o = static_cast<float*>(p.workspace);
+    // the split-K partials live behind the counter header, which stays untouched
+    a.ws_o = reinterpret_cast<float*>(static_cast<char*>(p.workspace) + kWorkspaceCounterBytes);
     a.ws_m = a.ws_o + rows * a.nsplit * p.D;
     a.ws_l = a.ws_m + rows * a.nsplit;
   }
   if (int rc = launch_attention_generic(p, a, st)) return rc;
   if (a.nsplit > 1) return launch_splitk_merge(p, a, st);
+  return 0;
+}
+
+extern "C" int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, void* stream) {
+  JPT_REQUIRE(workspace || bytes == 0, JPT_EINVAL, "flash_decode_workspace_init: null workspace");
+  if (bytes == 0) return 0;
+  cudaError_t e = cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail((int)e, "flash_decode_workspace_init: %s", cudaGetErrorString(e));
   return 0;
 }
 

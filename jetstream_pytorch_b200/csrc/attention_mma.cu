@@ -1,15 +1,17 @@
 // Ragged flash-decode attention for head_dim 128 and int8 caches on tensor
-// cores (sm_100a): a persistent, work-balanced kernel plus a small merge kernel.
+// cores (sm_100a): one persistent, work-balanced kernel.
 //
 // Work model.  A "tile" is 64 consecutive valid tokens of one (sequence, KV
 // head) segment.  All tiles of all segments form one global list ordered by
-// (sequence, head, tile); every CTA of the persistent grid takes an equal,
-// contiguous share of that list, so ragged lengths cost nothing in balance.
-// A CTA therefore works on a run of "pieces" (its share cut at segment
-// borders).  A piece that covers its whole segment is written out as final
-// rows; the at most two pieces per CTA that do not (the first and the last
-// one) go to a per-CTA scratch slot and are combined by the merge kernel,
-// which also writes the rows of empty sequences.
+// (sequence, head, tile), each segment preceded by kPieceCost "overhead" slots
+// that stand for the fixed cost of starting and finishing a segment; every CTA
+// of the persistent grid takes an equal, contiguous share of that list, so
+// ragged lengths cost nothing in balance.  A CTA therefore works on a run of
+// "pieces" (its share cut at segment borders).  A piece that covers its whole
+// segment is written out as final rows.  A piece that does not goes to a
+// per-CTA scratch slot (there are at most two per CTA: its first and its last
+// piece); the CTA that delivers the last missing piece of a segment (found with
+// one wrapping atomic counter per segment) combines them and writes the rows.
 //
 // Data path.  K and V tiles travel global -> shared memory as 16-byte cp.async
 // copies through a 3-stage ring that keeps running across piece borders; the
@@ -25,15 +27,22 @@
 // int8 -> fp16 without convert instructions: (x ^ 0x80) is x + 128 as an
 // unsigned byte and 0x6400 | byte is the fp16 number 1024 + byte, so one PRMT
 // yields two halves worth x + 1152.  For K the offset is taken out after the
-// dot product (S - 1152 * sum_d q_d, exact enough in fp32); for V one HSUB2
-// removes it so the accumulators only ever hold the signal.  Contraction and
-// output indices are free to permute, so head_dim is assigned to MMA slots
-// such that every thread reads whole 16-byte chunks of token rows:
+// dot product (S - 1152 * sum_d q_d); for V an all-ones m-tile accumulates
+// sum_t P^T next to O^T and 1152 times that sum is subtracted when a piece is
+// written (both corrections are far below the fp32 accumulation noise that the
+// 2e-2 output tolerance allows).  Contraction and output indices are free to
+// permute, so head_dim is assigned to MMA slots such that every thread reads
+// whole 16-byte chunks of token rows:
 //   QK^T: k-step j, slots {2c,2c+1,2c+8,2c+9}   <-> d = 32c + 4j + {0,1,2,3}
 //   PV  : m-tile x, rows {g, g+8}               <-> d = 16g + x, 16g + 8 + x
 // (g = lane / 4, c = lane % 4).  Shared-memory rows are 128 bytes with their
 // 16-byte chunks XOR-swizzled by (row & 7), which makes both access patterns
 // bank-conflict free.
+//
+// The running maximum of the online softmax is only raised when a new logit
+// exceeds it by more than kLazy (log2 units), so the accumulators are rarely
+// rescaled; probabilities then stay below 2^kLazy, well inside fp16.  The true
+// maximum is tracked on the side for the (m, l) outputs.
 #include <limits.h>
 #include <math.h>
 
@@ -47,16 +56,19 @@ constexpr int kStages = 3;
 constexpr int kThreads = 128;
 constexpr int kD = 128;
 constexpr int kMaxRows = 16;
+constexpr int kPieceCost = 1;  // overhead slots charged per segment, in tiles
+constexpr float kLazy = 8.f;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
-// Scratch handed to the kernels (all inside the caller's workspace).
+// Scratch handed to the kernel (all inside the caller's workspace).
 struct MmaScratch {
-  int32_t* prefix;    // [B + 1] tiles before each sequence (per head); [B] = total per head
-  int32_t* seqinfo;   // [B][4] (first, n, use_add, -) for additive masks
-  float* part_o;      // [num_ctas][2][16][128] unnormalised partial outputs
-  float* part_m;      // [num_ctas][2][16] (log2 domain)
-  float* part_l;      // [num_ctas][2][16]
+  unsigned* counters;  // [B * Hkv] wrapping arrival counters, zero between launches
+  int32_t* seqinfo;    // [B][4] (first, n, use_add, -) for additive masks
+  float* part_o;       // [num_ctas][2][16][128] unnormalised partial outputs
+  float* part_m;       // [num_ctas][2][16] reference maximum (log2 domain)
+  float* part_l;       // [num_ctas][2][16] sum of exp2(x - reference)
+  float* part_t;       // [num_ctas][2][16] true maximum (log2 domain)
   int num_ctas;
 };
 
@@ -82,11 +94,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
   return r;
 }
-__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("sub.f16x2 %0, %1, %2;\n" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   uint32_t r;
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(a));
@@ -108,15 +115,42 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return r;
 }
 
+#ifdef JPT_ATTN_TIMING
+__device__ unsigned long long g_attn_timing[4096 * 4];
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned smid() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+#endif
+
+struct __align__(16) Stage {
+  uint8_t k[kTile * kD];  // K rows, then V rows: 16 KB that double as the merge buffer of a piece
+  uint8_t v[kTile * kD];
+};
+
 template <bool kRows16>
 struct __align__(128) Smem {
-  struct Stage {
-    uint8_t k[kTile * kD];  // K rows, then V rows: 16 KB that double as the warp-merge buffer
-    uint8_t v[kTile * kD];
-  } kv[kStages];
+  Stage kv[kStages];
   uint8_t q[kStages][(kRows16 ? 16 : 8) * kD * 2];  // bf16 query rows of the piece starting in this stage
   float ks2[kStages][kTile];                        // k_scale * sm_scale * log2(e)
   float vs[kStages][kTile];                         // v_scale
+};
+
+// What the producer publishes about the tile it put into a stage.
+struct TileMeta {
+  int b, h;        // sequence, KV head
+  int t, T;        // tile inside the segment (-1: no tile, the CTA's share is exhausted), tiles of the segment
+  int n, first;    // valid tokens of the sequence and position of its first one
+  int use_add;     // additive mask values must be applied
+  int first_cta;   // CTA that holds tile 0 of the segment
+  int parts;       // number of CTAs the segment is spread over
+  int pad[3];
 };
 
 // Valid range of a sequence for every mask mode (additive masks have been
@@ -133,34 +167,66 @@ __device__ __forceinline__ SeqRange seq_range_x(const AttnArgs& a, const MmaScra
   return seq_range(a, b);
 }
 
-// Position in the global tile list.
-struct Cursor {
-  int b, h, t, T;  // sequence, head, tile inside the segment, tiles per segment of b
-  SeqRange rg;
-  int use_add;
-};
+__device__ __forceinline__ int tiles_of(int n) { return (n + kTile - 1) / kTile; }
+__device__ __forceinline__ int slots_of(int n) { return n > 0 ? tiles_of(n) + kPieceCost : 0; }
 
-__device__ __forceinline__ void cursor_load_seq(const AttnArgs& a, const MmaScratch& x, Cursor& cu) {
-  cu.rg = seq_range_x(a, x, cu.b, &cu.use_add);
-  cu.T = (cu.rg.n + kTile - 1) / kTile;
-}
-
-__device__ __forceinline__ void cursor_advance(const AttnArgs& a, const MmaScratch& x, Cursor& cu) {
-  if (++cu.t < cu.T) return;
-  cu.t = 0;
-  if (++cu.h < a.Hkv) return;
-  cu.h = 0;
-  do {
-    ++cu.b;
-    if (cu.b >= a.B) {  // past the end: only reached after the CTA's last tile
-      cu.b = a.B - 1;
-      cu.T = 1;
-      cu.rg.n = 0;
-      cu.rg.first = 0;
-      return;
+// Combine the `parts` partials of one segment (CTAs first .. first+parts-1) and
+// write its R final rows.  `scratch` is at least (parts + 3) * 16 floats of
+// shared memory.  Called by a whole CTA.
+__device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int first, int parts, int64_t row_base,
+                              float* scratch) {
+  const int tid = threadIdx.x, R = a.R;
+  float* s_w = scratch;                     // [parts][16] weights
+  float* s_M = scratch + parts * kMaxRows;  // [16] reference maximum
+  float* s_L = s_M + kMaxRows;              // [16] denominator relative to s_M
+  for (int i = tid; i < parts * R; i += kThreads) {
+    const int pi = i / R, r = i - pi * R;
+    s_w[pi * kMaxRows + r] = __ldcg(&x.part_m[((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows + r]);
+  }
+  __syncthreads();
+  if (tid < R) {
+    float M = -INFINITY;
+    for (int pi = 0; pi < parts; ++pi) M = fmaxf(M, s_w[pi * kMaxRows + tid]);
+    s_M[tid] = M;
+  }
+  __syncthreads();
+  for (int i = tid; i < parts * R; i += kThreads) {
+    const int pi = i / R, r = i - pi * R;
+    const float mw = s_w[pi * kMaxRows + r];
+    s_w[pi * kMaxRows + r] = mw == -INFINITY ? 0.f : fast_exp2(mw - s_M[r]);
+  }
+  __syncthreads();
+  if (tid < R) {
+    float L = 0.f, mt = -INFINITY;
+    for (int pi = 0; pi < parts; ++pi) {
+      const int64_t pr = ((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows + tid;
+      L += s_w[pi * kMaxRows + tid] * __ldcg(&x.part_l[pr]);
+      mt = fmaxf(mt, __ldcg(&x.part_t[pr]));
     }
-    cursor_load_seq(a, x, cu);
-  } while (cu.T == 0);
+    s_L[tid] = L;
+    // report the true maximum and the denominator relative to it
+    if (a.m) a.m[row_base + tid] = mt * kLn2;
+    if (a.l) a.l[row_base + tid] = L > 0.f ? L * fast_exp2(s_M[tid] - mt) : 0.f;
+  }
+  __syncthreads();
+  float acc[kMaxRows];
+#pragma unroll
+  for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
+  for (int pi = 0; pi < parts; ++pi) {
+    const float* src = x.part_o + (((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows) * kD + tid;
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) {
+      if (r < R) acc[r] += s_w[pi * kMaxRows + r] * __ldcg(src + r * kD);
+    }
+  }
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
+#pragma unroll
+  for (int r = 0; r < kMaxRows; ++r) {
+    if (r < R) {
+      const float L = s_L[r];
+      o[(row_base + r) * kD + tid] = __float2bfloat16_rn(L > 0.f ? acc[r] / L : 0.f);
+    }
+  }
 }
 
 template <bool kRows16>
@@ -174,19 +240,30 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
   const int R = a.R;
   const bool quant = a.k_scale != nullptr;
   const int cta = blockIdx.x;
+#ifdef JPT_ATTN_TIMING
+  if (tid == 0 && cta < 4096) {
+    g_attn_timing[4 * cta] = globaltimer_ns();
+    g_attn_timing[4 * cta + 2] = smid();
+    g_attn_timing[4 * cta + 1] = 0;
+    g_attn_timing[4 * cta + 3] = 0;
+  }
+  int dbg_pieces = 0, dbg_tiles = 0;
+#endif
 
   // ------------------------------------------------------------------ schedule
-  // Tiles per sequence -> exclusive prefix over sequences (each thread owns a
-  // slice of ceil(B/128) sequences); scratch aliases the scale arrays.
+  // Slots per sequence (tiles + overhead) -> exclusive prefix over sequences;
+  // each thread owns a slice of ceil(B/128) sequences.  The scan scratch
+  // aliases the scale arrays, which are not in use yet.
   int* scan = reinterpret_cast<int*>(&sm.ks2[0][0]);  // 129 ints <= 3 * 64 floats
   __shared__ int s_start[4];
+  __shared__ int s_flag;
+  __shared__ TileMeta s_meta[kStages];
   const int per = (a.B + kThreads - 1) / kThreads;
   const int b_lo = min(a.B, tid * per), b_hi = min(a.B, b_lo + per);
   int mine = 0;
   for (int b = b_lo; b < b_hi; ++b) {
     int ua;
-    const SeqRange r = seq_range_x(a, x, b, &ua);
-    mine += (r.n + kTile - 1) / kTile;
+    mine += slots_of(seq_range_x(a, x, b, &ua).n);
   }
   scan[tid] = mine;
   __syncthreads();
@@ -212,52 +289,45 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
     if (lane == 31) scan[kThreads] = incl;
   }
   __syncthreads();
-  const int total_per_head = scan[kThreads];
-  const long long total = (long long)total_per_head * a.Hkv;
-  if (cta == 0) {  // publish the prefix for the merge kernel
-    int run = scan[tid];
-    for (int b = b_lo; b < b_hi; ++b) {
-      x.prefix[b] = run;
-      int ua;
-      const SeqRange r = seq_range_x(a, x, b, &ua);
-      run += (r.n + kTile - 1) / kTile;
-    }
-    if (tid == 0) x.prefix[a.B] = total_per_head;
-  }
-  const long long share = (total + x.num_ctas - 1) / x.num_ctas;
-  const long long G0 = (long long)cta * share;
-  const long long G1 = min(total, G0 + share);
-  if (share == 0 || G0 >= G1) return;
-  const int count = (int)(G1 - G0);
+  const int total = scan[kThreads] * a.Hkv;  // the host checked that this fits in 31 bits
+  const int share = (total + x.num_ctas - 1) / x.num_ctas;
+  const int G0 = cta * share;
+  const int G1 = min(total, G0 + share);
   {
-    // the thread whose slice holds tile G0 walks it and publishes (b, h, t)
-    const long long lo = (long long)scan[tid] * a.Hkv;
-    const long long hi = (long long)scan[tid + 1] * a.Hkv;
-    if (G0 >= lo && G0 < hi) {
-      long long run = lo;
+    // the thread whose slice holds slot G0 walks it and publishes (b, h, slot in segment)
+    const int lo = scan[tid] * a.Hkv, hi = scan[tid + 1] * a.Hkv;
+    if (G0 < G1 && G0 >= lo && G0 < hi) {
+      int run = lo;
       for (int b = b_lo; b < b_hi; ++b) {
         int ua;
-        const SeqRange r = seq_range_x(a, x, b, &ua);
-        const int T = (r.n + kTile - 1) / kTile;
-        const long long nxt = run + (long long)T * a.Hkv;
+        const int sl = slots_of(seq_range_x(a, x, b, &ua).n);
+        const int nxt = run + sl * a.Hkv;
         if (G0 < nxt) {
-          const int rem = (int)(G0 - run);
+          const int rem = G0 - run;
           s_start[0] = b;
-          s_start[1] = rem / T;
-          s_start[2] = rem % T;
+          s_start[1] = rem / sl;
+          s_start[2] = rem % sl;
           break;
         }
         run = nxt;
       }
     }
   }
-  __syncthreads();  // also orders the last reads of `scan` before the ring is filled
-  Cursor icur;      // producer position
-  icur.b = s_start[0];
-  icur.h = s_start[1];
-  icur.t = s_start[2];
-  cursor_load_seq(a, x, icur);
-  Cursor ccur = icur;  // consumer position
+  // Rows of empty sequences are nobody's tile: sequence b is cleared by CTA b mod grid.
+  for (int b = cta; b < a.B; b += gridDim.x) {
+    int ua;
+    if (seq_range_x(a, x, b, &ua).n == 0) {
+      const int64_t r0 = (int64_t)b * a.Hkv * R;
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
+      for (int i = tid; i < a.Hkv * R * kD; i += kThreads) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
+      for (int i = tid; i < a.Hkv * R; i += kThreads) {
+        if (a.m) a.m[r0 + i] = -INFINITY;
+        if (a.l) a.l[r0 + i] = 0.f;
+      }
+    }
+  }
+  __syncthreads();  // s_start visible; last reads of `scan` done before the ring is filled
+  if (G0 >= G1) return;
 
   const int8_t* kbase = static_cast<const int8_t*>(a.k);
   const int8_t* vbase = static_cast<const int8_t*>(a.v);
@@ -265,36 +335,150 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
   const __nv_bfloat16* mask = static_cast<const __nv_bfloat16*>(a.mask);
 
   // ------------------------------------------------------------------ producer
+  // Position of the next tile to fetch (uniform across the CTA) ...
+  int pb = s_start[0], ph = s_start[1], pt, pslot = G0;  // pslot: global slot index of tile pt
+  int pT, pn, pfirst, puse_add;
+  // ... and what follows from it for this thread: rows (tid / 8) + 16 i of a
+  // tile, 16-byte column tid % 8.  The swizzled shared-memory offset of row
+  // + 16 i is that of row plus 2048 i.
+  const int prow = tid >> 3, pcol = tid & 7;
+  const uint32_t pdst = (uint32_t)(prow * kD + ((pcol ^ (prow & 7)) << 4));
+  const bool tile_pages = a.paged && (a.page_size % kTile) == 0;
+  const bool rows_packed = a.paged ? tile_pages : (a.kv_s == kD);  // rows of a tile kD bytes apart
+  const int kv_s32 = (int)a.kv_s, sc_s32 = (int)a.sc_s;
+  const int8_t *kseg, *vseg;  // segment base + this thread's column
+  int64_t scseg;
+  int ppos;                   // physical position of row 0 of tile pt
+  int pfirst_cta, pparts;
+
+  auto load_seq = [&]() {
+    const SeqRange r = seq_range_x(a, x, pb, &puse_add);
+    pn = r.n;
+    pfirst = r.first;
+    pT = tiles_of(r.n);
+  };
+  auto seg_setup = [&]() {  // pt, pslot are set
+    const int64_t seg = a.paged ? (int64_t)ph * a.kv_h : (int64_t)pb * a.kv_b + (int64_t)ph * a.kv_h;
+    kseg = kbase + seg + pcol * 16;
+    vseg = vbase + seg + pcol * 16;
+    scseg = a.paged ? 0 : (int64_t)pb * a.sc_b;
+    ppos = pfirst + pt * kTile;
+    if (ppos >= a.S) ppos -= a.S;
+    const int t0slot = pslot - pt;  // slot of tile 0 of this segment
+    pfirst_cta = t0slot / share;
+    pparts = (t0slot + pT - 1) / share - pfirst_cta + 1;
+  };
+  auto advance = [&]() {
+    ++pslot;
+    ppos += kTile;
+    if (ppos >= a.S) ppos -= a.S;
+    if (++pt < pT) return;
+    pt = 0;
+    pslot += kPieceCost;  // the overhead slots of the next segment
+    if (++ph == a.Hkv) {
+      ph = 0;
+      do {
+        if (++pb >= a.B) {  // past the end of the list
+          pb = a.B - 1;
+          pslot = INT_MAX / 2;
+          return;
+        }
+        load_seq();
+      } while (pT == 0);
+    }
+    seg_setup();
+  };
+  {
+    load_seq();
+    const int v0 = s_start[2];  // slot inside the segment: overhead slots come first
+    if (v0 < kPieceCost) {
+      pslot += kPieceCost - v0;
+      pt = 0;
+    } else {
+      pt = v0 - kPieceCost;
+    }
+    seg_setup();
+  }
+
   float pend = 0.f;  // this thread's scale of the tile issued last, stored one iteration later
   int pend_stage = -1;
+  bool first_issue = true;
 
-  auto issue_tile = [&](int stage, bool piece_start) {
-    const int col = tid & 7;
-    const int j0 = icur.t * kTile;
+  auto issue_tile = [&](int stage) {
+    const int j0 = pt * kTile;
+    const bool piece_start = first_issue || pt == 0;
+    first_issue = false;
+    if (tid == 0) {
+      TileMeta mt;
+      mt.b = pb; mt.h = ph; mt.t = pt; mt.T = pT; mt.n = pn; mt.first = pfirst; mt.use_add = puse_add;
+      mt.first_cta = pfirst_cta; mt.parts = pparts;
+      mt.pad[0] = mt.pad[1] = mt.pad[2] = 0;
+      s_meta[stage] = mt;
+    }
+    const uint32_t kdst = smem_u32(&sm.kv[stage].k[0]) + pdst;
+    const uint32_t vdst = smem_u32(&sm.kv[stage].v[0]) + pdst;
+    int page = -1, page_pos0 = 0;
+    if (tile_pages) {
+      const int pi = j0 / a.page_size;
+      page = a.page_table[(int64_t)pb * a.max_pages + pi];
+      page_pos0 = pi * a.page_size;
+    }
+    if (rows_packed && j0 + kTile <= pn && ppos + kTile <= a.S) {
+      // whole tile valid, no ring wrap, rows kD bytes apart: one address per tensor
+      const int64_t off = a.paged ? (int64_t)page * a.kv_page + (int64_t)(j0 - page_pos0 + prow) * kD
+                                  : (int64_t)(ppos + prow) * kD;
+      const int8_t* kp = kseg + off;
+      const int8_t* vp = vseg + off;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = (tid >> 3) + 16 * i;
-      const int j = j0 + row;
-      const bool valid = j < icur.rg.n;
-      int64_t sidx;
-      const int64_t off = kv_row_offset(a, icur.b, icur.h, physical_pos(a, icur.rg, valid ? j : 0), &sidx);
-      const uint32_t dst = (uint32_t)(row * kD + ((col ^ (row & 7)) << 4));
-      cp_async16(smem_u32(&sm.kv[stage].k[0]) + dst, kbase + off + col * 16, valid);
-      cp_async16(smem_u32(&sm.kv[stage].v[0]) + dst, vbase + off + col * 16, valid);
+      for (int i = 0; i < 4; ++i) {
+        cp_async16(kdst + 2048 * i, kp + 2048 * i, true);
+        cp_async16(vdst + 2048 * i, vp + 2048 * i, true);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = prow + 16 * i;
+        const bool valid = j0 + r < pn;
+        int pos = valid ? ppos + r : ppos;
+        if (pos >= a.S) pos -= a.S;
+        int64_t off;
+        if (a.paged) {
+          int pg = page, tok = pos - page_pos0;
+          if (!tile_pages) {
+            pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
+            tok = pos % a.page_size;
+          }
+          off = (int64_t)pg * a.kv_page + (int64_t)tok * kD;
+        } else {
+          off = (int64_t)pos * kv_s32;
+        }
+        cp_async16(kdst + 2048 * i, kseg + off, valid);
+        cp_async16(vdst + 2048 * i, vseg + off, valid);
+      }
     }
     if (piece_start) {
-      const __nv_bfloat16* q = qbase + ((int64_t)icur.b * a.Hkv + icur.h) * R * kD;
+      const __nv_bfloat16* q = qbase + ((int64_t)pb * a.Hkv + ph) * R * kD;
       for (int ch = tid; ch < R * 16; ch += kThreads) {
         cp_async16(smem_u32(&sm.q[stage][0]) + ch * 16, q + ch * 8, true);
       }
     }
     if (quant) {
-      const int tok = tid & 63;
-      const int j = j0 + tok;
+      const int r = tid & 63;
       pend = 1.f;
-      if (j < icur.rg.n) {
+      if (j0 + r < pn) {
+        int pos = ppos + r;
+        if (pos >= a.S) pos -= a.S;
         int64_t sidx;
-        (void)kv_row_offset(a, icur.b, icur.h, physical_pos(a, icur.rg, j), &sidx);
+        if (a.paged) {
+          int pg = page, tok = pos - page_pos0;
+          if (!tile_pages) {
+            pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
+            tok = pos % a.page_size;
+          }
+          sidx = (int64_t)pg * a.page_size + tok;
+        } else {
+          sidx = scseg + (int64_t)pos * sc_s32;
+        }
         pend = load_scale(tid < 64 ? a.k_scale : a.v_scale, sidx, a.scale_is_f32);
       }
       pend_stage = stage;
@@ -308,38 +492,68 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
       pend_stage = -1;
     }
   };
+  // Fetch the next tile of the share into `stage`, or mark the stage as empty.
+  auto produce = [&](int stage) {
+    if (pslot < G1) {
+      flush_side();
+      issue_tile(stage);
+      advance();
+    } else if (tid == 0) {
+      s_meta[stage].t = -1;
+    }
+    cp_async_commit();
+  };
 
   // ------------------------------------------------------------------ consumer state
   uint32_t qb[NT][8][2];
   float bias[NT][2];
   float o[NT][8][4];
-  float m_run[NT][2], l_run[NT][2];
+  float wsum[NT][4];  // sum_t P^T[t][row] from an all-ones m-tile: carries the V offset
+  float m_run[NT][2], m_true[NT][2], l_run[NT][2];
   int piece_t0 = 0;
   const float unit2 = a.sm_scale * kLog2e;
-
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (s < count) {
-      flush_side();
-      issue_tile(s, s == 0 || icur.t == 0);
-      cursor_advance(a, x, icur);
-    }
-    cp_async_commit();
+  // shared-memory offsets of this thread's operands inside a stage
+  const int tok0 = warp * 16;
+  uint32_t koff[2][2], voff[4];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int row = tok0 + 8 * hh + g;
+    koff[hh][0] = row * kD + (((2 * c) ^ (row & 7)) << 4);
+    koff[hh][1] = row * kD + (((2 * c + 1) ^ (row & 7)) << 4);
+  }
+#pragma unroll
+  for (int r4 = 0; r4 < 4; ++r4) {
+    const int row = tok0 + 2 * c + (r4 & 1) + 8 * (r4 >> 1);
+    voff[r4] = kTile * kD + row * kD + ((g ^ (row & 7)) << 4);
   }
 
-  for (int i = 0; i < count; ++i) {
-    const int stage = i % kStages;
+  produce(0);
+  produce(1);
+
+  int stage = 0;
+  for (int i = 0;; ++i) {
     cp_async_wait<kStages - 2>();
     flush_side();
     __syncthreads();
-    if (i + kStages - 1 < count) {
-      issue_tile((i + kStages - 1) % kStages, icur.t == 0);
-      cursor_advance(a, x, icur);
+    {
+      int ps = stage + 2;
+      if (ps >= kStages) ps -= kStages;
+      produce(ps);
     }
-    cp_async_commit();
+    const TileMeta mt = s_meta[stage];
+    if (mt.t < 0) break;
+    const int next_stage = stage + 1 == kStages ? 0 : stage + 1;
+    const bool last_of_share = s_meta[next_stage].t < 0;
+#ifdef JPT_ATTN_TIMING
+    ++dbg_tiles;
+#endif
 
     // ---------------- start of a piece: query fragments and fresh state
-    if (i == 0 || ccur.t == 0) {
-      piece_t0 = ccur.t;
+    if (i == 0 || mt.t == 0) {
+      piece_t0 = mt.t;
+#ifdef JPT_ATTN_TIMING
+      ++dbg_pieces;
+#endif
       const uint32_t q_addr = smem_u32(&sm.q[stage][0]);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -369,16 +583,16 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
         bias[nt][0] = 1152.f * __shfl_sync(0xffffffffu, sum, 8 * c);
         bias[nt][1] = 1152.f * __shfl_sync(0xffffffffu, sum, 8 * c + 4);
         m_run[nt][0] = m_run[nt][1] = -INFINITY;
+        m_true[nt][0] = m_true[nt][1] = -INFINITY;
         l_run[nt][0] = l_run[nt][1] = 0.f;
 #pragma unroll
         for (int xx = 0; xx < 8; ++xx) o[nt][xx][0] = o[nt][xx][1] = o[nt][xx][2] = o[nt][xx][3] = 0.f;
+        wsum[nt][0] = wsum[nt][1] = wsum[nt][2] = wsum[nt][3] = 0.f;
       }
     }
 
     // ---------------- S^T = K Q^T for this warp's 16 tokens
-    const uint32_t ks_addr = smem_u32(&sm.kv[stage].k[0]);
-    const uint32_t vs_addr = smem_u32(&sm.kv[stage].v[0]);
-    const int tok0 = warp * 16;
+    const uint32_t st_addr = smem_u32(&sm.kv[stage]);
     float sc[NT][2][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -388,10 +602,8 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
       uint32_t kw[2][8];
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        const int row = tok0 + 8 * hh + g;
-        const uint32_t rbase = ks_addr + row * kD;
-        const uint4 k0 = lds128(rbase + (((2 * c) ^ (row & 7)) << 4));
-        const uint4 k1 = lds128(rbase + (((2 * c + 1) ^ (row & 7)) << 4));
+        const uint4 k0 = lds128(st_addr + koff[hh][0]);
+        const uint4 k1 = lds128(st_addr + koff[hh][1]);
         kw[hh][0] = k0.x; kw[hh][1] = k0.y; kw[hh][2] = k0.z; kw[hh][3] = k0.w;
         kw[hh][4] = k1.x; kw[hh][5] = k1.y; kw[hh][6] = k1.z; kw[hh][7] = k1.w;
       }
@@ -409,18 +621,21 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
     }
 
     // ---------------- logits (log2 domain), masking, online softmax
-    const int jlo = ccur.t * kTile + tok0 + g;  // logical index of token g; token g+8 is jlo + 8
-    const bool valid_lo = jlo < ccur.rg.n, valid_hi = (jlo + 8) < ccur.rg.n;
+    const int jlo = mt.t * kTile + tok0 + g;  // logical index of token g; token g+8 is jlo + 8
+    const bool valid_lo = jlo < mt.n, valid_hi = (jlo + 8) < mt.n;
     const float sk_lo = quant ? sm.ks2[stage][tok0 + g] : unit2;
     const float sk_hi = quant ? sm.ks2[stage][tok0 + 8 + g] : unit2;
     const float vs_lo = quant ? sm.vs[stage][tok0 + g] : 1.f;
     const float vs_hi = quant ? sm.vs[stage][tok0 + 8 + g] : 1.f;
     float mk_lo = 0.f, mk_hi = 0.f;
-    if (ccur.use_add) {  // additive mask that is not a plain 0 / -inf range (rare)
-      if (valid_lo) mk_lo = kLog2e * __bfloat162float(mask[(int64_t)ccur.b * a.mk_b + physical_pos(a, ccur.rg, jlo)]);
-      if (valid_hi) mk_hi = kLog2e * __bfloat162float(mask[(int64_t)ccur.b * a.mk_b + physical_pos(a, ccur.rg, jlo + 8)]);
+    if (mt.use_add) {  // additive mask that is not a plain 0 / -inf range (rare)
+      SeqRange rg;
+      rg.n = mt.n;
+      rg.first = mt.first;
+      if (valid_lo) mk_lo = kLog2e * __bfloat162float(mask[(int64_t)mt.b * a.mk_b + physical_pos(a, rg, jlo)]);
+      if (valid_hi) mk_hi = kLog2e * __bfloat162float(mask[(int64_t)mt.b * a.mk_b + physical_pos(a, rg, jlo + 8)]);
     }
-    uint32_t pb[NT][2];
+    uint32_t pb2[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       float xv[4];  // (tok g,row 2c) (tok g,row 2c+1) (tok g+8,row 2c) (tok g+8,row 2c+1)
@@ -437,16 +652,18 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
       }
-      const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
-      const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
-      const float al0 = fast_exp2(m_run[nt][0] - mu0), al1 = fast_exp2(m_run[nt][1] - mu1);
-      m_run[nt][0] = mn0;
-      m_run[nt][1] = mn1;
-      const float p00 = fast_exp2(xv[0] - mu0), p01 = fast_exp2(xv[1] - mu1);
-      const float p10 = fast_exp2(xv[2] - mu0), p11 = fast_exp2(xv[3] - mu1);
-      l_run[nt][0] = l_run[nt][0] * al0 + (p00 + p10);
-      l_run[nt][1] = l_run[nt][1] * al1 + (p01 + p11);
-      if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+      m_true[nt][0] = fmaxf(m_true[nt][0], mx0);
+      m_true[nt][1] = fmaxf(m_true[nt][1], mx1);
+      // raise the reference maximum only when it is exceeded by more than kLazy
+      const bool up0 = mx0 > m_run[nt][0] + kLazy, up1 = mx1 > m_run[nt][1] + kLazy;
+      if (__any_sync(0xffffffffu, up0 || up1)) {
+        const float mn0 = up0 ? mx0 : m_run[nt][0], mn1 = up1 ? mx1 : m_run[nt][1];
+        const float al0 = up0 ? fast_exp2(m_run[nt][0] - mn0) : 1.f;  // exp2(-inf) = 0 on the first tokens
+        const float al1 = up1 ? fast_exp2(m_run[nt][1] - mn1) : 1.f;
+        m_run[nt][0] = mn0;
+        m_run[nt][1] = mn1;
+        l_run[nt][0] *= al0;
+        l_run[nt][1] *= al1;
 #pragma unroll
         for (int xx = 0; xx < 8; ++xx) {
           o[nt][xx][0] *= al0;
@@ -454,10 +671,19 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
           o[nt][xx][2] *= al0;
           o[nt][xx][3] *= al1;
         }
+        wsum[nt][0] *= al0;
+        wsum[nt][1] *= al1;
       }
+      // m_run is -inf only while every logit of the row so far was masked
+      const float mu0 = m_run[nt][0] == -INFINITY ? 0.f : m_run[nt][0];
+      const float mu1 = m_run[nt][1] == -INFINITY ? 0.f : m_run[nt][1];
+      const float p00 = fast_exp2(xv[0] - mu0), p01 = fast_exp2(xv[1] - mu1);
+      const float p10 = fast_exp2(xv[2] - mu0), p11 = fast_exp2(xv[3] - mu1);
+      l_run[nt][0] += p00 + p10;
+      l_run[nt][1] += p01 + p11;
       // P^T as the B operand: transpose the two 8x8 (token x row) blocks
-      pb[nt][0] = movmatrix_trans(pack_half2(p00 * vs_lo, p01 * vs_lo));
-      pb[nt][1] = movmatrix_trans(pack_half2(p10 * vs_hi, p11 * vs_hi));
+      pb2[nt][0] = movmatrix_trans(pack_half2(p00 * vs_lo, p01 * vs_lo));
+      pb2[nt][1] = movmatrix_trans(pack_half2(p10 * vs_hi, p11 * vs_hi));
     }
 
     // ---------------- O^T += V^T P^T: this thread converts the 16-byte chunk g
@@ -466,8 +692,7 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
       uint32_t vw[4][4];
 #pragma unroll
       for (int r4 = 0; r4 < 4; ++r4) {
-        const int row = tok0 + 2 * c + (r4 & 1) + 8 * (r4 >> 1);
-        const uint4 q4 = lds128(vs_addr + row * kD + ((g ^ (row & 7)) << 4));
+        const uint4 q4 = lds128(st_addr + voff[r4]);
         vw[r4][0] = q4.x ^ 0x80808080u; vw[r4][1] = q4.y ^ 0x80808080u;
         vw[r4][2] = q4.z ^ 0x80808080u; vw[r4][3] = q4.w ^ 0x80808080u;
       }
@@ -482,24 +707,31 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
         for (int e = 0; e < 4; ++e) {
           const uint32_t sel = (e & 1) ? 0x5342u : 0x5140u;
           uint32_t af[4];
-          af[0] = hsub2_u32(prmt(e < 2 ? a01 : a23, 0x64646464u, sel), 0x64806480u);
-          af[1] = hsub2_u32(prmt(e < 2 ? b01 : b23, 0x64646464u, sel), 0x64806480u);
-          af[2] = hsub2_u32(prmt(e < 2 ? c01 : c23, 0x64646464u, sel), 0x64806480u);
-          af[3] = hsub2_u32(prmt(e < 2 ? d01 : d23, 0x64646464u, sel), 0x64806480u);
+          af[0] = prmt(e < 2 ? a01 : a23, 0x64646464u, sel);
+          af[1] = prmt(e < 2 ? b01 : b23, 0x64646464u, sel);
+          af[2] = prmt(e < 2 ? c01 : c23, 0x64646464u, sel);
+          af[3] = prmt(e < 2 ? d01 : d23, 0x64646464u, sel);
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) mma_f16(o[nt][4 * wd + e], af, pb[nt][0], pb[nt][1]);
+          for (int nt = 0; nt < NT; ++nt) mma_f16(o[nt][4 * wd + e], af, pb2[nt][0], pb2[nt][1]);
         }
       }
+      // V entered as code + 1152; the all-ones tile accumulates sum_t P^T so the
+      // offset can be taken out when the piece is written.
+      const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) mma_f16(wsum[nt], ones, pb2[nt][0], pb2[nt][1]);
     }
 
     // ---------------- end of a piece: merge the four warps and write out
-    if (i == count - 1 || ccur.t == ccur.T - 1) {
-      const bool is_final = piece_t0 == 0 && ccur.t == ccur.T - 1;
+    if (last_of_share || mt.t == mt.T - 1) {
+      const bool is_final = piece_t0 == 0 && mt.t == mt.T - 1;
       const int slot = piece_t0 > 0 ? 0 : 1;
-      const int64_t row_base = ((int64_t)ccur.b * a.Hkv + ccur.h) * R;
+      const int64_t row_base = ((int64_t)mt.b * a.Hkv + mt.h) * R;
       float* obuf = reinterpret_cast<float*>(&sm.kv[stage]);  // [4 warps][8 rows][128] = K and V of the stage
-      float* msm = &sm.ks2[stage][0];                            // [4][8]
-      float* lsm = &sm.vs[stage][0];                             // [4][8]
+      float* msm = &sm.ks2[stage][0];                          // [4][8] reference maxima of the warps
+      float* wsm = &sm.ks2[stage][32];                         // [4][8] weights of the warps
+      float* lsm = &sm.vs[stage][0];                           // [4][8] denominators of the warps
+      float* tsm = &sm.vs[stage][32];                          // [4][8] true maxima; then [8] M, [8] L, [8] Mtrue
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         float l0 = l_run[nt][0], l1 = l_run[nt][1];
@@ -510,107 +742,103 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
         }
         __syncthreads();  // every warp is done with the tile (and with the previous pass)
         {
+          const float w0 = 1152.f * wsum[nt][0], w1 = 1152.f * wsum[nt][1];
           float4* d0 = reinterpret_cast<float4*>(obuf + ((warp * 8 + 2 * c) * kD) + 16 * g);
           float4* d1 = reinterpret_cast<float4*>(obuf + ((warp * 8 + 2 * c + 1) * kD) + 16 * g);
-          d0[0] = make_float4(o[nt][0][0], o[nt][1][0], o[nt][2][0], o[nt][3][0]);
-          d0[1] = make_float4(o[nt][4][0], o[nt][5][0], o[nt][6][0], o[nt][7][0]);
-          d0[2] = make_float4(o[nt][0][2], o[nt][1][2], o[nt][2][2], o[nt][3][2]);
-          d0[3] = make_float4(o[nt][4][2], o[nt][5][2], o[nt][6][2], o[nt][7][2]);
-          d1[0] = make_float4(o[nt][0][1], o[nt][1][1], o[nt][2][1], o[nt][3][1]);
-          d1[1] = make_float4(o[nt][4][1], o[nt][5][1], o[nt][6][1], o[nt][7][1]);
-          d1[2] = make_float4(o[nt][0][3], o[nt][1][3], o[nt][2][3], o[nt][3][3]);
-          d1[3] = make_float4(o[nt][4][3], o[nt][5][3], o[nt][6][3], o[nt][7][3]);
+          d0[0] = make_float4(o[nt][0][0] - w0, o[nt][1][0] - w0, o[nt][2][0] - w0, o[nt][3][0] - w0);
+          d0[1] = make_float4(o[nt][4][0] - w0, o[nt][5][0] - w0, o[nt][6][0] - w0, o[nt][7][0] - w0);
+          d0[2] = make_float4(o[nt][0][2] - w0, o[nt][1][2] - w0, o[nt][2][2] - w0, o[nt][3][2] - w0);
+          d0[3] = make_float4(o[nt][4][2] - w0, o[nt][5][2] - w0, o[nt][6][2] - w0, o[nt][7][2] - w0);
+          d1[0] = make_float4(o[nt][0][1] - w1, o[nt][1][1] - w1, o[nt][2][1] - w1, o[nt][3][1] - w1);
+          d1[1] = make_float4(o[nt][4][1] - w1, o[nt][5][1] - w1, o[nt][6][1] - w1, o[nt][7][1] - w1);
+          d1[2] = make_float4(o[nt][0][3] - w1, o[nt][1][3] - w1, o[nt][2][3] - w1, o[nt][3][3] - w1);
+          d1[3] = make_float4(o[nt][4][3] - w1, o[nt][5][3] - w1, o[nt][6][3] - w1, o[nt][7][3] - w1);
           if (g == 0) {
             msm[warp * 8 + 2 * c] = m_run[nt][0];
             msm[warp * 8 + 2 * c + 1] = m_run[nt][1];
             lsm[warp * 8 + 2 * c] = l0;
             lsm[warp * 8 + 2 * c + 1] = l1;
+            tsm[warp * 8 + 2 * c] = m_true[nt][0];
+            tsm[warp * 8 + 2 * c + 1] = m_true[nt][1];
           }
+        }
+        __syncthreads();
+        float rM = 0.f, rL = 0.f, rT = 0.f;
+        if (tid < 32) {  // thread (w, r): weight of warp w for row r; w == 0 also reduces the row
+          const int w = tid >> 3, r = tid & 7;
+          const float M = fmaxf(fmaxf(msm[r], msm[8 + r]), fmaxf(msm[16 + r], msm[24 + r]));
+          const float mw = msm[w * 8 + r];
+          wsm[w * 8 + r] = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
+          if (w == 0) {
+            float L = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < 4; ++ww) {
+              const float m2 = msm[ww * 8 + r];
+              L += (m2 == -INFINITY ? 0.f : fast_exp2(m2 - M)) * lsm[ww * 8 + r];
+            }
+            rM = M;
+            rL = L;
+            rT = fmaxf(fmaxf(tsm[r], tsm[8 + r]), fmaxf(tsm[16 + r], tsm[24 + r]));
+          }
+        }
+        __syncthreads();
+        if (tid < 8) {  // after the barrier: the reduced rows replace the per-warp true maxima
+          tsm[tid] = rM;
+          tsm[8 + tid] = rL;
+          tsm[16 + tid] = rT;
         }
         __syncthreads();
         const int rows_here = min(8, R - 8 * nt);
         for (int r = 0; r < rows_here; ++r) {
-          float M = msm[r];
+          float acc = 0.f;
 #pragma unroll
-          for (int w = 1; w < 4; ++w) M = fmaxf(M, msm[w * 8 + r]);
-          float L = 0.f, acc = 0.f;
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const float mw = msm[w * 8 + r];
-            const float wg = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
-            L += wg * lsm[w * 8 + r];
-            acc += wg * obuf[(w * 8 + r) * kD + tid];
-          }
+          for (int w = 0; w < 4; ++w) acc += wsm[w * 8 + r] * obuf[(w * 8 + r) * kD + tid];
           const int rr = 8 * nt + r;
+          const float M = tsm[r], L = tsm[8 + r], Mt = tsm[16 + r];
           if (is_final) {
             const int64_t row = row_base + rr;
             static_cast<__nv_bfloat16*>(a.o)[row * kD + tid] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
             if (tid == 0) {
-              if (a.m) a.m[row] = M * kLn2;
-              if (a.l) a.l[row] = L;
+              if (a.m) a.m[row] = Mt * kLn2;
+              if (a.l) a.l[row] = L > 0.f ? L * fast_exp2(M - Mt) : 0.f;
             }
           } else {
             const int64_t pr = ((int64_t)cta * 2 + slot) * kMaxRows + rr;
-            x.part_o[pr * kD + tid] = acc;
+            __stcg(&x.part_o[pr * kD + tid], acc);
             if (tid == 0) {
-              x.part_m[pr] = M;
-              x.part_l[pr] = L;
+              __stcg(&x.part_m[pr], M);
+              __stcg(&x.part_l[pr], L);
+              __stcg(&x.part_t[pr], Mt);
             }
           }
         }
       }
+      if (!is_final) {
+        // Whoever delivers the last piece of the segment combines all of them.
+        // The counter wraps back to zero on that arrival, ready for the next launch.
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+          const unsigned old = atomicInc(&x.counters[mt.b * a.Hkv + mt.h], (unsigned)(mt.parts - 1));
+          s_flag = old == (unsigned)(mt.parts - 1);
+        }
+        __syncthreads();
+        if (s_flag) {
+          __threadfence();
+          merge_segment(a, x, mt.first_cta, mt.parts, row_base, obuf);
+        }
+      }
       // The next iteration's barrier orders these reads before the stage is refilled.
     }
-    cursor_advance(a, x, ccur);
+    stage = next_stage;
   }
   cp_async_wait<0>();
-}
-
-// One block per (sequence, head) segment: combine the partials of segments that
-// were cut by CTA borders and write the rows of empty sequences.
-__global__ void __launch_bounds__(kThreads) flash_decode_merge_kernel(AttnArgs a, MmaScratch x) {
-  const int seg = blockIdx.x;
-  const int b = seg / a.Hkv, h = seg % a.Hkv;
-  const int R = a.R, tid = threadIdx.x;
-  const int T = x.prefix[b + 1] - x.prefix[b];
-  const int64_t row_base = (int64_t)seg * R;
-  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
-  if (T == 0) {
-    for (int r = 0; r < R; ++r) {
-      o[(row_base + r) * kD + tid] = __float2bfloat16_rn(0.f);
-      if (tid == 0) {
-        if (a.m) a.m[row_base + r] = -INFINITY;
-        if (a.l) a.l[row_base + r] = 0.f;
-      }
-    }
-    return;
+#ifdef JPT_ATTN_TIMING
+  if (tid == 0 && cta < 4096) {
+    g_attn_timing[4 * cta + 1] = globaltimer_ns();
+    g_attn_timing[4 * cta + 3] = (unsigned long long)dbg_tiles | ((unsigned long long)dbg_pieces << 32);
   }
-  const long long total = (long long)x.prefix[a.B] * a.Hkv;
-  const long long share = (total + x.num_ctas - 1) / x.num_ctas;
-  const long long gs = (long long)x.prefix[b] * a.Hkv + (long long)h * T;
-  const int first = (int)(gs / share), last = (int)((gs + T - 1) / share);
-  if (first == last) return;  // written as final rows by the main kernel
-  for (int r = 0; r < R; ++r) {
-    float M = -INFINITY;
-    for (int cta = first; cta <= last; ++cta) {
-      const int slot = cta == first ? 1 : 0;
-      M = fmaxf(M, x.part_m[((int64_t)cta * 2 + slot) * kMaxRows + r]);
-    }
-    float L = 0.f, acc = 0.f;
-    for (int cta = first; cta <= last; ++cta) {
-      const int slot = cta == first ? 1 : 0;
-      const int64_t pr = ((int64_t)cta * 2 + slot) * kMaxRows + r;
-      const float mw = x.part_m[pr];
-      const float wg = mw == -INFINITY ? 0.f : fast_exp2(mw - M);
-      L += wg * x.part_l[pr];
-      acc += wg * x.part_o[pr * kD + tid];
-    }
-    o[(row_base + r) * kD + tid] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-    if (tid == 0) {
-      if (a.m) a.m[row_base + r] = M * kLn2;
-      if (a.l) a.l[row_base + r] = L;
-    }
-  }
+#endif
 }
 
 // Additive masks -> valid ranges.  A mask row whose finite entries form one run
@@ -680,7 +908,7 @@ int sm_count() {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct ScratchLayout {
-  size_t prefix, seqinfo, part_m, part_l, part_o, total;
+  size_t counters, seqinfo, part_m, part_l, part_t, part_o, total;
   int num_ctas;
 };
 
@@ -689,13 +917,15 @@ ScratchLayout scratch_layout(const jpt_attn_params& p) {
   ScratchLayout s;
   s.num_ctas = sm_count() * (R > 8 ? 2 : 4);
   size_t off = 0;
-  s.prefix = off;
-  off = align_up(off + sizeof(int32_t) * (p.B + 1), 256);
+  s.counters = off;  // fixed-size header shared by every shape that uses the workspace
+  off = kWorkspaceCounterBytes;
   s.seqinfo = off;
   off = align_up(off + sizeof(int32_t) * 4 * p.B, 256);
   s.part_m = off;
   off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
   s.part_l = off;
+  off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
+  s.part_t = off;
   off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
   s.part_o = off;
   off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows * kD, 256);
@@ -715,6 +945,11 @@ bool attention_mma_eligible(const jpt_attn_params& p) {
   } else if (p.kv_b % 16 || p.kv_h % 16 || p.kv_s % 16) {
     return false;
   }
+  // the merge of a segment's pieces keeps (pieces + 3) * 16 floats in a 16 KB buffer
+  if (p.S > 16000) return false;
+  if ((size_t)p.B * p.Hkv * sizeof(unsigned) > kWorkspaceCounterBytes) return false;
+  // slot indices are 32-bit
+  if ((double)p.B * p.Hkv * ((double)p.S / kTile + 1 + kPieceCost) > 1.0e9) return false;
   return true;
 }
 
@@ -727,10 +962,11 @@ int launch_attention_mma(const jpt_attn_params& p, const AttnArgs& a, cudaStream
   JPT_REQUIRE(aligned(p.workspace, 256), JPT_EALIGN, "flash_decode: workspace must be 256-byte aligned");
   char* ws = static_cast<char*>(p.workspace);
   MmaScratch x;
-  x.prefix = reinterpret_cast<int32_t*>(ws + lay.prefix);
+  x.counters = reinterpret_cast<unsigned*>(ws + lay.counters);
   x.seqinfo = reinterpret_cast<int32_t*>(ws + lay.seqinfo);
   x.part_m = reinterpret_cast<float*>(ws + lay.part_m);
   x.part_l = reinterpret_cast<float*>(ws + lay.part_l);
+  x.part_t = reinterpret_cast<float*>(ws + lay.part_t);
   x.part_o = reinterpret_cast<float*>(ws + lay.part_o);
   x.num_ctas = lay.num_ctas;
 
@@ -751,9 +987,14 @@ int launch_attention_mma(const jpt_attn_params& p, const AttnArgs& a, cudaStream
   } else {
     flash_decode_i8_kernel<false><<<lay.num_ctas, kThreads, sizeof(Smem<false>), st>>>(a, x);
   }
-  if (int rc = check_launch("flash_decode_i8_kernel")) return rc;
-  flash_decode_merge_kernel<<<a.B * a.Hkv, kThreads, 0, st>>>(a, x);
-  return check_launch("flash_decode_merge_kernel");
+  return check_launch("flash_decode_i8_kernel");
 }
 
 }  // namespace jpt
+
+#ifdef JPT_ATTN_TIMING
+// Debug builds only: per-CTA (start ns, end ns, SM id, tiles | pieces << 32) of the last launch.
+extern "C" int jpt_debug_attn_timing(unsigned long long* out_host, int n_ctas) {
+  return (int)cudaMemcpyFromSymbol(out_host, jpt::g_attn_timing, sizeof(unsigned long long) * 4 * n_ctas);
+}
+#endif
