@@ -274,6 +274,14 @@ size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p);
  * overlap on the GPU.  (No counterpart in the reference.)
  */
 int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, void* stream);
+/*
+ * Health word of the attention kernels that used this workspace: 0, or a
+ * positive code if a bounded wait inside a kernel ever gave up (the kernel then
+ * returns early and its outputs are invalid).  Copies one int to the host and
+ * SYNCHRONISES the stream: a diagnostic for tests, not for the step path.
+ * (No counterpart in the reference.)
+ */
+int jpt_flash_decode_status(const void* workspace, void* stream);
 
 /*
  * Merge two softmax partials: g = max(m1,m2); o = (l1 e^{m1-g} o1 + l2 e^{m2-g}

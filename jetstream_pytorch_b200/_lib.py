@@ -70,6 +70,7 @@ _SIGNATURES = {
     "jpt_flash_decode": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
     "jpt_flash_decode_workspace_bytes": (c_size_t, [ctypes.POINTER(AttnParams)]),
     "jpt_flash_decode_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "jpt_flash_decode_status": (c_int, [c_void_p, c_void_p]),
     "jpt_merge_partials": (c_int, [c_void_p] * 6 + [c_int, c_void_p, c_int, c_i64, c_int, c_void_p]),
 }
 

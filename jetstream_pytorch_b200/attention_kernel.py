@@ -33,6 +33,19 @@ def _workspace(device, nbytes):
   return ws
 
 
+def kernel_status(device=None):
+  """0 if no attention kernel on `device` ever gave up on a bounded wait, else
+  the code it recorded.  Synchronises the current stream (diagnostic only)."""
+  for dev, ws in _workspaces.items():
+    if device is None or torch.device(device) == dev:
+      rc = _lib.lib().jpt_flash_decode_status(_lib.ptr(ws), _lib.stream())
+      if rc < 0:
+        _lib.check(rc)
+      if rc:
+        return rc
+  return 0
+
+
 def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale=None, v_scale=None,
                   scale_strides=(0, 0), mask_mode=_lib.MASK_NONE, start=None, end=None, mask=None,
                   mask_strides=(0, 0), sm_scale=1.0, kv_strides=(0, 0, 0), n_kv_heads=None, seq=None,

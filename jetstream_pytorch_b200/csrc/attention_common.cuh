@@ -82,7 +82,9 @@ __device__ __forceinline__ float load_scale(const void* base, int64_t idx, int i
 
 // Every workspace starts with this many bytes of per-segment arrival counters
 // that must stay zero between launches; no kernel puts anything else there.
-constexpr size_t kWorkspaceCounterBytes = 256 * 1024;  // one 32-bit counter for up to 65536 (sequence, head) pairs
+constexpr size_t kWorkspaceCounterBytes = 256 * 1024;  // header: counters, then one status word in its last 256 bytes
+constexpr size_t kWorkspaceStatusOffset = kWorkspaceCounterBytes - 256;
+constexpr size_t kWorkspaceMaxSegments = kWorkspaceStatusOffset / sizeof(unsigned);  // (sequence, head) pairs
 
 // Host-side launchers implemented by the individual kernels.
 int launch_attention_generic(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);

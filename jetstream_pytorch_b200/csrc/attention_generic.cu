@@ -321,6 +321,17 @@ extern "C" int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, vo
   return 0;
 }
 
+extern "C" int jpt_flash_decode_status(const void* workspace, void* stream) {
+  JPT_REQUIRE(workspace, JPT_EINVAL, "flash_decode_status: null workspace");
+  int status = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&status, static_cast<const char*>(workspace) + kWorkspaceStatusOffset, sizeof(int),
+                                  cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail((int)e, "flash_decode_status: %s", cudaGetErrorString(e));
+  return status;
+}
+
 extern "C" int jpt_merge_partials(const void* o1, const float* m1, const float* l1, const void* o2,
                                   const float* m2, const float* l2, int in_dtype, void* o, int out_dtype,
                                   int64_t rows, int D, void* stream) {

@@ -947,7 +947,7 @@ bool attention_mma_eligible(const jpt_attn_params& p) {
   }
   // the merge of a segment's pieces keeps (pieces + 3) * 16 floats in a 16 KB buffer
   if (p.S > 16000) return false;
-  if ((size_t)p.B * p.Hkv * sizeof(unsigned) > kWorkspaceCounterBytes) return false;
+  if ((size_t)p.B * p.Hkv > kWorkspaceMaxSegments) return false;
   // slot indices are 32-bit
   if ((double)p.B * p.Hkv * ((double)p.S / kTile + 1 + kPieceCost) > 1.0e9) return false;
   return true;

@@ -835,6 +835,16 @@ def test_attention_kernel_caller_against_oracle_decode_step():
   assert close(out[:, :, 0], eo)
 
 
+def test_attention_kernels_never_gave_up_on_a_wait():
+  """Runs after the attention tests of this file: the bounded waits inside the
+  persistent kernel must never have timed out."""
+  from jetstream_pytorch_b200 import attention_kernel as ak
+
+  q, k, v, ks, vs, start, end = _ragged_case(70, 4, 32, 8, 256, 128, True, True)
+  ak.ragged_mha(cu(q), cu(k), cu(v), 0, cu(start), cu(end), None, None, cu(ks), cu(vs), ring=True)
+  assert ak.kernel_status() == 0
+
+
 def test_argument_errors_are_reported_not_launched():
   from jetstream_pytorch_b200 import attention_kernel as ak
   from jetstream_pytorch_b200.insert import insert_dense
