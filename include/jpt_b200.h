@@ -284,6 +284,29 @@ int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, void* stream)
 int jpt_flash_decode_status(const void* workspace, void* stream);
 
 /*
+ * jpt_flash_decode for callers that cannot hand over a workspace because they
+ * cannot allocate device memory at the point of the call: code running inside a
+ * serving loop whose memory pool is fixed and fully handed out, a plugin host
+ * that forbids allocation after start-up, a callback on a path where cudaMalloc
+ * (which synchronises the device) must not run.  p->workspace and
+ * p->workspace_bytes are ignored; the scratch is a 16 MiB array built into the
+ * library, one per GPU that loads the library, held until the process exits.
+ * This entry point has no counterpart in the reference.
+ *
+ *   - Shapes whose jpt_flash_decode_workspace_bytes() exceeds 16 MiB are rejected
+ *     with JPT_EWORKSPACE; nothing is launched.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call outside any stream capture.
+ *   - No cudaMalloc / cudaFree / allocating library routine is called, here or
+ *     in anything this function calls.
+ *   - All calls on a GPU share the one array and each call clears the header it
+ *     relies on, so two calls that can overlap on the GPU (different streams
+ *     without ordering, concurrent host threads) race.  Calls ordered on one
+ *     stream are safe.
+ */
+int jpt_flash_decode_static(const jpt_attn_params* p, void* stream);
+
+/*
  * Merge two softmax partials: g = max(m1,m2); o = (l1 e^{m1-g} o1 + l2 e^{m2-g}
  * o2) / (l1 e^{m1-g} + l2 e^{m2-g}).  Replaces the "attn_global" block of
  * AttentionKernel / Int8KVAttentionKernel, jetstream_pt/layers.py:539-550,

@@ -68,6 +68,7 @@ _SIGNATURES = {
                                          c_void_p, c_void_p] + [c_int] * 7 + [c_i64] * 5 + [c_void_p]),
     "jpt_quantize_tokens": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "jpt_flash_decode": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
+    "jpt_flash_decode_static": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
     "jpt_flash_decode_workspace_bytes": (c_size_t, [ctypes.POINTER(AttnParams)]),
     "jpt_flash_decode_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "jpt_flash_decode_status": (c_int, [c_void_p, c_void_p]),

@@ -49,9 +49,14 @@ def kernel_status(device=None):
 def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale=None, v_scale=None,
                   scale_strides=(0, 0), mask_mode=_lib.MASK_NONE, start=None, end=None, mask=None,
                   mask_strides=(0, 0), sm_scale=1.0, kv_strides=(0, 0, 0), n_kv_heads=None, seq=None,
-                  want_ml=True, num_splits=0, force_generic=False):
+                  want_ml=True, num_splits=0, force_generic=False, static_scratch=False):
   """q [B,Hq,Tq,D] contiguous.  Returns o (q's shape and dtype), m, l float32
-  [B,Hq,Tq] (or None, None)."""
+  [B,Hq,Tq] (or None, None).
+
+  `static_scratch=True` routes the call through `jpt_flash_decode_static`: no
+  workspace tensor is created or passed, the kernels use the scratch array
+  built into the library (for callers that must not allocate at this point;
+  shapes needing more than its 16 MiB raise ValueError)."""
   q = q.contiguous()
   b, hq, tq, d = q.shape
   dev = q.device
@@ -99,11 +104,14 @@ def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale
     p.m, p.l = _lib.ptr(m), _lib.ptr(l)
   p.num_splits, p.force_generic = num_splits, int(force_generic)
   lib = _lib.lib()
-  need = lib.jpt_flash_decode_workspace_bytes(ctypes.byref(p))
-  if need:
-    ws = _workspace(dev, need)
-    p.workspace, p.workspace_bytes = _lib.ptr(ws), ws.numel()
-  _lib.check(lib.jpt_flash_decode(ctypes.byref(p), _lib.stream()))
+  if static_scratch:
+    _lib.check(lib.jpt_flash_decode_static(ctypes.byref(p), _lib.stream()))
+  else:
+    need = lib.jpt_flash_decode_workspace_bytes(ctypes.byref(p))
+    if need:
+      ws = _workspace(dev, need)
+      p.workspace, p.workspace_bytes = _lib.ptr(ws), ws.numel()
+    _lib.check(lib.jpt_flash_decode(ctypes.byref(p), _lib.stream()))
   del keep
   return o, m, l
 

@@ -321,6 +321,55 @@ extern "C" int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, vo
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// Attention without a caller-provided workspace.
+//
+// The scratch lives in this file-scope device array.  Every GPU whose context
+// loads the library carries its own 16 MiB copy until the process exits; all
+// calls on one GPU share it.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxStaticDevices = 64;
+void* g_static_scratch_addr[kMaxStaticDevices] = {};  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int jpt_flash_decode_static(const jpt_attn_params* pp, void* stream) {
+  JPT_REQUIRE(pp, JPT_EINVAL, "flash_decode_static: null params");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail((int)e, "flash_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  JPT_REQUIRE(dev >= 0 && dev < kMaxStaticDevices, JPT_ERANGE, "flash_decode_static: device ordinal %d unsupported", dev);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // One-time set-up for the current device: `g_static_scratch` as written in
+    // host code is only a handle, the address the kernels need comes from here.
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      return fail(e != cudaSuccess ? (int)e : JPT_EINVAL, "flash_decode_static: cudaGetSymbolAddress: %s",
+                  cudaGetErrorString(e));
+    }
+    g_static_scratch_addr[dev] = ptr;
+  }
+  jpt_attn_params p = *pp;
+  p.workspace = g_static_scratch_addr[dev];
+  p.workspace_bytes = kStaticScratchBytes;
+  if (int rc = validate(p)) return rc;
+  const size_t need = jpt_flash_decode_workspace_bytes(&p);
+  JPT_REQUIRE(need <= kStaticScratchBytes, JPT_EWORKSPACE,
+              "flash_decode_static: this shape needs %zu bytes of scratch, the built-in scratch holds %zu; "
+              "use jpt_flash_decode with a workspace of your own",
+              need, kStaticScratchBytes);
+  if (need) {
+    // The array keeps whatever the previous call left behind.  The arrival
+    // counters and the status word at its start must read zero on entry.
+    e = cudaMemsetAsync(p.workspace, 0, kWorkspaceCounterBytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail((int)e, "flash_decode_static: clearing the scratch header: %s", cudaGetErrorString(e));
+  }
+  return jpt_flash_decode(&p, stream);
+}
+
 extern "C" int jpt_flash_decode_status(const void* workspace, void* stream) {
   JPT_REQUIRE(workspace, JPT_EINVAL, "flash_decode_status: null workspace");
   int status = 0;
