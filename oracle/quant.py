@@ -14,18 +14,28 @@ def _rt(x32, dtype):
   return x32.to(dtype).to(torch.float32)
 
 
-def quantize_decode(val: torch.Tensor):
+def local_amax(val: torch.Tensor):
+  """max |val| over (heads, dim) per (batch, token) in fp32: the partial that a
+  rank holding only some KV heads contributes; the reference gets the full
+  maximum from GSPMD's reduction over the sharded head axis
+  (jetstream_pt/cache_manager.py:404-410, 532-535)."""
+  return val.to(torch.float32).abs().amax(dim=(-3, -1), keepdim=True)
+
+
+def quantize_decode(val: torch.Tensor, amax=None):
   """`Int8KVCacheGenerate.quantize`, jetstream_pt/cache_manager.py:532-537.
 
   val [B, H, T, D] (bf16 or fp32).  scale = amax(|val|) over (H, D) / 127, one
   per (batch, token); codes = (val / scale) cast to int8, i.e. truncated toward
   zero, with no clamp and no epsilon.  An all-zero token has scale 0 and 0/0 =
   NaN, which the cast turns into code 0.
+  `amax` (fp32 [B,1,T,1]) replaces the local maximum when the heads are sharded
+  and the caller has max-reduced `local_amax` over the ranks.
   Returns (codes int8 [B,H,T,D], scale [B,1,T,1] in val's dtype).
   """
   dt = val.dtype
   v = val.to(torch.float32)
-  a = v.abs().amax(dim=(-3, -1), keepdim=True)
+  a = v.abs().amax(dim=(-3, -1), keepdim=True) if amax is None else amax.to(torch.float32)
   s = _rt(a / 127.0, dt)
   t = _rt(v / s, dt)
   t = torch.where(torch.isnan(t), torch.zeros_like(t), t)

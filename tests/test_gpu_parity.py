@@ -182,6 +182,34 @@ def test_int8_update_large_shapes_full_cache_equality():
     assert same(t, e), n
 
 
+def test_int8_update_head_sharded_two_phase_equals_unsharded():
+  """KV heads split over two "ranks" (emulated on one GPU): local amax per
+  rank, element-wise max (the all-reduce), update with the reduced amax.  Codes,
+  scales and cache rows equal the unsharded oracle's slice."""
+  from jetstream_pytorch_b200.cache_manager import Int8KVCacheGenerate
+
+  g = torch.Generator().manual_seed(33)
+  b, h, s, d = 12, 8, 64, 128
+  xk = torch.randn(b, h, 1, d, generator=g).to(torch.bfloat16)
+  xv = torch.randn(b, h, 1, d, generator=g).to(torch.bfloat16)
+  xk[3] = 0
+  pos = torch.randint(0, s, (b,), generator=g)
+  ck = torch.zeros(b, h, s, d, dtype=torch.int8)
+  sk = torch.ones(b, 1, s, 1, dtype=torch.bfloat16)
+  exp = oc.int8_update(ck, ck, sk, sk, xk, xv, pos, ring_buffer=False, lazy=False)
+  env = make_env(batch_size=b, ring_buffer=False)
+  halves = [slice(0, 4), slice(4, 8)]
+  caches = [Int8KVCacheGenerate(cu(ck[:, hs]).contiguous(), cu(ck[:, hs]).contiguous(), cu(sk).clone(),
+                                cu(sk).clone(), cu(pos), env=env) for hs in halves]
+  amax = [c.local_amax(cu(xk[:, hs]).contiguous(), cu(xv[:, hs]).contiguous()) for c, hs in zip(caches, halves)]
+  red = torch.maximum(amax[0], amax[1])
+  for c, hs in zip(caches, halves):
+    r = c.update(cu(xk[:, hs]).contiguous(), cu(xv[:, hs]).contiguous(), 0, amax=red)
+    assert same(r[0], exp[0][:, hs]) and same(r[1], exp[1][:, hs])
+    assert same(r[2], exp[2][:, hs]) and same(r[3], exp[3][:, hs])
+    assert same(r[4], exp[4]) and same(r[5], exp[5]) and same(r[6], exp[6]) and same(r[7], exp[7])
+
+
 # ---------------------------------------------------------------------------
 # bf16 / fp32 dense cache
 # ---------------------------------------------------------------------------
