@@ -259,7 +259,7 @@ def run_cuda(args):
     device_step()
   torch.cuda.synchronize()
   graph = None
-  if world == 1 and not args.no_graph:
+  if not args.no_graph:  # with N > 1 the NCCL max-reductions are captured too
     try:
       graph = torch.cuda.CUDAGraph()
       with torch.cuda.graph(graph):
@@ -310,7 +310,7 @@ def run_cuda(args):
 
   reps = max(1, args.steps // 2)
   attn_fn, app_fn = attn_only, append_only
-  if world == 1 and not args.no_graph and graph is not None:
+  if not args.no_graph and graph is not None:
     try:
       g_attn, g_app = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
       attn_only(); append_only(); torch.cuda.synchronize()
@@ -371,9 +371,20 @@ def run_cuda(args):
   h2d = q_h.numel() * 2 + k_h.numel() * 2 + v_h.numel() * 2
   d2h = o_h.numel() * 2
 
-  if rank != 0:
+  def leave():
+    """Ranks leave together.  With NCCL work captured in CUDA graphs the process
+    group teardown has been seen to block, so multi-rank runs skip it and exit
+    once every rank has finished its GPU work."""
     if world > 1:
-      dist.destroy_process_group()
+      torch.cuda.synchronize()
+      dist.barrier()
+      torch.cuda.synchronize()
+      sys.stdout.flush()
+      sys.stderr.flush()
+      os._exit(0)
+
+  if rank != 0:
+    leave()
     return
 
   peak, peak_kind = peaks()
@@ -406,8 +417,7 @@ def run_cuda(args):
                             "sample": f"1 of {nl} layers (all 96 sequences) x 3 repeats, {per_layer:.2f} s per "
                                       f"layer; tokens/s extrapolated to {nl} layers"}
   print(json.dumps(line), flush=True)
-  if world > 1:
-    dist.destroy_process_group()
+  leave()
 
 
 def main():
