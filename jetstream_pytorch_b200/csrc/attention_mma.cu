@@ -105,6 +105,25 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], u
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Four 8x8 b16 matrices; lane l gives the address of row l % 8 of matrix l / 8,
+// and receives elements (l / 4, 2 (l % 4) .. +1) of each (transposed with .trans).
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -129,17 +148,29 @@ __device__ __forceinline__ unsigned smid() {
 }
 #endif
 
-struct __align__(16) Stage {
-  uint8_t k[kTile * kD];  // K rows, then V rows: 16 KB that double as the merge buffer of a piece
-  uint8_t v[kTile * kD];
+// int8 caches: 3 stages of 16 KB; bf16 caches: 2 stages of 32 KB.
+template <bool kBf16>
+struct Geometry {
+  static constexpr int kES = kBf16 ? 2 : 1;           // bytes per cache element
+  static constexpr int kRowBytes = kD * kES;          // one token row
+  static constexpr int kNS = kBf16 ? 2 : kStages;     // ring depth
+  static constexpr int kCpr = kRowBytes / 16;         // 16-byte chunks per row
+  static constexpr int kRpp = kThreads / kCpr;        // rows covered by one copy pass of the CTA
+  static constexpr int kPasses = kTile / kRpp;        // copy passes per tile (each moves 2048 bytes per tensor)
 };
 
-template <bool kRows16>
+template <bool kBf16>
+struct __align__(16) Stage {
+  uint8_t k[kTile * Geometry<kBf16>::kRowBytes];  // K rows, then V rows; the first 16 KB double as the merge buffer of a piece
+  uint8_t v[kTile * Geometry<kBf16>::kRowBytes];
+};
+
+template <bool kRows16, bool kBf16>
 struct __align__(128) Smem {
-  Stage kv[kStages];
-  uint8_t q[kStages][(kRows16 ? 16 : 8) * kD * 2];  // bf16 query rows of the piece starting in this stage
-  float ks2[kStages][kTile];                        // k_scale * sm_scale * log2(e)
-  float vs[kStages][kTile];                         // v_scale
+  Stage<kBf16> kv[Geometry<kBf16>::kNS];
+  uint8_t q[Geometry<kBf16>::kNS][(kRows16 ? 16 : 8) * kD * 2];  // bf16 query rows of the piece starting in this stage
+  float ks2[Geometry<kBf16>::kNS][kTile];                        // k_scale * sm_scale * log2(e)
+  float vs[Geometry<kBf16>::kNS][kTile];                         // v_scale
 };
 
 // What the producer publishes about the tile it put into a stage.
@@ -229,11 +260,14 @@ __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int first,
   }
 }
 
-template <bool kRows16>
-__global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_kernel(AttnArgs a, MmaScratch x) {
+template <bool kRows16, bool kBf16>
+__global__ void __launch_bounds__(kThreads, kRows16 ? 2 : (kBf16 ? 3 : 4))
+    flash_decode_kernel(AttnArgs a, MmaScratch x) {
   constexpr int NT = kRows16 ? 2 : 1;  // n-tiles of 8 query rows
+  using Geo = Geometry<kBf16>;
+  constexpr int kNS = Geo::kNS, kES = Geo::kES, kRowBytes = Geo::kRowBytes;
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  Smem<kRows16>& sm = *reinterpret_cast<Smem<kRows16>*>(smem_raw);
+  Smem<kRows16, kBf16>& sm = *reinterpret_cast<Smem<kRows16, kBf16>*>(smem_raw);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -257,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
   int* scan = reinterpret_cast<int*>(&sm.ks2[0][0]);  // 129 ints <= 3 * 64 floats
   __shared__ int s_start[4];
   __shared__ int s_flag;
-  __shared__ TileMeta s_meta[kStages];
+  __shared__ TileMeta s_meta[kNS];
   const int per = (a.B + kThreads - 1) / kThreads;
   const int b_lo = min(a.B, tid * per), b_hi = min(a.B, b_lo + per);
   int mine = 0;
@@ -338,11 +372,11 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
   // Position of the next tile to fetch (uniform across the CTA) ...
   int pb = s_start[0], ph = s_start[1], pt, pslot = G0;  // pslot: global slot index of tile pt
   int pT, pn, pfirst, puse_add;
-  // ... and what follows from it for this thread: rows (tid / 8) + 16 i of a
-  // tile, 16-byte column tid % 8.  The swizzled shared-memory offset of row
-  // + 16 i is that of row plus 2048 i.
-  const int prow = tid >> 3, pcol = tid & 7;
-  const uint32_t pdst = (uint32_t)(prow * kD + ((pcol ^ (prow & 7)) << 4));
+  // ... and what follows from it for this thread: 16-byte column tid % kCpr of
+  // rows (tid / kCpr) + kRpp i of a tile.  kRpp is a multiple of 8, so the
+  // swizzled shared-memory offset of row + kRpp i is that of row plus 2048 i.
+  const int prow = tid / Geo::kCpr, pcol = tid % Geo::kCpr;
+  const uint32_t pdst = (uint32_t)(prow * kRowBytes + ((pcol ^ (prow & 7)) << 4));
   const bool tile_pages = a.paged && (a.page_size % kTile) == 0;
   const bool rows_packed = a.paged ? tile_pages : (a.kv_s == kD);  // rows of a tile kD bytes apart
   const int kv_s32 = (int)a.kv_s, sc_s32 = (int)a.sc_s;
@@ -359,8 +393,8 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
   };
   auto seg_setup = [&]() {  // pt, pslot are set
     const int64_t seg = a.paged ? (int64_t)ph * a.kv_h : (int64_t)pb * a.kv_b + (int64_t)ph * a.kv_h;
-    kseg = kbase + seg + pcol * 16;
-    vseg = vbase + seg + pcol * 16;
+    kseg = kbase + seg * kES + pcol * 16;
+    vseg = vbase + seg * kES + pcol * 16;
     scseg = a.paged ? 0 : (int64_t)pb * a.sc_b;
     ppos = pfirst + pt * kTile;
     if (ppos >= a.S) ppos -= a.S;
@@ -412,7 +446,8 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
       TileMeta mt;
       mt.b = pb; mt.h = ph; mt.t = pt; mt.T = pT; mt.n = pn; mt.first = pfirst; mt.use_add = puse_add;
       mt.first_cta = pfirst_cta; mt.parts = pparts;
-      mt.pad[0] = mt.pad[1] = mt.pad[2] = 0;
+      mt.pad[0] = mt.pad[1] = 0;
+      mt.pad[2] = pslot + 1 >= G1;  // no tile follows in this CTA's share
       s_meta[stage] = mt;
     }
     const uint32_t kdst = smem_u32(&sm.kv[stage].k[0]) + pdst;
@@ -427,17 +462,17 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
       // whole tile valid, no ring wrap, rows kD bytes apart: one address per tensor
       const int64_t off = a.paged ? (int64_t)page * a.kv_page + (int64_t)(j0 - page_pos0 + prow) * kD
                                   : (int64_t)(ppos + prow) * kD;
-      const int8_t* kp = kseg + off;
-      const int8_t* vp = vseg + off;
+      const int8_t* kp = kseg + off * kES;
+      const int8_t* vp = vseg + off * kES;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < Geo::kPasses; ++i) {
         cp_async16(kdst + 2048 * i, kp + 2048 * i, true);
         cp_async16(vdst + 2048 * i, vp + 2048 * i, true);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = prow + 16 * i;
+      for (int i = 0; i < Geo::kPasses; ++i) {
+        const int r = prow + Geo::kRpp * i;
         const bool valid = j0 + r < pn;
         int pos = valid ? ppos + r : ppos;
         if (pos >= a.S) pos -= a.S;
@@ -452,8 +487,8 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
         } else {
           off = (int64_t)pos * kv_s32;
         }
-        cp_async16(kdst + 2048 * i, kseg + off, valid);
-        cp_async16(vdst + 2048 * i, vseg + off, valid);
+        cp_async16(kdst + 2048 * i, kseg + off * kES, valid);
+        cp_async16(vdst + 2048 * i, vseg + off * kES, valid);
       }
     }
     if (piece_start) {
@@ -515,35 +550,49 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
   // shared-memory offsets of this thread's operands inside a stage
   const int tok0 = warp * 16;
   uint32_t koff[2][2], voff[4];
+  if constexpr (!kBf16) {
 #pragma unroll
-  for (int hh = 0; hh < 2; ++hh) {
-    const int row = tok0 + 8 * hh + g;
-    koff[hh][0] = row * kD + (((2 * c) ^ (row & 7)) << 4);
-    koff[hh][1] = row * kD + (((2 * c + 1) ^ (row & 7)) << 4);
-  }
+    for (int hh = 0; hh < 2; ++hh) {
+      const int row = tok0 + 8 * hh + g;
+      koff[hh][0] = row * kD + (((2 * c) ^ (row & 7)) << 4);
+      koff[hh][1] = row * kD + (((2 * c + 1) ^ (row & 7)) << 4);
+    }
 #pragma unroll
-  for (int r4 = 0; r4 < 4; ++r4) {
-    const int row = tok0 + 2 * c + (r4 & 1) + 8 * (r4 >> 1);
-    voff[r4] = kTile * kD + row * kD + ((g ^ (row & 7)) << 4);
+    for (int r4 = 0; r4 < 4; ++r4) {
+      const int row = tok0 + 2 * c + (r4 & 1) + 8 * (r4 >> 1);
+      voff[r4] = kTile * kD + row * kD + ((g ^ (row & 7)) << 4);
+    }
+  } else {
+    // ldmatrix row addresses of this lane: matrix mi = lane / 8, row lane % 8.
+    // K (A operand, tokens on M): token tok0 + 8 (mi & 1) + row, 16-byte chunk 2 j + (mi >> 1).
+    // V (A operand through .trans, d on M): token tok0 + 8 (mi >> 1) + row, chunk 2 x + (mi & 1).
+    // The chunk of k-step j / m-tile x differs from chunk 0's only in bits 1..3,
+    // which the swizzle leaves alone or flips by a constant: offset ^ (2 j << 4).
+    const int mi = lane >> 3, r8 = lane & 7;
+    const int ktok = tok0 + 8 * (mi & 1) + r8, vtok = tok0 + 8 * (mi >> 1) + r8;
+    koff[0][0] = ktok * kRowBytes + (((mi >> 1) ^ (ktok & 7)) << 4);
+    voff[0] = kTile * kRowBytes + vtok * kRowBytes + (((mi & 1) ^ (vtok & 7)) << 4);
+    koff[0][1] = koff[1][0] = koff[1][1] = 0;
+    voff[1] = voff[2] = voff[3] = 0;
   }
 
-  produce(0);
-  produce(1);
+#pragma unroll
+  for (int s0 = 0; s0 < kNS - 1; ++s0) produce(s0);
 
   int stage = 0;
   for (int i = 0;; ++i) {
-    cp_async_wait<kStages - 2>();
+    cp_async_wait<kNS - 2>();
     flush_side();
     __syncthreads();
     {
-      int ps = stage + 2;
-      if (ps >= kStages) ps -= kStages;
+      int ps = stage + kNS - 1;
+      if (ps >= kNS) ps -= kNS;
       produce(ps);
     }
     const TileMeta mt = s_meta[stage];
     if (mt.t < 0) break;
-    const int next_stage = stage + 1 == kStages ? 0 : stage + 1;
-    const bool last_of_share = s_meta[next_stage].t < 0;
+    const int next_stage = stage + 1 == kNS ? 0 : stage + 1;
+    const bool last_of_share = mt.pad[2] != 0;
 #ifdef JPT_ATTN_TIMING
     ++dbg_tiles;
 #endif
@@ -559,7 +608,20 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
       for (int nt = 0; nt < NT; ++nt) {
         const int row = 8 * nt + g;
         float sum = 0.f;
-        if (row < R) {
+        if constexpr (kBf16) {
+          // B operand of k-step j: d = 16 j + 2 c, +1 and 16 j + 8 + 2 c, +1 of row g,
+          // which is what ldmatrix hands out for the chunks 2 j and 2 j + 1 of the 8 rows.
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            uint32_t r0, r1, r2, r3;
+            ldmatrix_x4(q_addr + (8 * nt + (lane & 7)) * (kD * 2) + (4 * k4 + (lane >> 3)) * 16, r0, r1, r2, r3);
+            const bool ok = row < R;
+            qb[nt][2 * k4][0] = ok ? r0 : 0u;
+            qb[nt][2 * k4][1] = ok ? r1 : 0u;
+            qb[nt][2 * k4 + 1][0] = ok ? r2 : 0u;
+            qb[nt][2 * k4 + 1][1] = ok ? r3 : 0u;
+          }
+        } else if (row < R) {
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {  // 8 bf16 per 16-byte load = k-steps 2*k4, 2*k4+1
             const uint4 raw = lds128(q_addr + row * (kD * 2) + 64 * c + 16 * k4);
@@ -598,7 +660,15 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int u = 0; u < 2; ++u) sc[nt][u][0] = sc[nt][u][1] = sc[nt][u][2] = sc[nt][u][3] = 0.f;
-    {
+    if constexpr (kBf16) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t af[4];
+        ldmatrix_x4(st_addr + (koff[0][0] ^ (uint32_t)(2 * j << 4)), af[0], af[1], af[2], af[3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16(sc[nt][j & 1], af, qb[nt][j][0], qb[nt][j][1]);
+      }
+    } else {
       uint32_t kw[2][8];
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
@@ -682,13 +752,26 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
       l_run[nt][0] += p00 + p10;
       l_run[nt][1] += p01 + p11;
       // P^T as the B operand: transpose the two 8x8 (token x row) blocks
-      pb2[nt][0] = movmatrix_trans(pack_half2(p00 * vs_lo, p01 * vs_lo));
-      pb2[nt][1] = movmatrix_trans(pack_half2(p10 * vs_hi, p11 * vs_hi));
+      if constexpr (kBf16) {
+        pb2[nt][0] = movmatrix_trans(pack_bf162(p00 * vs_lo, p01 * vs_lo));
+        pb2[nt][1] = movmatrix_trans(pack_bf162(p10 * vs_hi, p11 * vs_hi));
+      } else {
+        pb2[nt][0] = movmatrix_trans(pack_half2(p00 * vs_lo, p01 * vs_lo));
+        pb2[nt][1] = movmatrix_trans(pack_half2(p10 * vs_hi, p11 * vs_hi));
+      }
     }
 
     // ---------------- O^T += V^T P^T: this thread converts the 16-byte chunk g
-    // of token rows 2c, 2c+1, 2c+8, 2c+9
-    {
+    // of token rows 2c, 2c+1, 2c+8, 2c+9 (int8); bf16 rows come transposed out of ldmatrix
+    if constexpr (kBf16) {
+#pragma unroll
+      for (int xx = 0; xx < 8; ++xx) {
+        uint32_t af[4];
+        ldmatrix_x4_trans(st_addr + (voff[0] ^ (uint32_t)(2 * xx << 4)), af[0], af[1], af[2], af[3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][xx], af, pb2[nt][0], pb2[nt][1]);
+      }
+    } else {
       uint32_t vw[4][4];
 #pragma unroll
       for (int r4 = 0; r4 < 4; ++r4) {
@@ -741,7 +824,20 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
           l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
         }
         __syncthreads();  // every warp is done with the tile (and with the previous pass)
-        {
+        if constexpr (kBf16) {
+          // accumulator x holds d = 16 x + g and 16 x + 8 + g of rows 2c, 2c+1; the
+          // column is XORed with 8 c so that the 32 lanes of a store hit 32 banks
+          float* d0 = obuf + (warp * 8 + 2 * c) * kD;
+          float* d1 = d0 + kD;
+#pragma unroll
+          for (int xx = 0; xx < 8; ++xx) {
+            const int col = (16 * xx + g) ^ (8 * c);
+            d0[col] = o[nt][xx][0];
+            d1[col] = o[nt][xx][1];
+            d0[col ^ 8] = o[nt][xx][2];
+            d1[col ^ 8] = o[nt][xx][3];
+          }
+        } else {
           const float w0 = 1152.f * wsum[nt][0], w1 = 1152.f * wsum[nt][1];
           float4* d0 = reinterpret_cast<float4*>(obuf + ((warp * 8 + 2 * c) * kD) + 16 * g);
           float4* d1 = reinterpret_cast<float4*>(obuf + ((warp * 8 + 2 * c + 1) * kD) + 16 * g);
@@ -753,6 +849,8 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
           d1[1] = make_float4(o[nt][4][1] - w1, o[nt][5][1] - w1, o[nt][6][1] - w1, o[nt][7][1] - w1);
           d1[2] = make_float4(o[nt][0][3] - w1, o[nt][1][3] - w1, o[nt][2][3] - w1, o[nt][3][3] - w1);
           d1[3] = make_float4(o[nt][4][3] - w1, o[nt][5][3] - w1, o[nt][6][3] - w1, o[nt][7][3] - w1);
+        }
+        {
           if (g == 0) {
             msm[warp * 8 + 2 * c] = m_run[nt][0];
             msm[warp * 8 + 2 * c + 1] = m_run[nt][1];
@@ -792,7 +890,7 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : 4) flash_decode_i8_ker
         for (int r = 0; r < rows_here; ++r) {
           float acc = 0.f;
 #pragma unroll
-          for (int w = 0; w < 4; ++w) acc += wsm[w * 8 + r] * obuf[(w * 8 + r) * kD + tid];
+          for (int w = 0; w < 4; ++w) acc += wsm[w * 8 + r] * obuf[(w * 8 + r) * kD + (kBf16 ? tid ^ (8 * (r >> 1)) : tid)];
           const int rr = 8 * nt + r;
           const float M = tsm[r], L = tsm[8 + r], Mt = tsm[16 + r];
           if (is_final) {
@@ -915,7 +1013,7 @@ struct ScratchLayout {
 ScratchLayout scratch_layout(const jpt_attn_params& p) {
   const int R = (p.Hq / p.Hkv) * p.Tq;
   ScratchLayout s;
-  s.num_ctas = sm_count() * (R > 8 ? 2 : 4);
+  s.num_ctas = sm_count() * (R > 8 ? 2 : (p.kv_dtype == JPT_BF16 ? 3 : 4));
   size_t off = 0;
   s.counters = off;  // fixed-size header shared by every shape that uses the workspace
   off = kWorkspaceCounterBytes;
@@ -937,7 +1035,8 @@ ScratchLayout scratch_layout(const jpt_attn_params& p) {
 
 bool attention_mma_eligible(const jpt_attn_params& p) {
   const int R = (p.Hq / p.Hkv) * p.Tq;
-  if (p.D != kD || R > kMaxRows || p.q_dtype != JPT_BF16 || p.kv_dtype != JPT_INT8) return false;
+  if (p.D != kD || R > kMaxRows || p.q_dtype != JPT_BF16) return false;
+  if (p.kv_dtype != JPT_INT8 && p.kv_dtype != JPT_BF16) return false;
   if (p.mask_mode == JPT_MASK_ADD && p.mk_r != 0) return false;  // per-row masks: scalar kernel
   if (!aligned(p.q, 16) || !aligned(p.k, 16) || !aligned(p.v, 16)) return false;
   if (p.paged) {
@@ -972,22 +1071,29 @@ int launch_attention_mma(const jpt_attn_params& p, const AttnArgs& a, cudaStream
 
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(flash_decode_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)sizeof(Smem<false>));
-    cudaFuncSetAttribute(flash_decode_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)sizeof(Smem<true>));
+    cudaFuncSetAttribute(flash_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)sizeof(Smem<false, false>));
+    cudaFuncSetAttribute(flash_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)sizeof(Smem<true, false>));
+    cudaFuncSetAttribute(flash_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)sizeof(Smem<false, true>));
+    cudaFuncSetAttribute(flash_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)sizeof(Smem<true, true>));
     configured = true;
   }
   if (a.mask_mode == JPT_MASK_ADD) {
     mask_ranges_kernel<<<a.B, kThreads, 0, st>>>(a, x);
     if (int rc = check_launch("mask_ranges_kernel")) return rc;
   }
+  const bool bf16 = p.kv_dtype == JPT_BF16;
   if (a.R > 8) {
-    flash_decode_i8_kernel<true><<<lay.num_ctas, kThreads, sizeof(Smem<true>), st>>>(a, x);
+    if (bf16) flash_decode_kernel<true, true><<<lay.num_ctas, kThreads, sizeof(Smem<true, true>), st>>>(a, x);
+    else flash_decode_kernel<true, false><<<lay.num_ctas, kThreads, sizeof(Smem<true, false>), st>>>(a, x);
   } else {
-    flash_decode_i8_kernel<false><<<lay.num_ctas, kThreads, sizeof(Smem<false>), st>>>(a, x);
+    if (bf16) flash_decode_kernel<false, true><<<lay.num_ctas, kThreads, sizeof(Smem<false, true>), st>>>(a, x);
+    else flash_decode_kernel<false, false><<<lay.num_ctas, kThreads, sizeof(Smem<false, false>), st>>>(a, x);
   }
-  return check_launch("flash_decode_i8_kernel");
+  return check_launch("flash_decode_kernel");
 }
 
 }  // namespace jpt

@@ -571,7 +571,7 @@ def test_ragged_mha_generic_kernel_splitk(splits):
 
 @pytest.mark.parametrize("int8", [True, False])
 @pytest.mark.parametrize("ring", [False, True])
-@pytest.mark.parametrize("heads", [(64, 8), (32, 8), (32, 32), (16, 8)])
+@pytest.mark.parametrize("heads", [(64, 8), (32, 8), (32, 32), (16, 8), (32, 2), (24, 2)])
 def test_ragged_mha_head_dim_128_matches_oracle(int8, ring, heads):
   hq, hkv = heads
   _check_ragged(_ragged_case(63, 6, hq, hkv, 512, 128, int8, ring), ring)
@@ -584,10 +584,11 @@ def test_ragged_mha_llama2_70b_shape_full_size():
     _check_ragged(_ragged_case(64, 96, 64, 8, 2048, 128, True, ring), ring)
 
 
-def test_ragged_fast_and_generic_kernels_agree():
+@pytest.mark.parametrize("int8", [True, False])
+def test_ragged_fast_and_generic_kernels_agree(int8):
   from jetstream_pytorch_b200 import attention_kernel as ak
 
-  q, k, v, ks, vs, start, end = _ragged_case(65, 8, 64, 8, 1024, 128, True, True)
+  q, k, v, ks, vs, start, end = _ragged_case(65, 8, 64, 8, 1024, 128, int8, True)
   args = (cu(q), cu(k), cu(v), 0, cu(start), cu(end), None, None, cu(ks), cu(vs))
   o1, (m1, l1) = ak.ragged_mha(*args, ring=True)
   o2, (m2, l2) = ak.ragged_mha(*args, ring=True, force_generic=True)
@@ -595,6 +596,13 @@ def test_ragged_fast_and_generic_kernels_agree():
   live = torch.isfinite(m2)
   assert torch.allclose(m1[live], m2[live], atol=1e-3, rtol=1e-3)
   assert torch.allclose(l1[live], l2[live], atol=1e-3, rtol=1e-3)
+
+
+def test_ragged_mha_bf16_cache_llama3_8b_shape_full_size():
+  """BASELINE config 2's attention shape with a dense bf16 cache: B=32, 32 q /
+  8 kv heads, D=128, S=2048 (the paged form of it is covered further down)."""
+  for ring in (False, True):
+    _check_ragged(_ragged_case(67, 32, 32, 8, 2048, 128, False, ring), ring)
 
 
 def test_ragged_mqa_per_head_entry_points_and_stacked_layout():
