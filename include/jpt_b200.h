@@ -250,7 +250,7 @@ typedef struct jpt_attn_params {
   void* workspace;
   size_t workspace_bytes;
   int num_splits;       /* split-K factor; 0 = choose automatically */
-  int force_generic;    /* 1: always use the scalar kernel (testing) */
+  int force_generic;    /* testing: 1 = always the scalar kernel, 2 = the mma.sync kernel instead of the tcgen05 one */
 } jpt_attn_params;
 
 /*

@@ -17,6 +17,7 @@ SOURCES = [
     "prefill_insert.cu",
     "attention_generic.cu",
     "attention_mma.cu",
+    "attention_umma.cu",
 ]
 
 NVCC_FLAGS = [

@@ -93,6 +93,10 @@ size_t attention_mma_workspace_bytes(const jpt_attn_params& p);
 // Launches the persistent kernel and its merge (and the mask pre-pass when the
 // mask is additive); uses p.workspace for its scratch.
 int launch_attention_mma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
+// int8 caches with up to 8 grouped query rows: the tcgen05 kernel.  Its scratch
+// fits in attention_mma_workspace_bytes().
+bool attention_umma_eligible(const jpt_attn_params& p);
+int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
 int launch_splitk_merge(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
 
 }  // namespace jpt

@@ -268,7 +268,7 @@ using namespace jpt;
 extern "C" size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p) {
   if (!p || validate(*p) != 0) return 0;
   const int R = (p->Hq / p->Hkv) * p->Tq;
-  if (!p->force_generic && attention_mma_eligible(*p)) return attention_mma_workspace_bytes(*p);
+  if (p->force_generic != 1 && attention_mma_eligible(*p)) return attention_mma_workspace_bytes(*p);
   const int ns = resolve_splits(*p, R);
   if (ns <= 1) return 0;
   const size_t rows = (size_t)p->B * p->Hkv * R;
@@ -280,7 +280,7 @@ extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
   const jpt_attn_params& p = *pp;
   if (int rc = validate(p)) return rc;
   const int R = (p.Hq / p.Hkv) * p.Tq;
-  const bool use_mma = !p.force_generic && attention_mma_eligible(p);
+  const bool use_mma = p.force_generic != 1 && attention_mma_eligible(p);
   AttnArgs a{};
   a.q = p.q; a.k = p.k; a.v = p.v; a.k_scale = p.k_scale; a.v_scale = p.v_scale;
   a.page_table = p.page_table; a.start = p.start; a.end = p.end; a.mask = p.mask;
@@ -294,6 +294,7 @@ extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (use_mma) {
     a.nsplit = 1;
+    if (p.force_generic != 2 && attention_umma_eligible(p)) return launch_attention_umma(p, a, st);
     return launch_attention_mma(p, a, st);
   }
   a.nsplit = resolve_splits(p, R);

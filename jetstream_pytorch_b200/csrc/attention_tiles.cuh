@@ -1,0 +1,175 @@
+// Pieces shared by the persistent tensor-core decode-attention kernels: the
+// scratch handed to a launch, the record a producer publishes per tile, the
+// merge of a segment's partial results, and the host-side scratch layout.
+#pragma once
+
+#include <limits.h>
+#include <math.h>
+
+#include "attention_common.cuh"
+
+namespace jpt {
+
+constexpr int kThreads = 128;
+constexpr int kD = 128;
+constexpr int kMaxRows = 16;
+constexpr int kPieceCost = 1;  // overhead slots charged per segment, in tiles
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Scratch handed to the kernel (all inside the caller's workspace).
+struct MmaScratch {
+  unsigned* counters;  // [B * Hkv] wrapping arrival counters, zero between launches
+  int32_t* seqinfo;    // [B][4] (first, n, use_add, -) for additive masks
+  float* part_o;       // [num_ctas][2][16][128] unnormalised partial outputs
+  float* part_m;       // [num_ctas][2][16] reference maximum (log2 domain)
+  float* part_l;       // [num_ctas][2][16] sum of exp2(x - reference)
+  float* part_t;       // [num_ctas][2][16] true maximum (log2 domain)
+  int num_ctas;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(x));
+  return r;
+}
+
+
+// What the producer publishes about the tile it put into a stage.
+struct TileMeta {
+  int b, h;        // sequence, KV head
+  int t, T;        // tile inside the segment (-1: no tile, the CTA's share is exhausted), tiles of the segment
+  int n, first;    // valid tokens of the sequence and position of its first one
+  int use_add;     // additive mask values must be applied
+  int first_cta;   // CTA that holds tile 0 of the segment
+  int parts;       // number of CTAs the segment is spread over
+  int pad[3];
+};
+
+// Valid range of a sequence for every mask mode (additive masks have been
+// reduced to ranges by mask_ranges_kernel).
+__device__ __forceinline__ SeqRange seq_range_x(const AttnArgs& a, const MmaScratch& x, int b, int* use_add) {
+  *use_add = 0;
+  if (a.mask_mode == JPT_MASK_ADD) {
+    SeqRange r;
+    r.first = x.seqinfo[4 * b];
+    r.n = x.seqinfo[4 * b + 1];
+    *use_add = x.seqinfo[4 * b + 2];
+    return r;
+  }
+  return seq_range(a, b);
+}
+
+// Combine the `parts` partials of one segment (CTAs first .. first+parts-1) and
+// write its R final rows.  `scratch` is at least (parts + 3) * 16 floats of
+// shared memory.  Called by a whole CTA.
+static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int first, int parts, int64_t row_base,
+                              float* scratch) {
+  const int tid = threadIdx.x, R = a.R;
+  float* s_w = scratch;                     // [parts][16] weights
+  float* s_M = scratch + parts * kMaxRows;  // [16] reference maximum
+  float* s_L = s_M + kMaxRows;              // [16] denominator relative to s_M
+  for (int i = tid; i < parts * R; i += kThreads) {
+    const int pi = i / R, r = i - pi * R;
+    s_w[pi * kMaxRows + r] = __ldcg(&x.part_m[((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows + r]);
+  }
+  __syncthreads();
+  if (tid < R) {
+    float M = -INFINITY;
+    for (int pi = 0; pi < parts; ++pi) M = fmaxf(M, s_w[pi * kMaxRows + tid]);
+    s_M[tid] = M;
+  }
+  __syncthreads();
+  for (int i = tid; i < parts * R; i += kThreads) {
+    const int pi = i / R, r = i - pi * R;
+    const float mw = s_w[pi * kMaxRows + r];
+    s_w[pi * kMaxRows + r] = mw == -INFINITY ? 0.f : fast_exp2(mw - s_M[r]);
+  }
+  __syncthreads();
+  if (tid < R) {
+    float L = 0.f, mt = -INFINITY;
+    for (int pi = 0; pi < parts; ++pi) {
+      const int64_t pr = ((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows + tid;
+      L += s_w[pi * kMaxRows + tid] * __ldcg(&x.part_l[pr]);
+      mt = fmaxf(mt, __ldcg(&x.part_t[pr]));
+    }
+    s_L[tid] = L;
+    // report the true maximum and the denominator relative to it
+    if (a.m) a.m[row_base + tid] = mt * kLn2;
+    if (a.l) a.l[row_base + tid] = L > 0.f ? L * fast_exp2(s_M[tid] - mt) : 0.f;
+  }
+  __syncthreads();
+  float acc[kMaxRows];
+#pragma unroll
+  for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
+  for (int pi = 0; pi < parts; ++pi) {
+    const float* src = x.part_o + (((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows) * kD + tid;
+#pragma unroll
+    for (int r = 0; r < kMaxRows; ++r) {
+      if (r < R) acc[r] += s_w[pi * kMaxRows + r] * __ldcg(src + r * kD);
+    }
+  }
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
+#pragma unroll
+  for (int r = 0; r < kMaxRows; ++r) {
+    if (r < R) {
+      const float L = s_L[r];
+      o[(row_base + r) * kD + tid] = __float2bfloat16_rn(L > 0.f ? acc[r] / L : 0.f);
+    }
+  }
+}
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct ScratchLayout {
+  size_t counters, seqinfo, part_m, part_l, part_t, part_o, total;
+  int num_ctas;
+};
+
+// Layout of the scratch of a persistent launch of `num_ctas` CTAs.
+inline ScratchLayout scratch_layout(const jpt_attn_params& p, int num_ctas) {
+  ScratchLayout s;
+  s.num_ctas = num_ctas;
+  size_t off = 0;
+  s.counters = off;  // fixed-size header shared by every shape that uses the workspace
+  off = kWorkspaceCounterBytes;
+  s.seqinfo = off;
+  off = align_up(off + sizeof(int32_t) * 4 * p.B, 256);
+  s.part_m = off;
+  off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
+  s.part_l = off;
+  off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
+  s.part_t = off;
+  off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
+  s.part_o = off;
+  off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows * kD, 256);
+  s.total = off;
+  return s;
+}
+
+// Additive masks -> valid ranges in x.seqinfo (one CTA per sequence).
+int launch_mask_ranges(const AttnArgs& a, const MmaScratch& x, cudaStream_t st);
+
+}  // namespace jpt

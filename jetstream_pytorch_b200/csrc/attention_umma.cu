@@ -1,0 +1,693 @@
+// Ragged flash-decode attention for int8 caches, head_dim 128 and up to 8
+// grouped query rows on the 5th-generation tensor cores (tcgen05, sm_100a).
+//
+// The int8 codes never pass through registers: both contractions run as
+// integer MMAs that read K, V and the small second operands straight from
+// shared memory and accumulate int32 in tensor memory (TMEM).
+//
+//   S^T[128 tok x 16] = K[128 tok x 128 d] . Ql^T       kind::i8, K-major A and B
+//   O^T[128 d  x 32] = V^T[128 d x 128 tok] . Pl^T      kind::i8, MN-major A, K-major B
+//
+// "Levels" make the small operands 8-bit without losing the precision of the
+// bf16 / fp32 values they stand for:
+//   * a query row q (bf16) is split as q = s (h + l / 254) with s = amax|q| / 127
+//     and h, l signed bytes; rows 0..7 of Ql hold h, rows 8..15 hold l, so the
+//     two partial dot products of a token arrive in the same TMEM lane and
+//     S = s (S_h + S_l / 254) is exact to 2^-16 of the row's amax;
+//   * a probability p in [0, 1] (the running maximum is exact here), times the
+//     token's V scale relative to the largest V scale of the tile, becomes a
+//     24-bit fixed-point number whose three bytes are the unsigned levels
+//     Pl[8 l + r]; O = (O_0 + 2^8 O_1 + 2^16 O_2) c / (2^24 - 1).
+// Every int32 sum is exact (|sum| <= 128 * 127 * 255), so the only roundings
+// are the two splits above and the fp32 online-softmax arithmetic.
+//
+// A tile is 128 consecutive valid tokens of one (sequence, KV head) segment;
+// tiles are scheduled exactly as in the mma.sync kernel (equal contiguous
+// shares of one global tile list, pieces, last-arriver merge).  K and V rows
+// of a tile land in shared memory as 128-byte rows, 16-byte chunks XORed with
+// (row & 7): that is the canonical 128-byte-swizzle layout of the tensor core
+// for both operand roles (K-major for K, MN-major for V), so nothing is
+// rearranged.  In the softmax phase thread t owns token t of the tile (TMEM
+// lane t of S^T); in the output phase thread t owns head-dim index t (TMEM
+// lane t of O^T), which also removes the cross-warp merge of the accumulators.
+//
+// Every wait on an mbarrier is bounded; a CTA that gives up raises the status
+// word of the workspace, frees its tensor memory and returns.
+#include "attention_tiles.cuh"
+
+namespace jpt {
+namespace {
+
+constexpr int kTileU = 128;     // tokens per tile = TMEM lanes = threads per CTA
+constexpr int kStagesU = 2;     // K/V ring depth
+constexpr int kTmemCols = 64;   // S^T: columns 0..15, O^T: columns 16..47
+constexpr int kColO = 16;
+constexpr int kCtasPerSm = 3;
+constexpr int kWaitPolls = 1 << 20;
+
+struct __align__(1024) SmemU {
+  uint8_t kv[kStagesU][2][kTileU * kD];  // [stage][K, V][token][128 bytes], swizzled
+  uint8_t qlev[16 * kD];                 // query levels: rows 0..7 high bytes, 8..15 low bytes
+  uint8_t plev[32 * kTileU];             // probability levels: row 8 l + r, one byte per token
+  uint8_t qraw[8 * kD * 2];              // bf16 query rows of the piece whose first tile is in flight
+  float xch[4][12];                      // per warp: row maxima of the tile [8], largest V scale [1]
+  float red[4][8];                       // per warp: denominators at the end of a piece
+  float qsc[8];                          // s_r * sm_scale * log2(e) / 254
+  uint64_t bar[2];                       // MMA completion: S^T, O^T
+  uint32_t tmem_base;
+  int start[3];
+  int flag;
+  TileMeta meta[kStagesU];
+};
+
+__device__ __forceinline__ int tiles_u(int n) { return (n + kTileU - 1) / kTileU; }
+__device__ __forceinline__ int slots_u(int n) { return n > 0 ? tiles_u(n) + kPieceCost : 0; }
+
+// Byte offset of (row, byte) in a tile of 128-byte rows with 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz(int row, int byte) {
+  return (uint32_t)(row * 128 + ((((byte >> 4) ^ (row & 7))) << 4) + (byte & 15));
+}
+
+// Shared-memory matrix descriptor: 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);  // start address
+  d |= (uint64_t)(1024 >> 4) << 16;       // leading byte offset (one swizzle atom; unused for these shapes)
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                 // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptors: int32 accumulators, M = 128.
+constexpr uint32_t kIdescS = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);  // s8 x s8, N = 16
+constexpr uint32_t kIdescO =
+    (2u << 4) | (1u << 7) | (0u << 10) | (1u << 15) | ((32u >> 3) << 17) | ((128u >> 4) << 24);  // s8 (MN-major) x u8, N = 32
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < kWaitPolls; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// float <-> int keys with the same order, for redux.sync.max
+__device__ __forceinline__ int order_key(float x) {
+  const int i = __float_as_int(x);
+  return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float key_value(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_kernel(AttnArgs a, MmaScratch x, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  SmemU& sm = *reinterpret_cast<SmemU*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int R = a.R;
+  const bool quant = a.k_scale != nullptr;
+  const int cta = blockIdx.x;
+
+  // ------------------------------------------------------------------ schedule
+  // Slots per sequence (tiles + overhead) -> exclusive prefix over sequences;
+  // each thread owns a slice of ceil(B/128) sequences.  The scan scratch
+  // aliases the probability levels, which are not in use yet.
+  int* scan = reinterpret_cast<int*>(&sm.plev[0]);  // 129 ints
+  const int per = (a.B + kThreads - 1) / kThreads;
+  const int b_lo = min(a.B, tid * per), b_hi = min(a.B, b_lo + per);
+  int mine = 0;
+  for (int b = b_lo; b < b_hi; ++b) {
+    int ua;
+    mine += slots_u(seq_range_x(a, x, b, &ua).n);
+  }
+  scan[tid] = mine;
+  __syncthreads();
+  if (warp == 0) {
+    int v4[4], s = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v4[i] = scan[4 * lane + i];
+      s += v4[i];
+    }
+    int incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    int run = incl - s;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      scan[4 * lane + i] = run;
+      run += v4[i];
+    }
+    if (lane == 31) scan[kThreads] = incl;
+  }
+  __syncthreads();
+  const int total = scan[kThreads] * a.Hkv;  // the host checked that this fits in 31 bits
+  const int share = (total + x.num_ctas - 1) / x.num_ctas;
+  const int G0 = cta * share;
+  const int G1 = min(total, G0 + share);
+  {
+    // the thread whose slice holds slot G0 walks it and publishes (b, h, slot in segment)
+    const int lo = scan[tid] * a.Hkv, hi = scan[tid + 1] * a.Hkv;
+    if (G0 < G1 && G0 >= lo && G0 < hi) {
+      int run = lo;
+      for (int b = b_lo; b < b_hi; ++b) {
+        int ua;
+        const int sl = slots_u(seq_range_x(a, x, b, &ua).n);
+        const int nxt = run + sl * a.Hkv;
+        if (G0 < nxt) {
+          const int rem = G0 - run;
+          sm.start[0] = b;
+          sm.start[1] = rem / sl;
+          sm.start[2] = rem % sl;
+          break;
+        }
+        run = nxt;
+      }
+    }
+  }
+  // Rows of empty sequences are nobody's tile: sequence b is cleared by CTA b mod grid.
+  for (int b = cta; b < a.B; b += gridDim.x) {
+    int ua;
+    if (seq_range_x(a, x, b, &ua).n == 0) {
+      const int64_t r0 = (int64_t)b * a.Hkv * R;
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
+      for (int i = tid; i < a.Hkv * R * kD; i += kThreads) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
+      for (int i = tid; i < a.Hkv * R; i += kThreads) {
+        if (a.m) a.m[r0 + i] = -INFINITY;
+        if (a.l) a.l[r0 + i] = 0.f;
+      }
+    }
+  }
+  __syncthreads();  // sm.start visible; last reads of `scan` done
+  if (G0 >= G1) return;
+
+  // ------------------------------------------------------------------ barriers and tensor memory
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[1])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+
+  const int8_t* kbase = static_cast<const int8_t*>(a.k);
+  const int8_t* vbase = static_cast<const int8_t*>(a.v);
+  const __nv_bfloat16* qbase = static_cast<const __nv_bfloat16*>(a.q);
+  const __nv_bfloat16* mask = static_cast<const __nv_bfloat16*>(a.mask);
+
+  // ------------------------------------------------------------------ producer
+  // Position of the next tile to fetch (uniform across the CTA) ...
+  int pb = sm.start[0], ph = sm.start[1], pt, pslot = G0;  // pslot: global slot index of tile pt
+  int pT, pn, pfirst, puse_add;
+  // ... and what follows from it for this thread: 16-byte column tid % 8 of
+  // rows tid / 8 + 16 i of a tile.  The swizzled shared-memory offset of row
+  // + 16 i is that of row plus 2048 i.
+  const int prow = tid >> 3, pcol = tid & 7;
+  const uint32_t pdst = (uint32_t)(prow * kD + ((pcol ^ (prow & 7)) << 4));
+  // pages that hold whole 16-row copy passes: one table entry per pass
+  const bool pass_pages = a.paged && (a.page_size % 16) == 0 &&
+                          ((kTileU % a.page_size) == 0 || (a.page_size % kTileU) == 0);
+  const int passes_per_page = pass_pages ? a.page_size / 16 : 1;
+  const bool rows_packed = !a.paged && a.kv_s == kD;  // rows of a tile kD bytes apart
+  const int kv_s32 = (int)a.kv_s, sc_s32 = (int)a.sc_s;
+  const int8_t *kseg, *vseg;  // segment base + this thread's column
+  int64_t scseg;
+  int ppos;                   // physical position of row 0 of tile pt
+  int pfirst_cta, pparts;
+
+  auto load_seq = [&]() {
+    const SeqRange r = seq_range_x(a, x, pb, &puse_add);
+    pn = r.n;
+    pfirst = r.first;
+    pT = tiles_u(r.n);
+  };
+  auto seg_setup = [&]() {  // pt, pslot are set
+    const int64_t seg = a.paged ? (int64_t)ph * a.kv_h : (int64_t)pb * a.kv_b + (int64_t)ph * a.kv_h;
+    kseg = kbase + seg + pcol * 16;
+    vseg = vbase + seg + pcol * 16;
+    scseg = a.paged ? 0 : (int64_t)pb * a.sc_b;
+    ppos = pfirst + pt * kTileU;
+    if (ppos >= a.S) ppos -= a.S;
+    const int t0slot = pslot - pt;  // slot of tile 0 of this segment
+    pfirst_cta = t0slot / share;
+    pparts = (t0slot + pT - 1) / share - pfirst_cta + 1;
+  };
+  auto advance = [&]() {
+    ++pslot;
+    ppos += kTileU;
+    if (ppos >= a.S) ppos -= a.S;
+    if (++pt < pT) return;
+    pt = 0;
+    pslot += kPieceCost;  // the overhead slots of the next segment
+    if (++ph == a.Hkv) {
+      ph = 0;
+      do {
+        if (++pb >= a.B) {  // past the end of the list
+          pb = a.B - 1;
+          pslot = INT_MAX / 2;
+          return;
+        }
+        load_seq();
+      } while (pT == 0);
+    }
+    seg_setup();
+  };
+  {
+    load_seq();
+    const int v0 = sm.start[2];  // slot inside the segment: overhead slots come first
+    if (v0 < kPieceCost) {
+      pslot += kPieceCost - v0;
+      pt = 0;
+    } else {
+      pt = v0 - kPieceCost;
+    }
+    seg_setup();
+  }
+
+  float nks = 1.f, nvs = 0.f;  // scales of this thread's token in the tile fetched last
+  bool first_issue = true;
+
+  auto issue_tile = [&](int stage) {
+    const int j0 = pt * kTileU;
+    const bool piece_start = first_issue || pt == 0;
+    first_issue = false;
+    if (tid == 0) {
+      TileMeta mt;
+      mt.b = pb; mt.h = ph; mt.t = pt; mt.T = pT; mt.n = pn; mt.first = pfirst; mt.use_add = puse_add;
+      mt.first_cta = pfirst_cta; mt.parts = pparts;
+      mt.pad[0] = mt.pad[1] = 0;
+      mt.pad[2] = pslot + 1 >= G1;  // no tile follows in this CTA's share
+      sm.meta[stage] = mt;
+    }
+    const uint32_t kdst = smem_u32(&sm.kv[stage][0][0]) + pdst;
+    const uint32_t vdst = smem_u32(&sm.kv[stage][1][0]) + pdst;
+    if (rows_packed && j0 + kTileU <= pn && ppos + kTileU <= a.S) {
+      // whole tile valid, no ring wrap, rows kD bytes apart: one address per tensor
+      const int64_t off = (int64_t)(ppos + prow) * kD;
+      const int8_t* kp = kseg + off;
+      const int8_t* vp = vseg + off;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        cp_async16(kdst + 2048 * i, kp + 2048 * i, true);
+        cp_async16(vdst + 2048 * i, vp + 2048 * i, true);
+      }
+    } else if (pass_pages) {
+      // paged caches start at position 0: pass i (rows 16 i ..) lies inside one page
+      int pi = j0 / a.page_size, within = (j0 % a.page_size) / 16;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const bool valid = j0 + 16 * i + prow < pn;
+        const int page = (j0 + 16 * i) < pn ? a.page_table[(int64_t)pb * a.max_pages + pi] : 0;
+        const int64_t off = (int64_t)page * a.kv_page + (int64_t)(within * 16 + prow) * kD;
+        cp_async16(kdst + 2048 * i, kseg + off, valid);
+        cp_async16(vdst + 2048 * i, vseg + off, valid);
+        if (++within == passes_per_page) {
+          within = 0;
+          ++pi;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = prow + 16 * i;
+        const bool valid = j0 + r < pn;
+        int pos = valid ? ppos + r : ppos;
+        if (pos >= a.S) pos -= a.S;
+        int64_t off;
+        if (a.paged) {
+          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
+          off = (int64_t)pg * a.kv_page + (int64_t)(pos % a.page_size) * kD;
+        } else {
+          off = (int64_t)pos * kv_s32;
+        }
+        cp_async16(kdst + 2048 * i, kseg + off, valid);
+        cp_async16(vdst + 2048 * i, vseg + off, valid);
+      }
+    }
+    if (piece_start) {
+      const __nv_bfloat16* q = qbase + ((int64_t)pb * a.Hkv + ph) * R * kD;
+      for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.qraw[0]) + ch * 16, q + ch * 8, true);
+    }
+    // scales of token `tid` of the tile, consumed by this same thread
+    nks = 1.f;
+    nvs = 0.f;
+    if (j0 + tid < pn) {
+      nvs = 1.f;
+      if (quant) {
+        int pos = ppos + tid;
+        if (pos >= a.S) pos -= a.S;
+        int64_t sidx;
+        if (a.paged) {
+          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
+          sidx = (int64_t)pg * a.page_size + pos % a.page_size;
+        } else {
+          sidx = scseg + (int64_t)pos * sc_s32;
+        }
+        nks = load_scale(a.k_scale, sidx, a.scale_is_f32);
+        nvs = load_scale(a.v_scale, sidx, a.scale_is_f32);
+      }
+    }
+  };
+  // Fetch the next tile of the share into `stage`, or mark the stage as empty.
+  auto produce = [&](int stage) {
+    if (pslot < G1) {
+      issue_tile(stage);
+      advance();
+    } else if (tid == 0) {
+      sm.meta[stage].t = -1;
+    }
+    cp_async_commit();
+  };
+
+  // ------------------------------------------------------------------ consumer state
+  float m_run[8], l_run[8], o[8];  // l_run: this thread's token share of the denominators; o: head-dim index tid
+  int piece_t0 = 0;
+  uint32_t phase = 0;
+  bool dead = false;  // a wait ran out
+  const float unit2 = a.sm_scale * kLog2e;
+  const uint32_t bar_s = smem_u32(&sm.bar[0]), bar_o = smem_u32(&sm.bar[1]);
+  const uint32_t q_desc_addr = smem_u32(&sm.qlev[0]), p_desc_addr = smem_u32(&sm.plev[0]);
+  // this thread's byte of row r of the probability levels: ((tid / 16) ^ r) * 16 + tid % 16
+  const uint32_t p_addr = smem_u32(&sm.plev[0]) + (tid & 15);
+  const int tchunk = tid >> 4;
+
+  produce(0);
+
+  int stage = 0;
+  for (int i = 0;; ++i) {
+    cp_async_wait<0>();
+    const float cks = nks, cvs = nvs;  // scales of this thread's token in the tile of `stage`
+    fence_async_smem();                // the copied rows become visible to the tensor core
+    tc_fence_before();
+    __syncthreads();
+    const TileMeta mt = sm.meta[stage];
+    if (mt.t < 0) break;
+    const int next_stage = stage ^ 1;
+    const bool last_of_share = mt.pad[2] != 0;
+
+    // ---------------- start of a piece: query levels and fresh state
+    if (i == 0 || mt.t == 0) {
+      piece_t0 = mt.t;
+      {
+        // thread (row = tid / 16, chunk = tid % 16) converts 8 values of one query row
+        const int row = tid >> 4, ch = tid & 15;
+        float f[8];
+        if (row < R) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[row * (kD * 2) + ch * 16]);
+          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t = __bfloat1622float2(p2[e]);
+            f[2 * e] = t.x;
+            f[2 * e + 1] = t.y;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = 0.f;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+        for (int sh = 1; sh <= 8; sh <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+        const float inv = amax > 0.f ? 127.f / amax : 0.f;
+        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float t = f[e] * inv;
+          const float h = rintf(t);
+          const float l = rintf((t - h) * 254.f);
+          hi[e >> 2] |= ((uint32_t)(int)h & 0xffu) << (8 * (e & 3));
+          lo[e >> 2] |= ((uint32_t)(int)l & 0xffu) << (8 * (e & 3));
+        }
+        *reinterpret_cast<uint2*>(&sm.qlev[swz(row, 8 * ch)]) = make_uint2(hi[0], hi[1]);
+        *reinterpret_cast<uint2*>(&sm.qlev[swz(8 + row, 8 * ch)]) = make_uint2(lo[0], lo[1]);
+        if (ch == 0) sm.qsc[row] = amax * (1.f / 127.f) * unit2 * (1.f / 254.f);
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        m_run[r] = -INFINITY;
+        l_run[r] = 0.f;
+        o[r] = 0.f;
+      }
+      fence_async_smem();
+      __syncthreads();
+    }
+
+    // ---------------- S^T = K Ql^T on the tensor core; the next tile is requested meanwhile
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t k_addr = smem_u32(&sm.kv[stage][0][0]);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_i8(tmem, umma_desc(k_addr + 32 * ks), umma_desc(q_desc_addr + 32 * ks), kIdescS, ks > 0);
+      umma_commit(bar_s);
+    }
+    produce(next_stage);
+
+    if (!mbar_wait(bar_s, phase)) dead = true;
+    tc_fence_after();
+    float xv[8];
+    {
+      uint32_t s[16];
+      tmem_ld16(tmem_lane, s);
+      tmem_ld_wait();
+      const bool valid = mt.t * kTileU + tid < mt.n;
+      float mk = 0.f;
+      if (mt.use_add && valid) {  // additive mask that is not a plain 0 / -inf range (rare)
+        SeqRange rg;
+        rg.n = mt.n;
+        rg.first = mt.first;
+        mk = kLog2e * __bfloat162float(mask[(int64_t)mt.b * a.mk_b + physical_pos(a, rg, mt.t * kTileU + tid)]);
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float v = (float)((int)s[r] * 254 + (int)s[8 + r]) * (sm.qsc[r] * cks) + mk;
+        xv[r] = valid ? v : -INFINITY;
+      }
+    }
+    // tile maxima per row (and the largest V scale) across the 128 tokens
+    {
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int key = __reduce_max_sync(0xffffffffu, order_key(xv[r]));
+        if (lane == r) sm.xch[warp][r] = key_value(key);
+      }
+      const int key = __reduce_max_sync(0xffffffffu, order_key(cvs));
+      if (lane == 8) sm.xch[warp][8] = key_value(key);
+    }
+    tc_fence_before();
+    __syncthreads();
+    float alpha[8];
+    float cmax;
+    {
+      float4 t0[4], t1[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        t0[w] = *reinterpret_cast<const float4*>(&sm.xch[w][0]);
+        t1[w] = *reinterpret_cast<const float4*>(&sm.xch[w][4]);
+      }
+      cmax = fmaxf(fmaxf(sm.xch[0][8], sm.xch[1][8]), fmaxf(sm.xch[2][8], sm.xch[3][8]));
+      float tm[8];
+      tm[0] = fmaxf(fmaxf(t0[0].x, t0[1].x), fmaxf(t0[2].x, t0[3].x));
+      tm[1] = fmaxf(fmaxf(t0[0].y, t0[1].y), fmaxf(t0[2].y, t0[3].y));
+      tm[2] = fmaxf(fmaxf(t0[0].z, t0[1].z), fmaxf(t0[2].z, t0[3].z));
+      tm[3] = fmaxf(fmaxf(t0[0].w, t0[1].w), fmaxf(t0[2].w, t0[3].w));
+      tm[4] = fmaxf(fmaxf(t1[0].x, t1[1].x), fmaxf(t1[2].x, t1[3].x));
+      tm[5] = fmaxf(fmaxf(t1[0].y, t1[1].y), fmaxf(t1[2].y, t1[3].y));
+      tm[6] = fmaxf(fmaxf(t1[0].z, t1[1].z), fmaxf(t1[2].z, t1[3].z));
+      tm[7] = fmaxf(fmaxf(t1[0].w, t1[1].w), fmaxf(t1[2].w, t1[3].w));
+      const float pscale = cmax > 0.f ? cvs / cmax * 16777215.f : 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float mn = fmaxf(m_run[r], tm[r]);
+        const float mu = mn == -INFINITY ? 0.f : mn;  // -inf only while every logit of the row so far was masked
+        alpha[r] = fast_exp2(m_run[r] - mu);           // exp2(-inf) = 0 on the first tokens
+        m_run[r] = mn;
+        const float p = fast_exp2(xv[r] - mu);
+        l_run[r] = l_run[r] * alpha[r] + p;
+        const uint32_t y = __float2uint_rn(p * pscale);
+        const uint32_t pa = p_addr + (r * 128) + ((tchunk ^ r) << 4);
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa), "r"(y));
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 1024), "r"(y >> 8));
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 2048), "r"(y >> 16));
+      }
+    }
+    fence_async_smem();
+    __syncthreads();
+
+    // ---------------- O^T = V^T Pl^T on the tensor core
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t v_addr = smem_u32(&sm.kv[stage][1][0]);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_i8(tmem + kColO, umma_desc(v_addr + 4096 * ks), umma_desc(p_desc_addr + 32 * ks), kIdescO, ks > 0);
+      umma_commit(bar_o);
+    }
+    if (!mbar_wait(bar_o, phase)) dead = true;
+    phase ^= 1;
+    tc_fence_after();
+    {
+      uint32_t o01[16], o2[8];
+      tmem_ld16(tmem_lane + kColO, o01);
+      tmem_ld8(tmem_lane + kColO + 16, o2);
+      tmem_ld_wait();
+      const float oscale = cmax * (1.f / 16777215.f);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float t = (float)(int)o01[r] + 256.f * (float)(int)o01[8 + r] + 65536.f * (float)(int)o2[r];
+        o[r] = o[r] * alpha[r] + t * oscale;
+      }
+    }
+    if (__syncthreads_or(dead)) {
+      if (tid == 0) atomicExch(status, 1);
+      break;
+    }
+
+    // ---------------- end of a piece: write the rows, or a partial for the merge
+    if (last_of_share || mt.t == mt.T - 1) {
+      const bool is_final = piece_t0 == 0 && mt.t == mt.T - 1;
+      const int slot = piece_t0 > 0 ? 0 : 1;
+      const int64_t row_base = ((int64_t)mt.b * a.Hkv + mt.h) * R;
+      // denominators: sum the token shares of the 128 threads
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        float l = l_run[r];
+#pragma unroll
+        for (int sh = 1; sh <= 16; sh <<= 1) l += __shfl_xor_sync(0xffffffffu, l, sh);
+        if (lane == r) sm.red[warp][r] = l;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < R) {
+          const float L = (sm.red[0][r] + sm.red[1][r]) + (sm.red[2][r] + sm.red[3][r]);
+          const float M = m_run[r];
+          if (is_final) {
+            const int64_t row = row_base + r;
+            static_cast<__nv_bfloat16*>(a.o)[row * kD + tid] = __float2bfloat16_rn(L > 0.f ? o[r] / L : 0.f);
+            if (tid == 0) {
+              if (a.m) a.m[row] = M * kLn2;
+              if (a.l) a.l[row] = L > 0.f ? L : 0.f;
+            }
+          } else {
+            const int64_t pr = ((int64_t)cta * 2 + slot) * kMaxRows + r;
+            __stcg(&x.part_o[pr * kD + tid], o[r]);
+            if (tid == 0) {
+              __stcg(&x.part_m[pr], M);
+              __stcg(&x.part_l[pr], L);
+              __stcg(&x.part_t[pr], M);
+            }
+          }
+        }
+      }
+      if (!is_final) {
+        // Whoever delivers the last piece of the segment combines all of them.
+        // The counter wraps back to zero on that arrival, ready for the next launch.
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+          const unsigned old = atomicInc(&x.counters[mt.b * a.Hkv + mt.h], (unsigned)(mt.parts - 1));
+          sm.flag = old == (unsigned)(mt.parts - 1);
+        }
+        __syncthreads();
+        if (sm.flag) {
+          __threadfence();
+          // both MMAs of this stage are complete, so its K rows (16 KB) are free
+          merge_segment(a, x, mt.first_cta, mt.parts, row_base, reinterpret_cast<float*>(&sm.kv[stage][0][0]));
+        }
+      }
+      // The next iteration's barrier orders these reads before the stage is refilled.
+    }
+    stage = next_stage;
+  }
+  cp_async_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemCols) : "memory");
+  }
+}
+
+int umma_num_ctas() { return sm_count() * kCtasPerSm; }
+
+}  // namespace
+
+bool attention_umma_eligible(const jpt_attn_params& p) {
+  const int R = (p.Hq / p.Hkv) * p.Tq;
+  return attention_mma_eligible(p) && p.kv_dtype == JPT_INT8 && R <= 8;
+}
+
+int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st) {
+  const ScratchLayout lay = scratch_layout(p, umma_num_ctas());
+  JPT_REQUIRE(p.workspace && p.workspace_bytes >= lay.total, JPT_EWORKSPACE,
+              "flash_decode: workspace of %zu bytes needed, %zu given", lay.total, p.workspace_bytes);
+  JPT_REQUIRE(aligned(p.workspace, 256), JPT_EALIGN, "flash_decode: workspace must be 256-byte aligned");
+  char* ws = static_cast<char*>(p.workspace);
+  MmaScratch x;
+  x.counters = reinterpret_cast<unsigned*>(ws + lay.counters);
+  x.seqinfo = reinterpret_cast<int32_t*>(ws + lay.seqinfo);
+  x.part_m = reinterpret_cast<float*>(ws + lay.part_m);
+  x.part_l = reinterpret_cast<float*>(ws + lay.part_l);
+  x.part_t = reinterpret_cast<float*>(ws + lay.part_t);
+  x.part_o = reinterpret_cast<float*>(ws + lay.part_o);
+  x.num_ctas = lay.num_ctas;
+  int* status = reinterpret_cast<int*>(ws + kWorkspaceStatusOffset);
+
+  constexpr int smem_bytes = (int)sizeof(SmemU) + 1024;  // slack to align the base to 1024 bytes
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    configured = true;
+  }
+  if (a.mask_mode == JPT_MASK_ADD) {
+    if (int rc = launch_mask_ranges(a, x, st)) return rc;
+  }
+  flash_decode_i8_umma_kernel<<<lay.num_ctas, kThreads, smem_bytes, st>>>(a, x, status);
+  return check_launch("flash_decode_i8_umma_kernel");
+}
+
+}  // namespace jpt
