@@ -254,6 +254,27 @@ def run_cuda(args):
       dist.barrier()
     torch.cuda.synchronize()
 
+  if args.only:
+    # One kernel alone, launched eagerly: the command line for profiler captures.
+    def only_fn():
+      for i in range(nl):
+        if args.only == "attention":
+          ak.ragged_mha(hq_all[i], ck[i], cv[i], i, start_d, lens_d, None, None, ks[i], vs[i])
+        else:
+          caches[i].update(hk_all[i], hv_all[i], i)
+    for _ in range(max(3, args.warmup)):
+      only_fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+      only_fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"only": args.only, "layers": nl, "launches": nl * (args.steps + max(3, args.warmup)),
+                      "us_per_launch": e0.elapsed_time(e1) * 1e3 / (args.steps * nl)}), flush=True)
+    return
+
   # ---- warm-up (also sizes the split-K workspace), then try a CUDA graph of one step
   for _ in range(max(3, args.warmup)):
     device_step()
@@ -429,6 +450,8 @@ def main():
   ap.add_argument("--layers", type=int, default=80)
   ap.add_argument("--no-graph", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--only", choices=["attention", "append"], default=None,
+                  help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
   args = ap.parse_args()
   if args.impl == "reference":
     run_reference(args)

@@ -72,11 +72,23 @@ __device__ __forceinline__ SeqRange seq_range_x(const AttnArgs& a, const MmaScra
   return seq_range(a, b);
 }
 
+// Barrier of the 128 threads that run merge_segment: the whole CTA, or (in a
+// CTA with more warps) threads 0..127 through named barrier 2.
+template <bool kWorkerGroup>
+__device__ __forceinline__ void group_sync() {
+  if constexpr (kWorkerGroup) {
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+  } else {
+    __syncthreads();
+  }
+}
+
 // Combine the `parts` partials of one segment (CTAs first .. first+parts-1) and
 // write its R final rows.  `scratch` is at least (parts + 3) * 16 floats of
-// shared memory.  Called by a whole CTA.
+// shared memory.  Called by 128 threads (threadIdx.x 0..127).
+template <bool kWorkerGroup = false>
 static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int first, int parts, int64_t row_base,
-                              float* scratch) {
+                                     float* scratch) {
   const int tid = threadIdx.x, R = a.R;
   float* s_w = scratch;                     // [parts][16] weights
   float* s_M = scratch + parts * kMaxRows;  // [16] reference maximum
@@ -85,19 +97,19 @@ static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int
     const int pi = i / R, r = i - pi * R;
     s_w[pi * kMaxRows + r] = __ldcg(&x.part_m[((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows + r]);
   }
-  __syncthreads();
+  group_sync<kWorkerGroup>();
   if (tid < R) {
     float M = -INFINITY;
     for (int pi = 0; pi < parts; ++pi) M = fmaxf(M, s_w[pi * kMaxRows + tid]);
     s_M[tid] = M;
   }
-  __syncthreads();
+  group_sync<kWorkerGroup>();
   for (int i = tid; i < parts * R; i += kThreads) {
     const int pi = i / R, r = i - pi * R;
     const float mw = s_w[pi * kMaxRows + r];
     s_w[pi * kMaxRows + r] = mw == -INFINITY ? 0.f : fast_exp2(mw - s_M[r]);
   }
-  __syncthreads();
+  group_sync<kWorkerGroup>();
   if (tid < R) {
     float L = 0.f, mt = -INFINITY;
     for (int pi = 0; pi < parts; ++pi) {
@@ -110,7 +122,7 @@ static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int
     if (a.m) a.m[row_base + tid] = mt * kLn2;
     if (a.l) a.l[row_base + tid] = L > 0.f ? L * fast_exp2(s_M[tid] - mt) : 0.f;
   }
-  __syncthreads();
+  group_sync<kWorkerGroup>();
   float acc[kMaxRows];
 #pragma unroll
   for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;

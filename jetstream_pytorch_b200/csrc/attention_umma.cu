@@ -43,7 +43,7 @@ constexpr int kStagesU = 2;     // K/V ring depth
 constexpr int kTmemCols = 64;   // S^T: columns 0..15, O^T: columns 16..47
 constexpr int kColO = 16;
 constexpr int kCtasPerSm = 3;
-constexpr int kWaitPolls = 1 << 20;
+constexpr long long kWaitCycles = 1000000000ll;  // about half a second: far beyond any wait of a healthy run
 
 struct __align__(1024) SmemU {
   uint8_t kv[kStagesU][2][kTileU * kD];  // [stage][K, V][token][128 bytes], swizzled
@@ -95,16 +95,20 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 }
 // Bounded wait for the phase with the given parity; false when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < kWaitPolls; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+          : "=r"(ok)
+          : "r"(bar), "r"(parity)
+          : "memory");
+      if (ok) return true;
+    }
+    if (clock64() - t0 > kWaitCycles) return false;
   }
-  return false;
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -681,6 +685,8 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         (int)cudaSharedmemCarveoutMaxShared);  // three CTAs of 75 KB per SM
     configured = true;
   }
   if (a.mask_mode == JPT_MASK_ADD) {
