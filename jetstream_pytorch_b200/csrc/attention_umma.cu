@@ -408,7 +408,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   // ------------------------------------------------------------------ consumer state
   float m_run[8], l_run[8], o[8];  // l_run: this thread's token share of the denominators; o: head-dim index tid
   int piece_t0 = 0;
-  uint32_t phase = 0;
   bool dead = false;  // a wait ran out
   const float unit2 = a.sm_scale * kLog2e;
   const uint32_t bar_s = smem_u32(&sm.bar[0]), bar_o = smem_u32(&sm.bar[1]);
@@ -417,81 +416,108 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   const uint32_t p_addr = smem_u32(&sm.plev[0]) + (tid & 15);
   const int tchunk = tid >> 4;
 
-  produce(0);
-
-  int stage = 0;
-  for (int i = 0;; ++i) {
-    cp_async_wait<0>();
-    const float cks = nks, cvs = nvs;  // scales of this thread's token in the tile of `stage`
-    fence_async_smem();                // the copied rows become visible to the tensor core
+  // Query levels of the piece that starts with the tile in `st` (when it
+  // starts one), then S^T of that tile on the tensor core.  Called by the whole
+  // CTA once the tile's rows have landed and a barrier has made them (and the
+  // record) visible; the logits of the tile before are out of tensor memory.
+  auto prepare = [&](int st, const TileMeta& mt, bool first) {
+    if (first || mt.t == 0) {
+      // thread (row = tid / 16, chunk = tid % 16) converts 8 values of one query row
+      const int row = tid >> 4, ch = tid & 15;
+      float f[8];
+      if (row < R) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[row * (kD * 2) + ch * 16]);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t = __bfloat1622float2(p2[e]);
+          f[2 * e] = t.x;
+          f[2 * e + 1] = t.y;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = 0.f;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+      for (int sh = 1; sh <= 8; sh <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+      const float inv = amax > 0.f ? 127.f / amax : 0.f;
+      uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float t = f[e] * inv;
+        const float h = rintf(t);
+        const float l = rintf((t - h) * 254.f);
+        hi[e >> 2] |= ((uint32_t)(int)h & 0xffu) << (8 * (e & 3));
+        lo[e >> 2] |= ((uint32_t)(int)l & 0xffu) << (8 * (e & 3));
+      }
+      *reinterpret_cast<uint2*>(&sm.qlev[swz(row, 8 * ch)]) = make_uint2(hi[0], hi[1]);
+      *reinterpret_cast<uint2*>(&sm.qlev[swz(8 + row, 8 * ch)]) = make_uint2(lo[0], lo[1]);
+      if (ch == 0) sm.qsc[row] = amax * (1.f / 127.f) * unit2 * (1.f / 254.f);
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+    }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t k_addr = smem_u32(&sm.kv[st][0][0]);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_i8(tmem, umma_desc(k_addr + 32 * ks), umma_desc(q_desc_addr + 32 * ks), kIdescS, ks > 0);
+      umma_commit(bar_s);
+    }
+  };
+  // O^T of the tile with the given parity into the accumulators (alpha and cmax are that tile's)
+  auto add_output = [&](uint32_t parity, const float (&alpha)[8], float cmax) {
+    if (!mbar_wait(bar_o, parity)) dead = true;
+    tc_fence_after();
+    uint32_t o01[16], o2[8];
+    tmem_ld16(tmem_lane + kColO, o01);
+    tmem_ld8(tmem_lane + kColO + 16, o2);
+    tmem_ld_wait();
     tc_fence_before();
-    __syncthreads();
-    const TileMeta mt = sm.meta[stage];
-    if (mt.t < 0) break;
+    const float oscale = cmax * (1.f / 16777215.f);
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const float t = (float)(int)o01[r] + 256.f * (float)(int)o01[8 + r] + 65536.f * (float)(int)o2[r];
+      o[r] = o[r] * alpha[r] + t * oscale;
+    }
+  };
+
+  // The tensor core works one step ahead of the threads: S^T of tile i+1 is
+  // issued at the end of iteration i, and O^T of tile i is collected in
+  // iteration i+1 (at once only when tile i ends a piece), so neither MMA is
+  // waited for right after it was issued.
+  produce(0);
+  cp_async_wait<0>();
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  TileMeta mt = sm.meta[0];
+  if (mt.t >= 0) prepare(0, mt, true);
+
+  float alpha_prev[8], cmax_prev = 0.f;
+  bool pending = false;  // O^T of the tile before has not been added yet
+  int stage = 0;
+  for (int i = 0; mt.t >= 0; ++i) {
+    const float cks = nks, cvs = nvs;  // scales of this thread's token in the tile of `stage`
     const int next_stage = stage ^ 1;
     const bool last_of_share = mt.pad[2] != 0;
-
-    // ---------------- start of a piece: query levels and fresh state
-    if (i == 0 || mt.t == 0) {
+    const uint32_t par = (uint32_t)i & 1u;
+    if (i == 0 || mt.t == 0) {  // a piece starts (the one before was flushed when it ended)
       piece_t0 = mt.t;
-      {
-        // thread (row = tid / 16, chunk = tid % 16) converts 8 values of one query row
-        const int row = tid >> 4, ch = tid & 15;
-        float f[8];
-        if (row < R) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[row * (kD * 2) + ch * 16]);
-          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 t = __bfloat1622float2(p2[e]);
-            f[2 * e] = t.x;
-            f[2 * e + 1] = t.y;
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = 0.f;
-        }
-        float amax = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
-#pragma unroll
-        for (int sh = 1; sh <= 8; sh <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
-        const float inv = amax > 0.f ? 127.f / amax : 0.f;
-        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float t = f[e] * inv;
-          const float h = rintf(t);
-          const float l = rintf((t - h) * 254.f);
-          hi[e >> 2] |= ((uint32_t)(int)h & 0xffu) << (8 * (e & 3));
-          lo[e >> 2] |= ((uint32_t)(int)l & 0xffu) << (8 * (e & 3));
-        }
-        *reinterpret_cast<uint2*>(&sm.qlev[swz(row, 8 * ch)]) = make_uint2(hi[0], hi[1]);
-        *reinterpret_cast<uint2*>(&sm.qlev[swz(8 + row, 8 * ch)]) = make_uint2(lo[0], lo[1]);
-        if (ch == 0) sm.qsc[row] = amax * (1.f / 127.f) * unit2 * (1.f / 254.f);
-      }
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         m_run[r] = -INFINITY;
         l_run[r] = 0.f;
         o[r] = 0.f;
       }
-      fence_async_smem();
-      __syncthreads();
     }
 
-    // ---------------- S^T = K Ql^T on the tensor core; the next tile is requested meanwhile
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t k_addr = smem_u32(&sm.kv[stage][0][0]);
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        umma_i8(tmem, umma_desc(k_addr + 32 * ks), umma_desc(q_desc_addr + 32 * ks), kIdescS, ks > 0);
-      umma_commit(bar_s);
-    }
-    produce(next_stage);
-
-    if (!mbar_wait(bar_s, phase)) dead = true;
+    // ---------------- logits of this thread's token
+    if (!mbar_wait(bar_s, par)) dead = true;
     tc_fence_after();
     float xv[8];
     {
@@ -524,6 +550,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     }
     tc_fence_before();
     __syncthreads();
+
+    // ---------------- the output of the tile before; its stage is free after that
+    if (pending) {
+      add_output(par ^ 1u, alpha_prev, cmax_prev);
+      pending = false;
+    }
+    produce(next_stage);
+
     float alpha[8];
     float cmax;
     {
@@ -552,11 +586,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
         m_run[r] = mn;
         const float p = fast_exp2(xv[r] - mu);
         l_run[r] = l_run[r] * alpha[r] + p;
-        const uint32_t y = __float2uint_rn(p * pscale);
+        const uint32_t y = __float2uint_rn(fminf(p * pscale, 16777215.f));
         const uint32_t pa = p_addr + (r * 128) + ((tchunk ^ r) << 4);
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa), "r"(y));
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 1024), "r"(y >> 8));
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 2048), "r"(y >> 16));
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa), "r"(y) : "memory");
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 1024), "r"(y >> 8) : "memory");
+        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 2048), "r"(y >> 16) : "memory");
       }
     }
     fence_async_smem();
@@ -571,28 +605,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
         umma_i8(tmem + kColO, umma_desc(v_addr + 4096 * ks), umma_desc(p_desc_addr + 32 * ks), kIdescO, ks > 0);
       umma_commit(bar_o);
     }
-    if (!mbar_wait(bar_o, phase)) dead = true;
-    phase ^= 1;
-    tc_fence_after();
-    {
-      uint32_t o01[16], o2[8];
-      tmem_ld16(tmem_lane + kColO, o01);
-      tmem_ld8(tmem_lane + kColO + 16, o2);
-      tmem_ld_wait();
-      const float oscale = cmax * (1.f / 16777215.f);
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float t = (float)(int)o01[r] + 256.f * (float)(int)o01[8 + r] + 65536.f * (float)(int)o2[r];
-        o[r] = o[r] * alpha[r] + t * oscale;
-      }
-    }
-    if (__syncthreads_or(dead)) {
-      if (tid == 0) atomicExch(status, 1);
-      break;
-    }
 
-    // ---------------- end of a piece: write the rows, or a partial for the merge
-    if (last_of_share || mt.t == mt.T - 1) {
+    if (!(last_of_share || mt.t == mt.T - 1)) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r) alpha_prev[r] = alpha[r];
+      cmax_prev = cmax;
+      pending = true;
+    } else {
+      // ---------------- end of a piece: write the rows, or a partial for the merge
+      add_output(par, alpha, cmax);
       const bool is_final = piece_t0 == 0 && mt.t == mt.T - 1;
       const int slot = piece_t0 > 0 ? 0 : 1;
       const int64_t row_base = ((int64_t)mt.b * a.Hkv + mt.h) * R;
@@ -644,8 +665,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
           merge_segment(a, x, mt.first_cta, mt.parts, row_base, reinterpret_cast<float*>(&sm.kv[stage][0][0]));
         }
       }
-      // The next iteration's barrier orders these reads before the stage is refilled.
     }
+
+    // ---------------- the next tile: its rows have had the iteration to land
+    cp_async_wait<0>();
+    fence_async_smem();
+    tc_fence_before();
+    if (__syncthreads_or(dead)) {
+      if (tid == 0) atomicExch(status, 1);
+      break;
+    }
+    mt = sm.meta[next_stage];
+    if (mt.t >= 0) prepare(next_stage, mt, false);
     stage = next_stage;
   }
   cp_async_wait<0>();

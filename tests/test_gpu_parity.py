@@ -577,11 +577,13 @@ def test_ragged_mha_head_dim_128_matches_oracle(int8, ring, heads):
   _check_ragged(_ragged_case(63, 6, hq, hkv, 512, 128, int8, ring), ring)
 
 
-def test_ragged_mha_llama2_70b_shape_full_size():
+@pytest.mark.parametrize("kernel", [0, 2])
+def test_ragged_mha_llama2_70b_shape_full_size(kernel):
   """BASELINE config 3 at full size: B=96, 64 q / 8 kv heads, D=128, S=2048,
-  int8 KV with per-token scales, left aligned and ring."""
+  int8 KV with per-token scales, left aligned and ring; through the tcgen05
+  kernel (0) and the mma.sync kernel (2)."""
   for ring in (False, True):
-    _check_ragged(_ragged_case(64, 96, 64, 8, 2048, 128, True, ring), ring)
+    _check_ragged(_ragged_case(64, 96, 64, 8, 2048, 128, True, ring), ring, force_generic=kernel)
 
 
 @pytest.mark.parametrize("int8", [True, False])
@@ -596,6 +598,11 @@ def test_ragged_fast_and_generic_kernels_agree(int8):
   live = torch.isfinite(m2)
   assert torch.allclose(m1[live], m2[live], atol=1e-3, rtol=1e-3)
   assert torch.allclose(l1[live], l2[live], atol=1e-3, rtol=1e-3)
+  # force_generic=2: the mma.sync kernel where the tcgen05 one would have been picked (int8, <= 8 rows)
+  o3, (m3, l3) = ak.ragged_mha(*args, ring=True, force_generic=2)
+  assert close(o3, o2)
+  assert torch.allclose(m3[live], m2[live], atol=1e-3, rtol=1e-3)
+  assert torch.allclose(l3[live], l2[live], atol=1e-3, rtol=1e-3)
 
 
 def test_ragged_mha_bf16_cache_llama3_8b_shape_full_size():
