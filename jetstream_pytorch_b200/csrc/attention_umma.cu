@@ -60,6 +60,19 @@ struct __align__(1024) SmemU {
   TileMeta meta[kStagesU];
 };
 
+// 16-byte copy with compile-time offsets on both addresses (one pair of base registers per tensor)
+template <int kOff>
+__device__ __forceinline__ void cp_async16_at(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %2], 16;\n" ::"r"(dst), "l"(src), "n"(kOff));
+}
+template <int kI>
+__device__ __forceinline__ void cp_async_tile_rows(uint32_t kdst, uint32_t vdst, const void* kp, const void* vp) {
+  if constexpr (kI < 8) {
+    cp_async16_at<2048 * kI>(kdst, kp);
+    cp_async16_at<2048 * kI>(vdst, vp);
+    cp_async_tile_rows<kI + 1>(kdst, vdst, kp, vp);
+  }
+}
 __device__ __forceinline__ int tiles_u(int n) { return (n + kTileU - 1) / kTileU; }
 __device__ __forceinline__ int slots_u(int n) { return n > 0 ? tiles_u(n) + kPieceCost : 0; }
 
@@ -94,7 +107,16 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait for the phase with the given parity; false when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
@@ -109,6 +131,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     if (clock64() - t0 > kWaitCycles) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  return mbar_probe(bar, parity) || mbar_wait_slow(bar, parity);
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -134,8 +159,15 @@ __device__ __forceinline__ int order_key(float x) {
 __device__ __forceinline__ float key_value(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_kernel(AttnArgs a, MmaScratch x, int* status) {
-  extern __shared__ uint8_t smem_raw[];
-  SmemU& sm = *reinterpret_cast<SmemU*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // The swizzled tiles need a 1024-byte aligned base.  The array is declared
+  // with that alignment (and used in place, so that every access compiles to a
+  // shared-memory instruction); a base that is not aligned after all is reported.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  SmemU& sm = *reinterpret_cast<SmemU*>(smem_raw);
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicExch(status, 2);
+    return;
+  }
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int R = a.R;
@@ -332,11 +364,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       const int64_t off = (int64_t)(ppos + prow) * kD;
       const int8_t* kp = kseg + off;
       const int8_t* vp = vseg + off;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        cp_async16(kdst + 2048 * i, kp + 2048 * i, true);
-        cp_async16(vdst + 2048 * i, vp + 2048 * i, true);
-      }
+      cp_async_tile_rows<0>(kdst, vdst, kp, vp);
     } else if (pass_pages) {
       // paged caches start at position 0: pass i (rows 16 i ..) lies inside one page
       int pi = j0 / a.page_size, within = (j0 % a.page_size) / 16;
@@ -516,14 +544,32 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       }
     }
 
-    // ---------------- logits of this thread's token
+    // ---------------- the output of the tile before and the logits of this one leave
+    // tensor memory in one round trip; the stage of the tile before is free after that
     if (!mbar_wait(bar_s, par)) dead = true;
+    if (pending && !mbar_wait(bar_o, par ^ 1u)) dead = true;
     tc_fence_after();
     float xv[8];
     {
       uint32_t s[16];
-      tmem_ld16(tmem_lane, s);
-      tmem_ld_wait();
+      if (pending) {
+        uint32_t o01[16], o2[8];
+        tmem_ld16(tmem_lane + kColO, o01);
+        tmem_ld8(tmem_lane + kColO + 16, o2);
+        tmem_ld16(tmem_lane, s);
+        tmem_ld_wait();
+        const float oscale = cmax_prev * (1.f / 16777215.f);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const float t = (float)(int)o01[r] + 256.f * (float)(int)o01[8 + r] + 65536.f * (float)(int)o2[r];
+          o[r] = o[r] * alpha_prev[r] + t * oscale;
+        }
+        pending = false;
+      } else {
+        tmem_ld16(tmem_lane, s);
+        tmem_ld_wait();
+      }
+      produce(next_stage);
       const bool valid = mt.t * kTileU + tid < mt.n;
       float mk = 0.f;
       if (mt.use_add && valid) {  // additive mask that is not a plain 0 / -inf range (rare)
@@ -550,13 +596,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     }
     tc_fence_before();
     __syncthreads();
-
-    // ---------------- the output of the tile before; its stage is free after that
-    if (pending) {
-      add_output(par ^ 1u, alpha_prev, cmax_prev);
-      pending = false;
-    }
-    produce(next_stage);
 
     float alpha[8];
     float cmax;
@@ -712,7 +751,7 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   x.num_ctas = lay.num_ctas;
   int* status = reinterpret_cast<int*>(ws + kWorkspaceStatusOffset);
 
-  constexpr int smem_bytes = (int)sizeof(SmemU) + 1024;  // slack to align the base to 1024 bytes
+  constexpr int smem_bytes = (int)sizeof(SmemU);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
