@@ -73,6 +73,32 @@ __device__ __forceinline__ void cp_async_tile_rows(uint32_t kdst, uint32_t vdst,
     cp_async_tile_rows<kI + 1>(kdst, vdst, kp, vp);
   }
 }
+// The three bytes of y into level rows r, 8 + r, 16 + r (kRowOff = 128 r) of the probability levels.
+template <int kRowOff>
+__device__ __forceinline__ void store_levels(uint32_t addr, uint32_t y) {
+  asm volatile("st.shared.u8 [%0 + %2], %1;" ::"r"(addr), "r"(y), "n"(kRowOff) : "memory");
+  asm volatile("st.shared.u8 [%0 + %2], %1;" ::"r"(addr), "r"(y >> 8), "n"(kRowOff + 1024) : "memory");
+  asm volatile("st.shared.u8 [%0 + %2], %1;" ::"r"(addr), "r"(y >> 16), "n"(kRowOff + 2048) : "memory");
+}
+constexpr float kNoMax = -1.0e30f;  // "no logit seen yet": finite, far below any logit
+// Rows kRow .. 7 of one token: new running maximum, rescale factor, probability,
+// denominator share, and the probability's three level bytes.  m_run starts at
+// kNoMax (finite), so exp2(old - new) and exp2(-inf - new) need no special case.
+template <int kRow>
+__device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8], float (&alpha)[8], const float (&tm)[8],
+                                             const float (&xv)[8], float pscale, uint32_t p_base) {
+  if constexpr (kRow < 8) {
+    const float mn = fmaxf(m_run[kRow], tm[kRow]);
+    float al, p;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(al) : "f"(m_run[kRow] - mn));
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(p) : "f"(xv[kRow] - mn));
+    alpha[kRow] = al;
+    m_run[kRow] = mn;
+    l_run[kRow] = l_run[kRow] * al + p;
+    store_levels<128 * kRow>(p_base ^ (uint32_t)(kRow << 4), __float2uint_rn(p * pscale));
+    softmax_rows<kRow + 1>(m_run, l_run, alpha, tm, xv, pscale, p_base);
+  }
+}
 __device__ __forceinline__ int tiles_u(int n) { return (n + kTileU - 1) / kTileU; }
 __device__ __forceinline__ int slots_u(int n) { return n > 0 ? tiles_u(n) + kPieceCost : 0; }
 
@@ -440,9 +466,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   const float unit2 = a.sm_scale * kLog2e;
   const uint32_t bar_s = smem_u32(&sm.bar[0]), bar_o = smem_u32(&sm.bar[1]);
   const uint32_t q_desc_addr = smem_u32(&sm.qlev[0]), p_desc_addr = smem_u32(&sm.plev[0]);
-  // this thread's byte of row r of the probability levels: ((tid / 16) ^ r) * 16 + tid % 16
-  const uint32_t p_addr = smem_u32(&sm.plev[0]) + (tid & 15);
-  const int tchunk = tid >> 4;
+  // this thread's byte of row r of the probability levels: ((tid / 16) ^ r) * 16 + tid % 16.
+  // plev is 1024-byte aligned, so the XOR with r << 4 can be applied to the whole address.
+  const uint32_t p_base = smem_u32(&sm.plev[0]) + (tid & 15) + ((uint32_t)(tid >> 4) << 4);
 
   // Query levels of the piece that starts with the tile in `st` (when it
   // starts one), then S^T of that tile on the tensor core.  Called by the whole
@@ -538,7 +564,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       piece_t0 = mt.t;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        m_run[r] = -INFINITY;
+        m_run[r] = kNoMax;
         l_run[r] = 0.f;
         o[r] = 0.f;
       }
@@ -571,28 +597,31 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       }
       produce(next_stage);
       const bool valid = mt.t * kTileU + tid < mt.n;
-      float mk = 0.f;
+      float mk = valid ? 0.f : -INFINITY;  // a token past the end: finite dot product + (-inf)
       if (mt.use_add && valid) {  // additive mask that is not a plain 0 / -inf range (rare)
         SeqRange rg;
         rg.n = mt.n;
         rg.first = mt.first;
         mk = kLog2e * __bfloat162float(mask[(int64_t)mt.b * a.mk_b + physical_pos(a, rg, mt.t * kTileU + tid)]);
       }
+      const float4 q0 = *reinterpret_cast<const float4*>(&sm.qsc[0]), q1 = *reinterpret_cast<const float4*>(&sm.qsc[4]);
+      const float qc[8] = {q0.x * cks, q0.y * cks, q0.z * cks, q0.w * cks, q1.x * cks, q1.y * cks, q1.z * cks, q1.w * cks};
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float v = (float)((int)s[r] * 254 + (int)s[8 + r]) * (sm.qsc[r] * cks) + mk;
-        xv[r] = valid ? v : -INFINITY;
-      }
+      for (int r = 0; r < 8; ++r) xv[r] = fmaf((float)((int)s[r] * 254 + (int)s[8 + r]), qc[r], mk);
     }
     // tile maxima per row (and the largest V scale) across the 128 tokens
     {
+      int key[9];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const int key = __reduce_max_sync(0xffffffffu, order_key(xv[r]));
-        if (lane == r) sm.xch[warp][r] = key_value(key);
+      for (int r = 0; r < 8; ++r) key[r] = __reduce_max_sync(0xffffffffu, order_key(xv[r]));
+      key[8] = __reduce_max_sync(0xffffffffu, order_key(cvs));
+      if (lane == 0) {
+        *reinterpret_cast<float4*>(&sm.xch[warp][0]) =
+            make_float4(key_value(key[0]), key_value(key[1]), key_value(key[2]), key_value(key[3]));
+        *reinterpret_cast<float4*>(&sm.xch[warp][4]) =
+            make_float4(key_value(key[4]), key_value(key[5]), key_value(key[6]), key_value(key[7]));
+        sm.xch[warp][8] = key_value(key[8]);
       }
-      const int key = __reduce_max_sync(0xffffffffu, order_key(cvs));
-      if (lane == 8) sm.xch[warp][8] = key_value(key);
     }
     tc_fence_before();
     __syncthreads();
@@ -616,21 +645,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       tm[5] = fmaxf(fmaxf(t1[0].y, t1[1].y), fmaxf(t1[2].y, t1[3].y));
       tm[6] = fmaxf(fmaxf(t1[0].z, t1[1].z), fmaxf(t1[2].z, t1[3].z));
       tm[7] = fmaxf(fmaxf(t1[0].w, t1[1].w), fmaxf(t1[2].w, t1[3].w));
-      const float pscale = cmax > 0.f ? cvs / cmax * 16777215.f : 0.f;
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float mn = fmaxf(m_run[r], tm[r]);
-        const float mu = mn == -INFINITY ? 0.f : mn;  // -inf only while every logit of the row so far was masked
-        alpha[r] = fast_exp2(m_run[r] - mu);           // exp2(-inf) = 0 on the first tokens
-        m_run[r] = mn;
-        const float p = fast_exp2(xv[r] - mu);
-        l_run[r] = l_run[r] * alpha[r] + p;
-        const uint32_t y = __float2uint_rn(fminf(p * pscale, 16777215.f));
-        const uint32_t pa = p_addr + (r * 128) + ((tchunk ^ r) << 4);
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa), "r"(y) : "memory");
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 1024), "r"(y >> 8) : "memory");
-        asm volatile("st.shared.u8 [%0], %1;" ::"r"(pa + 2048), "r"(y >> 16) : "memory");
-      }
+      // p <= 1 and the ratio is held at 1 (the fast division may land one ulp above), so
+      // the product stays below 2^24 without a clamp per row
+      const float pscale = cmax > 0.f ? fminf(__fdividef(cvs, cmax), 1.f) * 16777215.f : 0.f;
+      softmax_rows<0>(m_run, l_run, alpha, tm, xv, pscale, p_base);
     }
     fence_async_smem();
     __syncthreads();
@@ -669,7 +687,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       for (int r = 0; r < 8; ++r) {
         if (r < R) {
           const float L = (sm.red[0][r] + sm.red[1][r]) + (sm.red[2][r] + sm.red[3][r]);
-          const float M = m_run[r];
+          const float M = m_run[r] > 0.5f * kNoMax ? m_run[r] : -INFINITY;  // every logit of the row was masked
           if (is_final) {
             const int64_t row = row_base + r;
             static_cast<__nv_bfloat16*>(a.o)[row * kD + tid] = __float2bfloat16_rn(L > 0.f ? o[r] / L : 0.f);
