@@ -256,10 +256,17 @@ def run_cuda(args):
 
   if args.only:
     # One kernel alone, launched eagerly: the command line for profiler captures.
+    fg = 2 if args.attn_kernel == "mma" else 0  # the mma.sync kernel instead of the tcgen05 one
+    if args.only == "attention" and args.kv == "bf16":  # the same shape with an unquantised cache
+      ckb = torch.randn((nl, B, hkv, S, D), generator=gen, device=dev, dtype=torch.bfloat16)
+      cvb = torch.randn((nl, B, hkv, S, D), generator=gen, device=dev, dtype=torch.bfloat16)
+
     def only_fn():
       for i in range(nl):
-        if args.only == "attention":
-          ak.ragged_mha(hq_all[i], ck[i], cv[i], i, start_d, lens_d, None, None, ks[i], vs[i])
+        if args.only == "attention" and args.kv == "bf16":
+          ak.ragged_mha(hq_all[i], ckb[i], cvb[i], i, start_d, lens_d, None, None, None, None)
+        elif args.only == "attention":
+          ak.ragged_mha(hq_all[i], ck[i], cv[i], i, start_d, lens_d, None, None, ks[i], vs[i], force_generic=fg)
         else:
           caches[i].update(hk_all[i], hv_all[i], i)
     for _ in range(max(3, args.warmup)):
@@ -271,8 +278,14 @@ def run_cuda(args):
       only_fn()
     e1.record()
     torch.cuda.synchronize()
-    print(json.dumps({"only": args.only, "layers": nl, "launches": nl * (args.steps + max(3, args.warmup)),
-                      "us_per_launch": e0.elapsed_time(e1) * 1e3 / (args.steps * nl)}), flush=True)
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * nl)
+    nbytes = attention_bytes(lens, hkv) if args.only == "attention" else append_bytes(hkv)
+    if args.only == "attention" and args.kv == "bf16":
+      nbytes = int(lens.sum()) * hkv * D * 2 * 2 + 2 * B * hq * D * 2
+    # eager launches: for kernels shorter than the host's ~35 us per call this is the host's pace, not the kernel's
+    print(json.dumps({"only": args.only, "kv": args.kv, "attn_kernel": args.attn_kernel, "layers": nl,
+                      "launches": nl * (args.steps + max(3, args.warmup)), "us_per_eager_call": us,
+                      "algorithmic_bytes": nbytes, "gbs_at_that_pace": nbytes / us / 1e3}), flush=True)
     return
 
   # ---- warm-up (also sizes the split-K workspace), then try a CUDA graph of one step
@@ -452,6 +465,9 @@ def main():
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--only", choices=["attention", "append"], default=None,
                   help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
+  ap.add_argument("--kv", choices=["int8", "bf16"], default="int8", help="with --only attention: cache dtype")
+  ap.add_argument("--attn-kernel", choices=["auto", "mma"], default="auto",
+                  help="with --only attention: 'mma' forces the mma.sync kernel for the int8 cache")
   args = ap.parse_args()
   if args.impl == "reference":
     run_reference(args)
