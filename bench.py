@@ -234,12 +234,19 @@ def run_cuda(args):
   caches = [Int8KVCacheGenerate(ck[i], cv[i], ks[i], vs[i], pos_d, env=env) for i in range(nl)]
   start_d = torch.zeros(B, dtype=torch.int32, device=dev)
 
+  # Head-sharded scales need the amax over all ranks: inside the append launch over NVLink
+  # peer memory (default), or as local_amax + NCCL all_reduce(MAX) + update (--amax-exchange nccl).
+  px = None
+  if world > 1 and args.amax_exchange == "peers":
+    from jetstream_pytorch_b200.cache_manager import PeerAmaxExchange
+    px = PeerAmaxExchange.with_torch_distributed(B)
+
   def layer_step(i, q, xk, xv):
     amax = None
-    if world > 1:
+    if world > 1 and px is None:
       amax = caches[i].local_amax(xk, xv)
       dist.all_reduce(amax, op=dist.ReduceOp.MAX)
-    r = caches[i].update(xk, xv, i, amax=amax)
+    r = caches[i].update(xk, xv, i, amax=amax, peers=px)
     o, _ = ak.ragged_mha(q, r[0], r[1], i, start_d, lens_d, None, None, r[4], r[5])
     return o
 
@@ -430,7 +437,10 @@ def run_cuda(args):
       "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
       "vs_baseline": None, "dtype": "int8 KV / bf16 q / fp32 accumulate", "data": "synthetic",
       "config": {"workload": WORKLOAD, "layers": nl, "global_batch": B, "kv_heads_per_gpu": hkv,
-                 "parallelism": f"kv-head sharding x{world}", "l2": "each layer has its own cache buffers "
+                 "parallelism": f"kv-head sharding x{world}",
+                 "amax_exchange": ("in-kernel over NVLink peer memory" if px is not None else
+                                   ("nccl all_reduce" if world > 1 else "none")),
+                 "peer_exchange_status": (px.status() if px is not None else None), "l2": "each layer has its own cache buffers "
                  f"({2 * B * hkv * S * D * nl / 2**30:.1f} GiB per GPU in total, >> 126 MB L2)",
                  "cuda_graph": graph is not None},
       "us_per_layer": ms_step * 1e3 / nl,
@@ -463,6 +473,8 @@ def main():
   ap.add_argument("--layers", type=int, default=80)
   ap.add_argument("--no-graph", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--amax-exchange", choices=["peers", "nccl"], default="peers",
+                  help="N > 1: how the per-token amax is max-reduced over the ranks")
   ap.add_argument("--only", choices=["attention", "append"], default=None,
                   help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
   ap.add_argument("--kv", choices=["int8", "bf16"], default="int8", help="with --only attention: cache dtype")

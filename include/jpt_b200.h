@@ -87,6 +87,54 @@ int jpt_kv_quant_append_dense(const void* xk, const void* xv, int in_dtype,
                               float* amax_out, void* stream);
 
 /*
+ * The same update for caches whose KV heads are split across the GPUs of one
+ * node, with the max-reduction of the per-token amax done INSIDE the launch
+ * over NVLink peer memory: every rank stores (launch number, partial amax) as
+ * one 64-bit word per (K|V, slot) into every rank's exchange buffer and reads
+ * what the others stored into its own; no collective call, no second kernel.
+ * Replaces the reduction that GSPMD inserts for the sharded head axis of
+ * jetstream_pt/cache_manager.py:532-535 (environment.py:225-242 gives the
+ * sharding).  Codes and scales are bit-identical to the single-GPU ones (max
+ * is order-independent).
+ *
+ * All ranks must call this the same number of times, in the same order, with
+ * the same B.  A rank whose peer does not arrive within about half a second
+ * goes on with the values it has and raises the status of its buffer
+ * (jpt_peer_exchange_status); nothing waits without a limit.
+ *
+ * Setting up (once per process, any host-side transport for the handles):
+ *   bytes = jpt_peer_exchange_bytes(B, world);
+ *   jpt_peer_exchange_alloc(bytes, &own);            zero-filled device memory
+ *   jpt_peer_exchange_export(own, handle);           64 bytes, send to the peers
+ *   jpt_peer_exchange_import(handle_of_r, &buf[r]);  for every other rank r
+ *   px = { rank, world, B, { buf[0..world-1] } } with buf[rank] = own.
+ * jpt_peer_exchange_release(buf[r]) and jpt_peer_exchange_free(own) undo it.
+ */
+typedef struct jpt_peer_exchange {
+  int rank, world; /* 1 <= world <= 8 */
+  int batch;       /* the B the buffers were sized for */
+  void* buffers[8];
+} jpt_peer_exchange;
+
+size_t jpt_peer_exchange_bytes(int B, int world);
+int jpt_peer_exchange_alloc(size_t bytes, void** ptr);
+int jpt_peer_exchange_free(void* ptr);
+int jpt_peer_exchange_export(void* ptr, void* handle64);
+int jpt_peer_exchange_import(const void* handle64, void** peer_ptr);
+int jpt_peer_exchange_release(void* peer_ptr);
+/* 0: every wait of every launch so far was satisfied; 1: some launch gave up. */
+int jpt_peer_exchange_status(const void* own_buffer, void* stream);
+
+int jpt_kv_quant_append_dense_peers(const void* xk, const void* xv, int in_dtype,
+                                    int8_t* cache_k, int8_t* cache_v, void* k_scaler,
+                                    void* v_scaler, int8_t* k_quant, int8_t* v_quant,
+                                    void* k_scale, void* v_scale, const int32_t* pos,
+                                    int pos_count, int pos_host, int B, int H, int S,
+                                    int D, int64_t cs_b, int64_t cs_h, int64_t cs_s,
+                                    int64_t ss_b, int64_t ss_s,
+                                    const jpt_peer_exchange* px, void* stream);
+
+/*
  * Row scatter without quantisation, K and V in one launch:
  *   dst[l*ds_l + b*ds_b + h*ds_h + pos_b*ds_s + d] = src[((l*B + b)*H + h)*D + d]
  * Replaces KVCacheGenerate.update (jetstream_pt/cache_manager.py:227-293; NL=1)

@@ -27,6 +27,11 @@ c_void_p, c_int, c_i64, c_size_t, c_float = (
 )
 
 
+class PeerExchangeStruct(ctypes.Structure):
+  """Mirror of `struct jpt_peer_exchange` (include/jpt_b200.h)."""
+  _fields_ = [("rank", c_int), ("world", c_int), ("batch", c_int), ("buffers", c_void_p * 8)]
+
+
 class AttnParams(ctypes.Structure):
   """Mirror of `struct jpt_attn_params`."""
 
@@ -56,6 +61,16 @@ _SIGNATURES = {
     "jpt_kv_quant_append_dense": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 8
                                   + [c_void_p, c_int, c_int] + [c_int] * 4 + [c_i64] * 5
                                   + [c_void_p, c_void_p, c_void_p]),
+    "jpt_peer_exchange_bytes": (ctypes.c_size_t, [c_int, c_int]),
+    "jpt_peer_exchange_alloc": (c_int, [ctypes.c_size_t, ctypes.POINTER(c_void_p)]),
+    "jpt_peer_exchange_free": (c_int, [c_void_p]),
+    "jpt_peer_exchange_export": (c_int, [c_void_p, c_void_p]),
+    "jpt_peer_exchange_import": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "jpt_peer_exchange_release": (c_int, [c_void_p]),
+    "jpt_peer_exchange_status": (c_int, [c_void_p, c_void_p]),
+    "jpt_kv_quant_append_dense_peers": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 8
+                                        + [c_void_p, c_int, c_int] + [c_int] * 4 + [c_i64] * 5
+                                        + [c_void_p, c_void_p]),
     "jpt_kv_scatter_rows": (c_int, [c_void_p] * 4 + [c_int, c_void_p, c_int, c_int, c_int]
                             + [c_int] * 5 + [c_i64] * 4 + [c_void_p]),
     "jpt_kv_append_paged": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,

@@ -8,6 +8,8 @@ Cache layouts (unchanged from the reference): dense [B,H,S,D] or stacked
 """
 
 import numpy as np
+import ctypes
+
 import torch
 
 from jetstream_pytorch_b200 import _lib
@@ -237,7 +239,7 @@ class Int8KVCacheGenerate:
     vscaler = torch.ones(s_shape, dtype=torch.bfloat16, device=device)
     return cls(cache_k, cache_v, kscaler, vscaler, 0, None, env=env)
 
-  def _quant_append(self, xk, xv, cache_k, cache_v, k_scaler, v_scaler, outs=None, amax_in=None):
+  def _quant_append(self, xk, xv, cache_k, cache_v, k_scaler, v_scaler, outs=None, amax_in=None, peers=None):
     """Quantise the new token of every slot and (when a cache view is given)
     write codes and scale at this step's position: one launch for K and V."""
     b, h, t, d = xk.shape
@@ -263,10 +265,18 @@ class Int8KVCacheGenerate:
       cs = (cs_b, cs_h, cs_s)
       ss = (k_scaler.stride(0), k_scaler.stride(2))
       p, n, host, keep = _pos_args(self.input_pos, xk.device, b)
-    _lib.check(_lib.lib().jpt_kv_quant_append_dense(
-        _lib.ptr(xk), _lib.ptr(xv), _lib.dt(xk), _lib.ptr(cache_k), _lib.ptr(cache_v), _lib.ptr(k_scaler),
-        _lib.ptr(v_scaler), _lib.ptr(kq), _lib.ptr(vq), _lib.ptr(ks), _lib.ptr(vs), p, n, host, b, h, s, d,
-        cs[0], cs[1], cs[2], ss[0], ss[1], _lib.ptr(amax_in), None, _lib.stream()))
+    if peers is not None:
+      if amax_in is not None:
+        raise ValueError("give either the reduced amax or the peer exchange, not both")
+      _lib.check(_lib.lib().jpt_kv_quant_append_dense_peers(
+          _lib.ptr(xk), _lib.ptr(xv), _lib.dt(xk), _lib.ptr(cache_k), _lib.ptr(cache_v), _lib.ptr(k_scaler),
+          _lib.ptr(v_scaler), _lib.ptr(kq), _lib.ptr(vq), _lib.ptr(ks), _lib.ptr(vs), p, n, host, b, h, s, d,
+          cs[0], cs[1], cs[2], ss[0], ss[1], ctypes.byref(peers.struct), _lib.stream()))
+    else:
+      _lib.check(_lib.lib().jpt_kv_quant_append_dense(
+          _lib.ptr(xk), _lib.ptr(xv), _lib.dt(xk), _lib.ptr(cache_k), _lib.ptr(cache_v), _lib.ptr(k_scaler),
+          _lib.ptr(v_scaler), _lib.ptr(kq), _lib.ptr(vq), _lib.ptr(ks), _lib.ptr(vs), p, n, host, b, h, s, d,
+          cs[0], cs[1], cs[2], ss[0], ss[1], _lib.ptr(amax_in), None, _lib.stream()))
     del keep
     return kq, vq, ks, vs
 
@@ -293,19 +303,21 @@ class Int8KVCacheGenerate:
     kq, _, ks, _ = self._quant_append(x, x, None, None, None, None)
     return (kq.reshape(b, t, h, d).permute(0, 2, 1, 3).contiguous(), ks.reshape(b, t, 1, 1).permute(0, 2, 1, 3))
 
-  def update(self, xk, xv, layer_id: int, amax=None):
+  def update(self, xk, xv, layer_id: int, amax=None, peers=None):
     """cache_manager.py:539-582.  `amax` (float32 [2,B], optional) replaces the
     local per-token maxima when the KV heads are sharded across GPUs and the
     caller has max-reduced `local_amax` over the ranks (the reference gets the
-    same effect from GSPMD's all-reduce of the amax over the sharded head axis)."""
+    same effect from GSPMD's all-reduce of the amax over the sharded head axis).
+    `peers` (a `PeerAmaxExchange`, optional) does that reduction inside the
+    launch over NVLink peer memory instead: no `local_amax`, no collective."""
     env = self.env
     if env.lazy_cache_update:
       if env.new_cache_stacked:
         outs = (self.new_ks[layer_id], self.new_vs[layer_id], self.new_k_scaler[layer_id],
                 self.new_v_scaler[layer_id])
-        k_quant, v_quant, kscale, vscale = self._quant_append(xk, xv, None, None, None, None, outs, amax)
+        k_quant, v_quant, kscale, vscale = self._quant_append(xk, xv, None, None, None, None, outs, amax, peers)
       else:
-        k_quant, v_quant, kscale, vscale = self._quant_append(xk, xv, None, None, None, None, None, amax)
+        k_quant, v_quant, kscale, vscale = self._quant_append(xk, xv, None, None, None, None, None, amax, peers)
         if env.generate_cache_stacked:
           self.new_ks.append(k_quant)
           self.new_vs.append(v_quant)
@@ -320,12 +332,12 @@ class Int8KVCacheGenerate:
       # written here.
       k_quant, v_quant, kscale, vscale = self._quant_append(
           xk, xv, self.cache_k[layer_id], self.cache_v[layer_id], self.k_scaler[layer_id],
-          self.v_scaler[layer_id], None, amax)
+          self.v_scaler[layer_id], None, amax, peers)
     else:
       # ring buffer (one shared position) and left aligned (one per slot) differ
       # only in how many positions `input_pos` holds
       k_quant, v_quant, kscale, vscale = self._quant_append(
-          xk, xv, self.cache_k, self.cache_v, self.k_scaler, self.v_scaler, None, amax)
+          xk, xv, self.cache_k, self.cache_v, self.k_scaler, self.v_scaler, None, amax, peers)
     return (self.cache_k, self.cache_v, k_quant, v_quant, self.k_scaler, self.v_scaler, kscale, vscale)
 
   def finalize(self):
@@ -403,3 +415,67 @@ class PageKVCacheGenerate:
     k = torch.zeros(tuple(shape), dtype=dtype, device=device)
     v = torch.zeros(tuple(shape), dtype=dtype, device=device)
     return cls(k, v, None, None, None, env=env)
+
+
+class PeerAmaxExchange:
+  """Exchange buffers for the in-kernel max-reduction of the per-token amax
+  between the GPUs of one node that hold the KV heads of a cache
+  (`Int8KVCacheGenerate.update(..., peers=...)`).
+
+  Every rank allocates one small buffer, exports its CUDA IPC handle and opens
+  the handles of the others; `handles_all_gather(handle) -> [handle of rank 0,
+  ...]` is any host-side all-gather of 64-byte strings
+  (`PeerAmaxExchange.with_torch_distributed` uses the default process group).
+  All ranks must then make the same sequence of `update` calls."""
+
+  def __init__(self, batch_size, rank, world_size, handles_all_gather):
+    lib = _lib.lib()
+    self.rank, self.world = rank, world_size
+    nbytes = lib.jpt_peer_exchange_bytes(batch_size, world_size)
+    if nbytes == 0:
+      raise ValueError(f"peer exchange for batch {batch_size} on {world_size} ranks is not possible (1..8 ranks)")
+    own = ctypes.c_void_p()
+    _lib.check(lib.jpt_peer_exchange_alloc(nbytes, ctypes.byref(own)))
+    self._own = own
+    handle = ctypes.create_string_buffer(64)
+    _lib.check(lib.jpt_peer_exchange_export(own, handle))
+    handles = handles_all_gather(handle.raw)
+    self.struct = _lib.PeerExchangeStruct()
+    self.struct.rank, self.struct.world, self.struct.batch = rank, world_size, batch_size
+    self._opened = []
+    for r in range(world_size):
+      if r == rank:
+        self.struct.buffers[r] = own.value
+      else:
+        peer = ctypes.c_void_p()
+        _lib.check(lib.jpt_peer_exchange_import(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(peer)))
+        self._opened.append(peer)
+        self.struct.buffers[r] = peer.value
+
+  @classmethod
+  def with_torch_distributed(cls, batch_size):
+    import torch.distributed as dist
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+
+    def gather(h):
+      out = [None] * world
+      dist.all_gather_object(out, h)
+      return out
+
+    px = cls(batch_size, rank, world, gather)
+    dist.barrier()  # every rank has opened every buffer before anybody launches
+    return px
+
+  def status(self):
+    """0 while every wait of every launch was satisfied; 1 after a launch gave up on a peer."""
+    return _lib.lib().jpt_peer_exchange_status(self._own, _lib.stream())
+
+  def close(self):
+    lib = _lib.lib()
+    for p in self._opened:
+      lib.jpt_peer_exchange_release(p)
+    self._opened = []
+    if self._own is not None:
+      lib.jpt_peer_exchange_free(self._own)
+      self._own = None

@@ -43,6 +43,8 @@ namespace {
 // values are held in registers between the amax pass and the quantise pass
 // (NV vectors of VEC elements per thread).
 // ---------------------------------------------------------------------------
+constexpr int kMaxPeers = 8;
+
 struct QuantAppendArgs {
   const void* x[2];     // xk, xv
   int8_t* cache[2];     // may be null
@@ -60,7 +62,26 @@ struct QuantAppendArgs {
   int paged;
   int B, H, S, D, ps;
   int64_t cs_b, cs_h, cs_s, ss_b, ss_s;  // dense; paged uses cs_h = P*ps*D, cs_s = D
+  // Head-sharded caches: the partial amax of every rank travels through peer memory inside this launch.
+  unsigned long long* px_slots[kMaxPeers];  // slot area of each rank's exchange buffer (index = rank); null: off
+  unsigned* px_state;                       // this rank's {launches done, CTAs done, gave up}
+  int px_rank, px_world;
 };
+
+// Exchange buffer of one rank: kPeerStateBytes of state, then slots[parity][writer rank][2 B],
+// each slot one 64-bit word (launch number << 32 | amax bits) written with a single store,
+// so a reader sees either an older launch's word or the complete new one.
+constexpr size_t kPeerStateBytes = 64;
+constexpr long long kPeerWaitCycles = 1000000000ll;  // about half a second
+
+__device__ __forceinline__ void st_peer(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_peer(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
 
 template <typename T, int VEC>
 struct VecIO;
@@ -143,6 +164,37 @@ __global__ void __launch_bounds__(256) quant_append_kernel(QuantAppendArgs a) {
     }
   }
   amax = block_max(amax, red);
+  if (a.px_state) {
+    // All-ranks maximum over NVLink: thread 0 stores (launch number, partial amax) into every
+    // rank's buffer and then reads the words the other ranks stored into this rank's buffer.
+    __shared__ float s_amax;
+    if (threadIdx.x == 0) {
+      const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&a.px_state[0]) + 1u;
+      const int idx = which * a.B + slot;
+      const size_t row = (size_t)(epoch & 1u) * a.px_world;
+      const unsigned long long word = ((unsigned long long)epoch << 32) | __float_as_uint(amax);
+      for (int r = 0; r < a.px_world; ++r) st_peer(a.px_slots[r] + (row + a.px_rank) * (2 * a.B) + idx, word);
+      float m = amax;
+      const long long t0 = clock64();
+      for (int r = 0; r < a.px_world; ++r) {
+        if (r == a.px_rank) continue;
+        const unsigned long long* p = a.px_slots[a.px_rank] + (row + r) * (2 * a.B) + idx;
+        unsigned long long v = ld_peer(p);
+        while ((unsigned)(v >> 32) != epoch) {
+          if (clock64() - t0 > kPeerWaitCycles) {  // the peer never came: report, go on with what is there
+            atomicExch(&a.px_state[2], 1u);
+            v = 0;
+            break;
+          }
+          v = ld_peer(p);
+        }
+        m = fmaxf(m, __uint_as_float((unsigned)v));
+      }
+      s_amax = m;
+    }
+    __syncthreads();
+    amax = s_amax;
+  }
   if (a.amax_out) {  // phase one of a sharded update: publish the partial amax
     if (threadIdx.x == 0) a.amax_out[which * a.B + slot] = amax;
     return;
@@ -182,6 +234,15 @@ __global__ void __launch_bounds__(256) quant_append_kernel(QuantAppendArgs a) {
   if (threadIdx.x == 0) {
     if (a.scale_out[which]) static_cast<T*>(a.scale_out[which])[slot] = from_f32<T>(scale);
     if (write_cache && a.scaler[which]) static_cast<T*>(a.scaler[which])[scaler_idx] = from_f32<T>(scale);
+    if (a.px_state) {  // the last CTA of the launch advances the launch number for the next one
+      __threadfence();
+      const unsigned done = atomicAdd(&a.px_state[1], 1u);
+      if (done == gridDim.x * gridDim.y - 1) {
+        a.px_state[1] = 0;
+        __threadfence();
+        atomicAdd(&a.px_state[0], 1u);
+      }
+    }
   }
 }
 
@@ -348,6 +409,13 @@ extern "C" const char* jpt_last_error_string(void) { return last_error_buffer();
 extern "C" int jpt_version(void) { return 100; }
 extern "C" long long jpt_launch_count(void) { return launch_count(); }
 
+// Shared body of the dense entry points; px may be null.
+static int quant_append_dense(const void* xk, const void* xv, int in_dtype, int8_t* cache_k, int8_t* cache_v,
+                              void* k_scaler, void* v_scaler, int8_t* k_quant, int8_t* v_quant, void* k_scale,
+                              void* v_scale, const int32_t* pos, int pos_count, int pos_host, int B, int H, int S,
+                              int D, int64_t cs_b, int64_t cs_h, int64_t cs_s, int64_t ss_b, int64_t ss_s,
+                              const float* amax_in, float* amax_out, const jpt_peer_exchange* px, void* stream);
+
 extern "C" int jpt_kv_quant_append_dense(const void* xk, const void* xv, int in_dtype, int8_t* cache_k,
                                          int8_t* cache_v, void* k_scaler, void* v_scaler, int8_t* k_quant,
                                          int8_t* v_quant, void* k_scale, void* v_scale, const int32_t* pos,
@@ -355,28 +423,80 @@ extern "C" int jpt_kv_quant_append_dense(const void* xk, const void* xv, int in_
                                          int64_t cs_b, int64_t cs_h, int64_t cs_s, int64_t ss_b,
                                          int64_t ss_s, const float* amax_in, float* amax_out,
                                          void* stream) {
-  JPT_REQUIRE(xk && xv, JPT_EINVAL, "kv_quant_append_dense: null input");
-  JPT_REQUIRE(in_dtype == JPT_BF16 || in_dtype == JPT_F32, JPT_EINVAL,
-              "kv_quant_append_dense: input dtype must be bf16 or f32");
-  JPT_REQUIRE(B > 0 && H > 0 && D > 0 && S > 0, JPT_EINVAL, "kv_quant_append_dense: bad shape");
-  JPT_REQUIRE((cache_k == nullptr) == (cache_v == nullptr), JPT_EINVAL,
-              "kv_quant_append_dense: cache_k and cache_v must both be given or both be null");
-  JPT_REQUIRE(pos == nullptr || pos_count == 1 || pos_count == B, JPT_EINVAL,
-              "kv_quant_append_dense: pos_count must be 1 or B");
-  QuantAppendArgs a{};
-  a.x[0] = xk; a.x[1] = xv;
-  a.cache[0] = cache_k; a.cache[1] = cache_v;
-  a.scaler[0] = k_scaler; a.scaler[1] = v_scaler;
-  a.quant[0] = k_quant; a.quant[1] = v_quant;
-  a.scale_out[0] = k_scale; a.scale_out[1] = v_scale;
-  a.pos = pos; a.pos_count = pos_count; a.pos_host = pos_host;
-  a.amax_in = amax_in; a.amax_out = amax_out;
-  a.paged = 0;
-  a.B = B; a.H = H; a.S = S; a.D = D; a.ps = 0;
-  a.cs_b = cs_b; a.cs_h = cs_h; a.cs_s = cs_s; a.ss_b = ss_b; a.ss_s = ss_s;
+  return quant_append_dense(xk, xv, in_dtype, cache_k, cache_v, k_scaler, v_scaler, k_quant, v_quant, k_scale, v_scale,
+                            pos, pos_count, pos_host, B, H, S, D, cs_b, cs_h, cs_s, ss_b, ss_s, amax_in, amax_out,
+                            nullptr, stream);
+}
+
+extern "C" int jpt_kv_quant_append_dense_peers(const void* xk, const void* xv, int in_dtype, int8_t* cache_k,
+                                               int8_t* cache_v, void* k_scaler, void* v_scaler, int8_t* k_quant,
+                                               int8_t* v_quant, void* k_scale, void* v_scale, const int32_t* pos,
+                                               int pos_count, int pos_host, int B, int H, int S, int D,
+                                               int64_t cs_b, int64_t cs_h, int64_t cs_s, int64_t ss_b,
+                                               int64_t ss_s, const jpt_peer_exchange* px, void* stream) {
+  JPT_REQUIRE(px, JPT_EINVAL, "kv_quant_append_dense_peers: null exchange");
+  JPT_REQUIRE(px->world >= 1 && px->world <= kMaxPeers && px->rank >= 0 && px->rank < px->world, JPT_EINVAL,
+              "kv_quant_append_dense_peers: rank %d of %d", px->rank, px->world);
+  JPT_REQUIRE(px->batch == B, JPT_EINVAL, "kv_quant_append_dense_peers: buffers are sized for batch %d, not %d",
+              px->batch, B);
+  for (int r = 0; r < px->world; ++r)
+    JPT_REQUIRE(px->buffers[r] && aligned(px->buffers[r], 8), JPT_EINVAL,
+                "kv_quant_append_dense_peers: buffer of rank %d missing or unaligned", r);
+  return quant_append_dense(xk, xv, in_dtype, cache_k, cache_v, k_scaler, v_scaler, k_quant, v_quant, k_scale, v_scale,
+                            pos, pos_count, pos_host, B, H, S, D, cs_b, cs_h, cs_s, ss_b, ss_s, nullptr, nullptr, px,
+                            stream);
+}
+
+extern "C" size_t jpt_peer_exchange_bytes(int B, int world) {
+  if (B <= 0 || world <= 0 || world > kMaxPeers) return 0;
+  return kPeerStateBytes + (size_t)2 * world * 2 * B * sizeof(unsigned long long);
+}
+
+extern "C" int jpt_peer_exchange_alloc(size_t bytes, void** ptr) {
+  JPT_REQUIRE(ptr && bytes >= kPeerStateBytes, JPT_EINVAL, "peer_exchange_alloc: bad arguments");
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+  if (e != cudaSuccess) return fail((int)e, "peer_exchange_alloc: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+extern "C" int jpt_peer_exchange_free(void* ptr) {
+  const cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return fail((int)e, "peer_exchange_free: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+extern "C" int jpt_peer_exchange_export(void* ptr, void* handle64) {
+  JPT_REQUIRE(ptr && handle64, JPT_EINVAL, "peer_exchange_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  const cudaError_t e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), ptr);
+  if (e != cudaSuccess) return fail((int)e, "peer_exchange_export: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+extern "C" int jpt_peer_exchange_import(const void* handle64, void** peer_ptr) {
+  JPT_REQUIRE(handle64 && peer_ptr, JPT_EINVAL, "peer_exchange_import: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  const cudaError_t e = cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail((int)e, "peer_exchange_import: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+extern "C" int jpt_peer_exchange_release(void* peer_ptr) {
+  const cudaError_t e = cudaIpcCloseMemHandle(peer_ptr);
+  if (e != cudaSuccess) return fail((int)e, "peer_exchange_release: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+extern "C" int jpt_peer_exchange_status(const void* own_buffer, void* stream) {
+  JPT_REQUIRE(own_buffer, JPT_EINVAL, "peer_exchange_status: null buffer");
+  unsigned st3[3] = {0, 0, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return in_dtype == JPT_BF16 ? launch_quant_append<__nv_bfloat16>(a, B, st)
-                              : launch_quant_append<float>(a, B, st);
+  cudaError_t e = cudaMemcpyAsync(st3, own_buffer, sizeof(st3), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail((int)e, "peer_exchange_status: %s", cudaGetErrorString(e));
+  return (int)st3[2];
 }
 
 extern "C" int jpt_kv_scatter_rows(const void* src_k, const void* src_v, void* dst_k, void* dst_v,
@@ -464,3 +584,40 @@ extern "C" int jpt_page_token_indices(const int32_t* lens, const int32_t* page_i
       lens, page_indices, B, max_pages, ps, pti, n_active, new_lengths);
   return check_launch("page_token_indices_kernel");
 }
+
+static int quant_append_dense(const void* xk, const void* xv, int in_dtype, int8_t* cache_k, int8_t* cache_v,
+                              void* k_scaler, void* v_scaler, int8_t* k_quant, int8_t* v_quant, void* k_scale,
+                              void* v_scale, const int32_t* pos, int pos_count, int pos_host, int B, int H, int S,
+                              int D, int64_t cs_b, int64_t cs_h, int64_t cs_s, int64_t ss_b, int64_t ss_s,
+                              const float* amax_in, float* amax_out, const jpt_peer_exchange* px, void* stream) {
+  JPT_REQUIRE(xk && xv, JPT_EINVAL, "kv_quant_append_dense: null input");
+  JPT_REQUIRE(in_dtype == JPT_BF16 || in_dtype == JPT_F32, JPT_EINVAL,
+              "kv_quant_append_dense: input dtype must be bf16 or f32");
+  JPT_REQUIRE(B > 0 && H > 0 && D > 0 && S > 0, JPT_EINVAL, "kv_quant_append_dense: bad shape");
+  JPT_REQUIRE((cache_k == nullptr) == (cache_v == nullptr), JPT_EINVAL,
+              "kv_quant_append_dense: cache_k and cache_v must both be given or both be null");
+  JPT_REQUIRE(pos == nullptr || pos_count == 1 || pos_count == B, JPT_EINVAL,
+              "kv_quant_append_dense: pos_count must be 1 or B");
+  QuantAppendArgs a{};
+  a.x[0] = xk; a.x[1] = xv;
+  a.cache[0] = cache_k; a.cache[1] = cache_v;
+  a.scaler[0] = k_scaler; a.scaler[1] = v_scaler;
+  a.quant[0] = k_quant; a.quant[1] = v_quant;
+  a.scale_out[0] = k_scale; a.scale_out[1] = v_scale;
+  a.pos = pos; a.pos_count = pos_count; a.pos_host = pos_host;
+  a.amax_in = amax_in; a.amax_out = amax_out;
+  if (px) {
+    for (int r = 0; r < px->world; ++r)
+      a.px_slots[r] = reinterpret_cast<unsigned long long*>(static_cast<char*>(px->buffers[r]) + kPeerStateBytes);
+    a.px_state = static_cast<unsigned*>(px->buffers[px->rank]);
+    a.px_rank = px->rank;
+    a.px_world = px->world;
+  }
+  a.paged = 0;
+  a.B = B; a.H = H; a.S = S; a.D = D; a.ps = 0;
+  a.cs_b = cs_b; a.cs_h = cs_h; a.cs_s = cs_s; a.ss_b = ss_b; a.ss_s = ss_s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return in_dtype == JPT_BF16 ? launch_quant_append<__nv_bfloat16>(a, B, st)
+                              : launch_quant_append<float>(a, B, st);
+}
+

@@ -1,0 +1,112 @@
+"""The in-kernel NVLink max-reduction of the per-token amax (head-sharded int8 caches).
+
+One rank: the exchange machinery (launch numbers, parity, completion counter)
+against the plain update.  Two ranks (run when the box has two GPUs): each
+process owns half of the KV heads; codes and scales must equal the unsharded
+update bit for bit.  Nothing here waits without a limit: a rank that loses
+its peer goes on after about half a second and reports it through status().
+"""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+pytestmark = pytest.mark.gpu
+
+B, H, S, D, STEPS = 12, 8, 64, 128, 5
+
+
+def _inputs(step):
+  g = torch.Generator().manual_seed(500 + step)
+  xk = torch.randn(B, H, 1, D, generator=g).to(torch.bfloat16)
+  xv = (torch.randn(B, H, 1, D, generator=g) * 3).to(torch.bfloat16)
+  if step == 2:
+    xk[3] = 0  # an all-zero token: scale 0, codes 0
+  return xk, xv
+
+
+def _make_cache(heads, dev):
+  from jetstream_pytorch_b200.cache_manager import Int8KVCacheGenerate
+  from jetstream_pytorch_b200.environment import JetEngineEnvironment, JetEngineEnvironmentData
+
+  data = JetEngineEnvironmentData(batch_size=B, cache_sequence_length=S, num_layers=1, ring_buffer=False, testing=True,
+                                  cache_shape=(B, heads, S, D))
+  data.quant_config.enable_kv_quantization = True
+  env = JetEngineEnvironment(data, device=dev)
+  ck = torch.zeros((B, heads, S, D), dtype=torch.int8, device=dev)
+  cv = torch.zeros((B, heads, S, D), dtype=torch.int8, device=dev)
+  ks = torch.zeros((B, 1, S, 1), dtype=torch.bfloat16, device=dev)
+  vs = torch.zeros((B, 1, S, 1), dtype=torch.bfloat16, device=dev)
+  pos = torch.arange(B, dtype=torch.int32, device=dev) % S
+  return Int8KVCacheGenerate(ck, cv, ks, vs, pos, env=env), (ck, cv, ks, vs)
+
+
+def _run_steps(cache, lo, hi, dev, peers):
+  for step in range(STEPS):
+    xk, xv = _inputs(step)
+    cache.input_pos = ((torch.arange(B, dtype=torch.int32) + step) % S).to(dev)
+    cache.update(xk[:, lo:hi].contiguous().to(dev), xv[:, lo:hi].contiguous().to(dev), 0, peers=peers)
+  torch.cuda.synchronize(dev)
+
+
+def test_single_rank_exchange_equals_plain_update():
+  from jetstream_pytorch_b200.cache_manager import PeerAmaxExchange
+
+  dev = torch.device("cuda", 0)
+  plain, ref = _make_cache(H, dev)
+  _run_steps(plain, 0, H, dev, None)
+  fused, got = _make_cache(H, dev)
+  px = PeerAmaxExchange(B, 0, 1, lambda h: [h])
+  try:
+    _run_steps(fused, 0, H, dev, px)
+    assert px.status() == 0
+  finally:
+    px.close()
+  for a, b in zip(ref, got):
+    assert torch.equal(a, b)
+
+
+def _worker(rank, world, port, out_path):
+  import torch.distributed as dist
+
+  os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+  os.environ["NCCL_NVLS_ENABLE"] = "0"
+  torch.cuda.set_device(rank)
+  dev = torch.device("cuda", rank)
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  from jetstream_pytorch_b200.cache_manager import PeerAmaxExchange
+
+  hs = H // world
+  cache, got = _make_cache(hs, dev)
+  px = PeerAmaxExchange.with_torch_distributed(B)
+  _run_steps(cache, rank * hs, (rank + 1) * hs, dev, px)
+  status = px.status()
+  dist.barrier()  # nobody frees a buffer that a peer may still write to
+  px.close()
+  torch.save({"status": status, "tensors": [t.cpu() for t in got]}, f"{out_path}.{rank}")
+  dist.barrier()
+  dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_equal_the_unsharded_update(tmp_path):
+  import torch.multiprocessing as mp
+
+  world = 2
+  out = str(tmp_path / "rank")
+  mp.spawn(_worker, args=(world, 29600 + os.getpid() % 300, out), nprocs=world, join=True)
+  dev = torch.device("cuda", 0)
+  plain, ref = _make_cache(H, dev)
+  _run_steps(plain, 0, H, dev, None)
+  ref = [t.cpu() for t in ref]
+  hs = H // world
+  for rank in range(world):
+    res = torch.load(f"{out}.{rank}")
+    assert res["status"] == 0
+    ck, cv, ks, vs = res["tensors"]
+    assert torch.equal(ck, ref[0][:, rank * hs:(rank + 1) * hs])
+    assert torch.equal(cv, ref[1][:, rank * hs:(rank + 1) * hs])
+    assert torch.equal(ks, ref[2]) and torch.equal(vs, ref[3])
