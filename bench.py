@@ -187,6 +187,62 @@ def run_reference(args):
 # ---------------------------------------------------------------------------
 
 
+def run_insert_burst(args, dev):
+  """BASELINE config 4: 64 prefill inserts, each scattering and quantising a prefix of
+  L in {128..2048} tokens x 32 layers into pages of an int8 paged cache (batch 128,
+  page size 64).  The whole burst (2048 launches) replays as one CUDA graph; the line
+  reports the HBM rate of the fused quantise + scatter against its algorithmic bytes."""
+  import numpy as np
+  from jetstream_pytorch_b200.page_attention_manager import PageAttentionManager
+
+  nl, bi, ps, hk, maxp, n_ins = 32, 128, 64, HKV, 32, 64
+  pages = bi * maxp
+  rng = np.random.RandomState(1004)
+  lens = rng.choice([128, 256, 512, 1024, 2048], size=n_ins)
+  gen = torch.Generator(device=dev).manual_seed(1004)
+  pre = [(torch.randn((1, hk, 2048, D), generator=gen, device=dev).to(torch.bfloat16),
+          torch.randn((1, hk, 2048, D), generator=gen, device=dev).to(torch.bfloat16)) for _ in range(nl)]
+  pools = [(torch.zeros((hk, pages, ps, D), dtype=torch.int8, device=dev),
+            torch.zeros((hk, pages, ps, D), dtype=torch.int8, device=dev)) for _ in range(nl)]
+  scales = [(torch.zeros((1, pages, ps, 1), dtype=torch.bfloat16, device=dev),
+             torch.zeros((1, pages, ps, 1), dtype=torch.bfloat16, device=dev)) for _ in range(nl)]
+  pam = PageAttentionManager(bi, pages, ps, maxp, free_page_order=rng.permutation(pages))
+  plan = []
+  nbytes = 0
+  for j, L in enumerate(lens):
+    L = int(L)
+    n_pages, idx = pam.reserve_pages_insert(j, L)
+    plan.append((L, torch.as_tensor(np.asarray(idx), dtype=torch.int32, device=dev)))
+    nbytes += nl * (2 * L * hk * D * 2 + 2 * n_pages * ps * hk * D + 2 * n_pages * ps * 2)
+
+  def burst():
+    for L, upd in plan:
+      pam.insert_prefill_cache([(k[:, :, :L], v[:, :, :L]) for k, v in pre], pools, upd, decode_scales=scales)
+
+  burst()
+  torch.cuda.synchronize()
+  graph = torch.cuda.CUDAGraph()
+  with torch.cuda.graph(graph):
+    burst()
+  for _ in range(max(3, args.warmup)):
+    graph.replay()
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(args.steps):
+    graph.replay()
+  e1.record()
+  torch.cuda.synchronize()
+  ms = e0.elapsed_time(e1) / args.steps
+  peak, kind = peaks()
+  gbs = nbytes / (ms * 1e-3) / 1e9
+  print(json.dumps({"only": "insert", "workload": "64 inserts x 32 layers, L in {128,256,512,1024,2048}, int8 paged "
+                    "cache (batch 128, page 64, 8 kv heads, D=128), quantise on insert", "launches_per_burst": n_ins * nl,
+                    "tokens_per_burst": int(lens.sum()), "ms_per_burst": ms, "algorithmic_bytes": nbytes,
+                    "achieved_gbs": gbs, "peak": peak, "peak_kind": kind, "frac": gbs / peak,
+                    "inserts_per_s": n_ins / (ms * 1e-3)}), flush=True)
+
+
 def run_cuda(args):
   import torch.distributed as dist
 
@@ -209,6 +265,9 @@ def run_cuda(args):
   hkv, hq = HKV // world, HQ // world
   nl = args.layers
   lib = _lib.lib()
+  if args.only == "insert":
+    run_insert_burst(args, dev)
+    return
 
   # ---- device-resident state: every layer owns its cache (>> L2 in total)
   lens = make_lengths()
@@ -475,7 +534,7 @@ def main():
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--amax-exchange", choices=["peers", "nccl"], default="peers",
                   help="N > 1: how the per-token amax is max-reduced over the ranks")
-  ap.add_argument("--only", choices=["attention", "append"], default=None,
+  ap.add_argument("--only", choices=["attention", "append", "insert"], default=None,
                   help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
   ap.add_argument("--kv", choices=["int8", "bf16"], default="int8", help="with --only attention: cache dtype")
   ap.add_argument("--attn-kernel", choices=["auto", "mma"], default="auto",

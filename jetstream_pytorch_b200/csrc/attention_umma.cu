@@ -86,7 +86,7 @@ constexpr float kNoMax = -1.0e30f;  // "no logit seen yet": finite, far below an
 // kNoMax (finite), so exp2(old - new) and exp2(-inf - new) need no special case.
 template <int kRow>
 __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8], float (&alpha)[8], const float (&tm)[8],
-                                             const float (&xv)[8], float pscale, uint32_t p_base) {
+                                             const float (&xv)[8], float pscale, const uint32_t (&p_row)[8]) {
   if constexpr (kRow < 8) {
     const float mn = fmaxf(m_run[kRow], tm[kRow]);
     float al, p;
@@ -95,8 +95,8 @@ __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8
     alpha[kRow] = al;
     m_run[kRow] = mn;
     l_run[kRow] = l_run[kRow] * al + p;
-    store_levels<128 * kRow>(p_base ^ (uint32_t)(kRow << 4), __float2uint_rn(p * pscale));
-    softmax_rows<kRow + 1>(m_run, l_run, alpha, tm, xv, pscale, p_base);
+    store_levels<128 * kRow>(p_row[kRow], __float2uint_rn(p * pscale));
+    softmax_rows<kRow + 1>(m_run, l_run, alpha, tm, xv, pscale, p_row);
   }
 }
 __device__ __forceinline__ int tiles_u(int n) { return (n + kTileU - 1) / kTileU; }
@@ -177,12 +177,12 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// float <-> int keys with the same order, for redux.sync.max
-__device__ __forceinline__ int order_key(float x) {
-  const int i = __float_as_int(x);
-  return i ^ ((i >> 31) & 0x7fffffff);
+// maximum over the 32 lanes in one instruction
+__device__ __forceinline__ float warp_max(float x) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+  return r;
 }
-__device__ __forceinline__ float key_value(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_kernel(AttnArgs a, MmaScratch x, int* status) {
   // The swizzled tiles need a 1024-byte aligned base.  The array is declared
@@ -468,7 +468,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   const uint32_t q_desc_addr = smem_u32(&sm.qlev[0]), p_desc_addr = smem_u32(&sm.plev[0]);
   // this thread's byte of row r of the probability levels: ((tid / 16) ^ r) * 16 + tid % 16.
   // plev is 1024-byte aligned, so the XOR with r << 4 can be applied to the whole address.
-  const uint32_t p_base = smem_u32(&sm.plev[0]) + (tid & 15) + ((uint32_t)(tid >> 4) << 4);
+  uint32_t p_row[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+    p_row[r] = (smem_u32(&sm.plev[0]) + (tid & 15) + ((uint32_t)(tid >> 4) << 4)) ^ (uint32_t)(r << 4);
 
   // Query levels of the piece that starts with the tile in `st` (when it
   // starts one), then S^T of that tile on the tensor core.  Called by the whole
@@ -535,8 +538,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     const float oscale = cmax * (1.f / 16777215.f);
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-      const float t = (float)(int)o01[r] + 256.f * (float)(int)o01[8 + r] + 65536.f * (float)(int)o2[r];
-      o[r] = o[r] * alpha[r] + t * oscale;
+      const float t01 = (float)((int)o01[r] + ((int)o01[8 + r] << 8));
+      o[r] = fmaf(o[r], alpha[r], fmaf((float)(int)o2[r], oscale * 65536.f, t01 * oscale));
     }
   };
 
@@ -584,11 +587,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
         tmem_ld8(tmem_lane + kColO + 16, o2);
         tmem_ld16(tmem_lane, s);
         tmem_ld_wait();
-        const float oscale = cmax_prev * (1.f / 16777215.f);
+        const float oscale = cmax_prev * (1.f / 16777215.f), oscale2 = oscale * 65536.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-          const float t = (float)(int)o01[r] + 256.f * (float)(int)o01[8 + r] + 65536.f * (float)(int)o2[r];
-          o[r] = o[r] * alpha_prev[r] + t * oscale;
+          // levels 0 and 1 combine exactly in int32 (|O_0 + 256 O_1| < 2^31)
+          const float t01 = (float)((int)o01[r] + ((int)o01[8 + r] << 8));
+          o[r] = fmaf(o[r], alpha_prev[r], fmaf((float)(int)o2[r], oscale2, t01 * oscale));
         }
         pending = false;
       } else {
@@ -611,16 +615,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     }
     // tile maxima per row (and the largest V scale) across the 128 tokens
     {
-      int key[9];
+      float wm[9];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) key[r] = __reduce_max_sync(0xffffffffu, order_key(xv[r]));
-      key[8] = __reduce_max_sync(0xffffffffu, order_key(cvs));
+      for (int r = 0; r < 8; ++r) wm[r] = warp_max(xv[r]);
+      wm[8] = warp_max(cvs);
       if (lane == 0) {
-        *reinterpret_cast<float4*>(&sm.xch[warp][0]) =
-            make_float4(key_value(key[0]), key_value(key[1]), key_value(key[2]), key_value(key[3]));
-        *reinterpret_cast<float4*>(&sm.xch[warp][4]) =
-            make_float4(key_value(key[4]), key_value(key[5]), key_value(key[6]), key_value(key[7]));
-        sm.xch[warp][8] = key_value(key[8]);
+        *reinterpret_cast<float4*>(&sm.xch[warp][0]) = make_float4(wm[0], wm[1], wm[2], wm[3]);
+        *reinterpret_cast<float4*>(&sm.xch[warp][4]) = make_float4(wm[4], wm[5], wm[6], wm[7]);
+        sm.xch[warp][8] = wm[8];
       }
     }
     tc_fence_before();
@@ -648,7 +650,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       // p <= 1 and the ratio is held at 1 (the fast division may land one ulp above), so
       // the product stays below 2^24 without a clamp per row
       const float pscale = cmax > 0.f ? fminf(__fdividef(cvs, cmax), 1.f) * 16777215.f : 0.f;
-      softmax_rows<0>(m_run, l_run, alpha, tm, xv, pscale, p_base);
+      softmax_rows<0>(m_run, l_run, alpha, tm, xv, pscale, p_row);
     }
     fence_async_smem();
     __syncthreads();
