@@ -126,11 +126,31 @@ static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int
   float acc[kMaxRows];
 #pragma unroll
   for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
-  for (int pi = 0; pi < parts; ++pi) {
-    const float* src = x.part_o + (((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows) * kD + tid;
+  if (R <= 8) {
+    // two pieces per step: 16 independent loads in flight instead of one L2 round trip per piece
+    for (int pi = 0; pi < parts; pi += 2) {
+      const bool two = pi + 1 < parts;
+      const float* s0 = x.part_o + (((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows) * kD + tid;
+      const float* s1 = x.part_o + (((int64_t)(first + pi + 1) * 2) * kMaxRows) * kD + tid;
+      float v0[8], v1[8];
 #pragma unroll
-    for (int r = 0; r < kMaxRows; ++r) {
-      if (r < R) acc[r] += s_w[pi * kMaxRows + r] * __ldcg(src + r * kD);
+      for (int r = 0; r < 8; ++r) {
+        v0[r] = r < R ? __ldcg(s0 + r * kD) : 0.f;
+        v1[r] = (two && r < R) ? __ldcg(s1 + r * kD) : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        acc[r] += s_w[pi * kMaxRows + r] * v0[r];
+        if (two) acc[r] += s_w[(pi + 1) * kMaxRows + r] * v1[r];
+      }
+    }
+  } else {
+    for (int pi = 0; pi < parts; ++pi) {
+      const float* src = x.part_o + (((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows) * kD + tid;
+#pragma unroll
+      for (int r = 0; r < kMaxRows; ++r) {
+        if (r < R) acc[r] += s_w[pi * kMaxRows + r] * __ldcg(src + r * kD);
+      }
     }
   }
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);

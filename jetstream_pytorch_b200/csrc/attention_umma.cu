@@ -43,6 +43,10 @@ constexpr int kStagesU = 2;     // K/V ring depth
 constexpr int kTmemCols = 64;   // S^T: columns 0..15, O^T: columns 16..47
 constexpr int kColO = 16;
 constexpr int kCtasPerSm = 3;
+#ifndef JPT_PIECE_COST_U
+#define JPT_PIECE_COST_U 1
+#endif
+constexpr int kPieceCostU = JPT_PIECE_COST_U;  // overhead slots charged per segment, in 128-token tiles
 constexpr long long kWaitCycles = 1000000000ll;  // about half a second: far beyond any wait of a healthy run
 
 struct __align__(1024) SmemU {
@@ -100,7 +104,7 @@ __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8
   }
 }
 __device__ __forceinline__ int tiles_u(int n) { return (n + kTileU - 1) / kTileU; }
-__device__ __forceinline__ int slots_u(int n) { return n > 0 ? tiles_u(n) + kPieceCost : 0; }
+__device__ __forceinline__ int slots_u(int n) { return n > 0 ? tiles_u(n) + kPieceCostU : 0; }
 
 // Byte offset of (row, byte) in a tile of 128-byte rows with 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz(int row, int byte) {
@@ -184,6 +188,22 @@ __device__ __forceinline__ float warp_max(float x) {
   return r;
 }
 
+#ifdef JPT_UMMA_SPANS
+// Debug builds only: per CTA, nanosecond stamps of the phases of its life.
+__device__ unsigned long long g_umma_spans[1024 * 8];
+__device__ __forceinline__ unsigned long long gtimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define JPT_SPAN(k)                                                                    \
+  do {                                                                                 \
+    if (threadIdx.x == 0 && blockIdx.x < 1024) g_umma_spans[8 * blockIdx.x + (k)] = gtimer_ns(); \
+  } while (0)
+#else
+#define JPT_SPAN(k) do {} while (0)
+#endif
+
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_kernel(AttnArgs a, MmaScratch x, int* status) {
   // The swizzled tiles need a 1024-byte aligned base.  The array is declared
   // with that alignment (and used in place, so that every access compiles to a
@@ -199,6 +219,26 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   const int R = a.R;
   const bool quant = a.k_scale != nullptr;
   const int cta = blockIdx.x;
+#ifdef JPT_UMMA_SPANS
+  if (threadIdx.x == 0 && blockIdx.x < 1024)
+    for (int z = 0; z < 8; ++z) g_umma_spans[8 * blockIdx.x + z] = 0;
+#endif
+  JPT_SPAN(0);
+
+  // ------------------------------------------------------------------ barriers and tensor memory
+  // (warp 1; warp 0 is busy with the scan below, the barriers of the schedule publish the result)
+  if (tid == 32) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[1])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
 
   // ------------------------------------------------------------------ schedule
   // Slots per sequence (tiles + overhead) -> exclusive prefix over sequences;
@@ -260,38 +300,36 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       }
     }
   }
-  // Rows of empty sequences are nobody's tile: sequence b is cleared by CTA b mod grid.
-  for (int b = cta; b < a.B; b += gridDim.x) {
-    int ua;
-    if (seq_range_x(a, x, b, &ua).n == 0) {
-      const int64_t r0 = (int64_t)b * a.Hkv * R;
-      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
-      for (int i = tid; i < a.Hkv * R * kD; i += kThreads) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
-      for (int i = tid; i < a.Hkv * R; i += kThreads) {
-        if (a.m) a.m[r0 + i] = -INFINITY;
-        if (a.l) a.l[r0 + i] = 0.f;
-      }
-    }
-  }
-  __syncthreads();  // sm.start visible; last reads of `scan` done
-  if (G0 >= G1) return;
-
-  // ------------------------------------------------------------------ barriers and tensor memory
-  if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[0])));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[1])));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
-                 "r"((uint32_t)kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
+  __syncthreads();  // sm.start and the tensor-memory address visible; last reads of `scan` done
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  JPT_SPAN(1);
+  // Rows of empty sequences are nobody's tile: sequence b is cleared by CTA b mod grid
+  // (at the end of the CTA's life, off the path to its first tile).
+  auto clear_empty_rows = [&]() {
+    for (int b = cta; b < a.B; b += gridDim.x) {
+      int ua;
+      if (seq_range_x(a, x, b, &ua).n == 0) {
+        const int64_t r0 = (int64_t)b * a.Hkv * R;
+        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
+        for (int i = tid; i < a.Hkv * R * kD; i += kThreads) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
+        for (int i = tid; i < a.Hkv * R; i += kThreads) {
+          if (a.m) a.m[r0 + i] = -INFINITY;
+          if (a.l) a.l[r0 + i] = 0.f;
+        }
+      }
+    }
+  };
+  if (G0 >= G1) {  // no tile for this CTA
+    clear_empty_rows();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemCols) : "memory");
+    }
+    return;
+  }
+  JPT_SPAN(2);
   const uint32_t tmem_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
 
   const int8_t* kbase = static_cast<const int8_t*>(a.k);
@@ -342,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     if (ppos >= a.S) ppos -= a.S;
     if (++pt < pT) return;
     pt = 0;
-    pslot += kPieceCost;  // the overhead slots of the next segment
+    pslot += kPieceCostU;  // the overhead slots of the next segment
     if (++ph == a.Hkv) {
       ph = 0;
       do {
@@ -359,11 +397,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   {
     load_seq();
     const int v0 = sm.start[2];  // slot inside the segment: overhead slots come first
-    if (v0 < kPieceCost) {
-      pslot += kPieceCost - v0;
+    if (v0 < kPieceCostU) {
+      pslot += kPieceCostU - v0;
       pt = 0;
     } else {
-      pt = v0 - kPieceCost;
+      pt = v0 - kPieceCostU;
     }
     seg_setup();
   }
@@ -553,6 +591,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   tc_fence_before();
   __syncthreads();
   TileMeta mt = sm.meta[0];
+  JPT_SPAN(3);
   if (mt.t >= 0) prepare(0, mt, true);
 
   float alpha_prev[8], cmax_prev = 0.f;
@@ -737,11 +776,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     mt = sm.meta[next_stage];
     if (mt.t >= 0) prepare(next_stage, mt, false);
     stage = next_stage;
+    if (i == 0) JPT_SPAN(4);
+#ifdef JPT_UMMA_SPANS
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {
+      g_umma_spans[8 * blockIdx.x + 6] += 1;                                  // tiles
+      if (i == 0 || sm.meta[stage ^ 1].t >= 0) g_umma_spans[8 * blockIdx.x + 7] += (mt.t == 0);  // pieces started after the first
+    }
+#endif
   }
+  JPT_SPAN(5);
+  clear_empty_rows();
   cp_async_wait<0>();
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemCols) : "memory");
   }
 }
@@ -787,3 +835,9 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
 }
 
 }  // namespace jpt
+
+#ifdef JPT_UMMA_SPANS
+extern "C" int jpt_debug_umma_spans(unsigned long long* out_host, int n_ctas) {
+  return (int)cudaMemcpyFromSymbol(out_host, jpt::g_umma_spans, sizeof(unsigned long long) * 8 * n_ctas);
+}
+#endif
