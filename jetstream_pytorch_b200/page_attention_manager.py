@@ -16,6 +16,50 @@ import torch
 from jetstream_pytorch_b200 import _lib
 
 
+def _layer_strides(prefill_caches, decode_caches, decode_scales):
+  """(prefix, pool, scale-pool) layer strides in elements when every layer's
+  tensors are same-shaped views at a constant address step (so that one launch
+  can serve all layers), else None."""
+  n = len(prefill_caches)
+  if n < 2 or len(decode_caches) != n or (decode_scales is not None and len(decode_scales) != n):
+    return None
+
+  def step(tensors):
+    t0 = tensors[0]
+    if not t0.is_cuda:
+      return None
+    for t in tensors:
+      if t.shape != t0.shape or t.dtype != t0.dtype or t.stride() != t0.stride():
+        return None
+    d = tensors[1].data_ptr() - t0.data_ptr()
+    if d <= 0 or d % t0.element_size():
+      return None
+    for i, t in enumerate(tensors):
+      if t.data_ptr() - t0.data_ptr() != i * d:
+        return None
+    return d // t0.element_size()
+
+  pk = [c[0] for c in prefill_caches]
+  pv = [c[1] for c in prefill_caches]
+  ck = [c[0] for c in decode_caches]
+  cv = [c[1] for c in decode_caches]
+  if pk[0].stride(-1) != 1 or pv[0].stride() != pk[0].stride() or not ck[0].is_contiguous() or not cv[0].is_contiguous():
+    return None
+  sp, sv, sc, scv = step(pk), step(pv), step(ck), step(cv)
+  if sp is None or sp != sv or sc is None or sc != scv:
+    return None
+  ss = 0
+  if decode_scales is not None:
+    ks = [c[0] for c in decode_scales]
+    vs = [c[1] for c in decode_scales]
+    if ks[0] is None:
+      return None
+    ss, ssv = step(ks), step(vs)
+    if ss is None or ss != ssv:
+      return None
+  return sp, sc, ss
+
+
 class PageAttentionManager:
   """Manages page blocks: reserve pages for prefill insert and decode, hand the
   page/token indices of a decode step to the cache, move prefill caches into
@@ -140,6 +184,18 @@ class PageAttentionManager:
     dev = decode_caches[0][0].device
     upd = _lib.as_i32(update_indexes, dev).contiguous()
     n_pages = upd.numel()
+    stacked = _layer_strides(prefill_caches, decode_caches, decode_scales)
+    if stacked is not None:
+      # the layers lie at a constant stride (views of stacked tensors): one launch for all of them
+      ps_l, cs_l, ss_l = stacked
+      (pk, pv), (ck, cv) = prefill_caches[0], decode_caches[0]
+      h, p, ps, d = ck.shape
+      ks, vs = decode_scales[0] if decode_scales is not None else (None, None)
+      _lib.check(_lib.lib().jpt_prefill_insert_paged(
+          _lib.ptr(pk), _lib.ptr(pv), _lib.dt(pk), _lib.ptr(ck), _lib.ptr(cv), _lib.dt(ck), _lib.ptr(ks),
+          _lib.ptr(vs), _lib.ptr(upd), n_pages, len(prefill_caches), h, pk.shape[2], p, ps, d, ps_l, pk.stride(1),
+          pk.stride(2), cs_l, ss_l, _lib.stream()))
+      return decode_caches
     for i, ((pk, pv), (ck, cv)) in enumerate(zip(prefill_caches, decode_caches)):
       h, p, ps, d = ck.shape
       _, hp, l, dp = pk.shape

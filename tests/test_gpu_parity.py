@@ -426,6 +426,47 @@ def test_paged_int8_extension_insert_and_append_exact():
 # ---------------------------------------------------------------------------
 
 
+@pytest.mark.parametrize("int8", [False, True])
+def test_paged_insert_of_stacked_layers_is_one_launch_with_the_same_result(int8):
+  """Layers that are views of stacked tensors go through one launch
+  (jpt_prefill_insert_paged with NL layers); separately allocated layers take a
+  launch each.  Pools and scale pools must come out identical."""
+  from jetstream_pytorch_b200 import _lib
+  from jetstream_pytorch_b200.page_attention_manager import PageAttentionManager
+
+  nl, h, pages, ps, d, length = 3, 4, 12, 16, 128, 37
+  g = torch.Generator().manual_seed(77)
+  pre_k = cu(torch.randn(nl, 1, h, length, d, generator=g).to(torch.bfloat16))
+  pre_v = cu(torch.randn(nl, 1, h, length, d, generator=g).to(torch.bfloat16))
+  dt = torch.int8 if int8 else torch.bfloat16
+  results = []
+  for stacked in (True, False):
+    if stacked:
+      pk, pv = torch.zeros((nl, h, pages, ps, d), dtype=dt, device="cuda"), torch.zeros((nl, h, pages, ps, d), dtype=dt, device="cuda")
+      sk, sv = (torch.zeros((nl, 1, pages, ps, 1), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+      pools = [(pk[i], pv[i]) for i in range(nl)]
+      scales = [(sk[i], sv[i]) for i in range(nl)]
+    else:
+      pools = [(torch.zeros((h, pages, ps, d), dtype=dt, device="cuda"), torch.zeros((h, pages, ps, d), dtype=dt, device="cuda"))
+               for _ in range(nl)]
+      scales = [(torch.zeros((1, pages, ps, 1), dtype=torch.bfloat16, device="cuda"),
+                 torch.zeros((1, pages, ps, 1), dtype=torch.bfloat16, device="cuda")) for _ in range(nl)]
+    pam = PageAttentionManager(4, pages, ps, 4)
+    _, idx = pam.reserve_pages_insert(1, length)
+    before = _lib.lib().jpt_launch_count()
+    pam.insert_prefill_cache([(pre_k[i], pre_v[i]) for i in range(nl)], pools, idx, decode_scales=scales if int8 else None)
+    torch.cuda.synchronize()
+    results.append((_lib.lib().jpt_launch_count() - before, pools, scales))
+  (n_one, pools_a, scales_a), (n_many, pools_b, scales_b) = results
+  assert n_one == 1 and n_many == nl
+  for (ka, va), (kb, vb) in zip(pools_a, pools_b):
+    assert torch.equal(ka, kb) and torch.equal(va, vb)
+  if int8:
+    for (ka, va), (kb, vb) in zip(scales_a, scales_b):
+      assert torch.equal(ka, kb) and torch.equal(va, vb)
+    assert pools_a[1][0].abs().max() > 0
+
+
 @pytest.mark.parametrize("quant", [False, True])
 def test_dense_insert_no_wrap_and_wrap_match_oracle(quant):
   from jetstream_pytorch_b200.insert import insert_dense
