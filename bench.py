@@ -510,10 +510,13 @@ def run_cuda(args):
                  f"({2 * B * hkv * S * D * nl / 2**30:.1f} GiB per GPU in total, >> 126 MB L2)",
                  "cuda_graph": graph is not None},
       "us_per_layer": ms_step * 1e3 / nl,
-      "roofline": {"bound": "hbm", "kernel": "flash_decode (+ split-K merge)", "achieved": achieved, "peak": peak,
+      "roofline": {"bound": "hbm", "kernel": "flash_decode_i8_umma_kernel (tcgen05; pieces merged in-kernel)", "achieved": achieved, "peak": peak,
                    "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                    "frac_of_8000_nominal": achieved / 8000.0, "algorithmic_bytes_per_launch": a_bytes,
-                   "us_per_launch": ms_attn * 1e3, "traffic": None},
+                   "us_per_launch": ms_attn * 1e3,
+                   # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload on one GPU
+                   # (ncu capture summarised in profiles/flash_decode_i8_umma__ragged_llama2_70b_b96_s2048.md)
+                   "traffic": 194.54e6 if world == 1 else None},
       "kernels": {"kv_quant_append": {"us_per_launch": ms_app * 1e3, "algorithmic_bytes": append_bytes(hkv),
                                       "achieved_gbs": app_gbs}},
       "e2e": {"value": B / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
