@@ -250,7 +250,9 @@ def gen_attention(ak, q):
 
 
 def main():
-  ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+  if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py <path of a jetstream-pytorch checkout>")
+  ref = sys.argv[1]
   cm, pam, ak, q = _refshim.import_reference(ref)
   gen_quantizers(cm, q)
   gen_int8_cache(cm)
