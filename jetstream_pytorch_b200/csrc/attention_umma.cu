@@ -239,6 +239,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     tc_fence_before();
   }
+  // Up to here nothing of global memory was touched: with a programmatic launch all of
+  // it ran under the kernel before this one (the append of the new token).
+  grid_dependency_wait();
+  grid_dependency_trigger();
 
   // ------------------------------------------------------------------ schedule
   // Slots per sequence (tiles + overhead) -> exclusive prefix over sequences;
@@ -830,7 +834,7 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   if (a.mask_mode == JPT_MASK_ADD) {
     if (int rc = launch_mask_ranges(a, x, st)) return rc;
   }
-  flash_decode_i8_umma_kernel<<<lay.num_ctas, kThreads, smem_bytes, st>>>(a, x, status);
+  launch_after_previous(flash_decode_i8_umma_kernel, dim3(lay.num_ctas), dim3(kThreads), smem_bytes, st, a, x, status);
   return check_launch("flash_decode_i8_umma_kernel");
 }
 

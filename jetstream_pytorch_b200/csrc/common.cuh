@@ -119,4 +119,36 @@ __device__ __forceinline__ int8_t insert_code(float x, float recip) {
   return (int8_t)(int)t;
 }
 
+// Programmatic dependent launch: a kernel launched with launch_after_previous()
+// may start (CTA launch ramp, set-up that touches no global data) while the
+// kernel before it in the stream is still running; grid_dependency_wait() blocks
+// until that kernel has completed and its writes are visible, and is a no-op for
+// an ordinary launch.  grid_dependency_trigger() lets the kernel after this one
+// start the same way.  The attribute is left out while the stream is being captured into a
+// graph, and with JPT_NO_PDL=1 in the environment.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_previous(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                         Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  // Inside a CUDA graph the launch gaps are already short and the early start measured slower
+  // (59.1 against 57.0 us per decode layer); eager launches gain from it (12 % end to end).
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) capturing = cudaStreamCaptureStatusNone;
+  cfg.numAttrs = (pdl_enabled() && capturing == cudaStreamCaptureStatusNone) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace jpt

@@ -2,6 +2,7 @@
 // paged), plain row scatter (bf16 / fp32 append and lazy finalize), and the
 // device-side page/token index walk.
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include <atomic>
 
@@ -24,6 +25,14 @@ int fail(int code, const char* fmt, ...) {
 
 static std::atomic<long long> g_launches{0};
 long long launch_count() { return g_launches.load(); }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("JPT_NO_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
 
 int check_launch(const char* what) {
   g_launches.fetch_add(1);
@@ -137,6 +146,8 @@ __device__ __forceinline__ void store_codes(int8_t* p, const int8_t (&c)[VEC]) {
 template <typename T, int VEC, int NV>
 __global__ void __launch_bounds__(256) quant_append_kernel(QuantAppendArgs a) {
   __shared__ float red[33];
+  grid_dependency_wait();     // the new token may come from the kernel before this one
+  grid_dependency_trigger();  // the attention launch that follows may set itself up meanwhile
   const int item = blockIdx.x, which = blockIdx.y;
   const int HD = a.H * a.D;
   int slot, page = 0, tok = 0;
@@ -258,14 +269,14 @@ int launch_quant_append(const QuantAppendArgs& a, int items, cudaStream_t st) {
     const int nvec = HD / 16;
     if (nvec <= 256) {
       int threads = ((nvec + 31) / 32) * 32;
-      quant_append_kernel<T, 16, 1><<<grid, threads, 0, st>>>(a);
+      launch_after_previous(quant_append_kernel<T, 16, 1>, grid, dim3(threads), 0, st, a);
     } else {
-      quant_append_kernel<T, 16, 2><<<grid, 256, 0, st>>>(a);
+      launch_after_previous(quant_append_kernel<T, 16, 2>, grid, dim3(256), 0, st, a);
     }
   } else {
     JPT_REQUIRE(HD <= 256 * 32, JPT_ERANGE, "quant_append: H*D = %d too large for the scalar path", HD);
     int threads = HD < 256 ? ((HD + 31) / 32) * 32 : 256;
-    quant_append_kernel<T, 1, 32><<<grid, threads, 0, st>>>(a);
+    launch_after_previous(quant_append_kernel<T, 1, 32>, grid, dim3(threads), 0, st, a);
   }
   return check_launch("quant_append_kernel");
 }
