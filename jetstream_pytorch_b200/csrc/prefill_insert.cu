@@ -140,6 +140,59 @@ __global__ void __launch_bounds__(256) insert_quant_kernel(InsertArgs a) {
   if (threadIdx.x == 0 && scaler) scaler[dst.sidx] = from_f32<T>(scale);
 }
 
+// The same work with one warp per token (8 tokens per CTA) and NVW 16-element
+// vectors per lane: the maximum stays inside the warp (no shared memory, no
+// block barrier) and every lane has NVW independent loads in flight.  Used
+// when H*D is a multiple of 512.
+template <typename T, int NVW>
+__global__ void __launch_bounds__(256) insert_quant_warp_kernel(InsertArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp, which = blockIdx.y, l = blockIdx.z;
+  if (t >= a.Ltot) return;
+  const Dest dst = resolve(a, l, t);
+  int8_t* cache = static_cast<int8_t*>(a.cache[which]);
+  T* scaler = static_cast<T*>(a.scaler[which]);
+  if (t >= a.L) {  // page tail: code 0, scale 0
+    if (!dst.ok) return;
+#pragma unroll
+    for (int n = 0; n < NVW; ++n) {
+      const int e = (n * 32 + lane) * 16;
+      const int h = e / a.D, d = e - h * a.D;
+      *reinterpret_cast<uint4*>(cache + dst.row0 + h * dst.hstep + d) = make_uint4(0, 0, 0, 0);
+    }
+    if (lane == 0 && scaler) scaler[dst.sidx] = from_f32<T>(0.f);
+    return;
+  }
+  const T* src = static_cast<const T*>(a.prefix[which]) + l * a.ps_l + (int64_t)t * a.ps_t;
+  float v[NVW][16];
+  float amax = 0.f;
+#pragma unroll
+  for (int n = 0; n < NVW; ++n) {
+    const int e = (n * 32 + lane) * 16;
+    const int h = e / a.D, d = e - h * a.D;
+    load_vec<T, 16>(src + h * a.ps_h + d, v[n]);
+  }
+#pragma unroll
+  for (int n = 0; n < NVW; ++n)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[n][i]));
+#pragma unroll
+  for (int sh = 16; sh >= 1; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+  const float scale = insert_scale<T>(amax);
+  const float recip = insert_recip<T>(scale);
+  if (!dst.ok) return;
+#pragma unroll
+  for (int n = 0; n < NVW; ++n) {
+    const int e = (n * 32 + lane) * 16;
+    const int h = e / a.D, d = e - h * a.D;
+    int8_t c[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) c[i] = insert_code<T>(v[n][i], recip);
+    *reinterpret_cast<uint4*>(cache + dst.row0 + h * dst.hstep + d) = *reinterpret_cast<const uint4*>(c);
+  }
+  if (lane == 0 && scaler) scaler[dst.sidx] = from_f32<T>(scale);
+}
+
 // Same-dtype copy: one thread per chunk of `chunk` bytes.
 __global__ void insert_copy_kernel(InsertArgs a, int elem_bytes, int chunk) {
   const int which = blockIdx.y, l = blockIdx.z;
@@ -180,6 +233,13 @@ int launch_quant(const InsertArgs& a, cudaStream_t st) {
                 a.cs_l % 16 == 0 && a.cs_b % 16 == 0 && a.cs_h % 16 == 0 && a.cs_s % 16 == 0;
   for (int w = 0; w < a.ntensors; ++w) vec_ok = vec_ok && aligned(a.prefix[w], 16) && aligned(a.cache[w], 16);
   dim3 grid(a.Ltot, a.ntensors, a.NL);
+  if (vec_ok && (HD == 512 || HD == 1024 || HD == 2048)) {
+    const dim3 wgrid((a.Ltot + 7) / 8, a.ntensors, a.NL);
+    if (HD == 512) insert_quant_warp_kernel<T, 1><<<wgrid, 256, 0, st>>>(a);
+    else if (HD == 1024) insert_quant_warp_kernel<T, 2><<<wgrid, 256, 0, st>>>(a);
+    else insert_quant_warp_kernel<T, 4><<<wgrid, 256, 0, st>>>(a);
+    return check_launch("insert_quant_warp_kernel");
+  }
   if (vec_ok && HD <= 16 * 256 * 2) {
     const int nvec = HD / 16;
     if (nvec <= 256) {
