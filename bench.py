@@ -196,7 +196,7 @@ def run_insert_burst(args, dev):
   from jetstream_pytorch_b200 import _lib
   from jetstream_pytorch_b200.page_attention_manager import PageAttentionManager
 
-  nl, bi, ps, hk, maxp, n_ins = 32, 128, 64, HKV, 32, 64
+  nl, bi, ps, hk, maxp, n_ins = min(32, args.layers), 128, 64, HKV, 32, 64  # --layers below 32 shrinks the case (profiling)
   pages = bi * maxp
   rng = np.random.RandomState(1004)
   lens = rng.choice([128, 256, 512, 1024, 2048], size=n_ins)
@@ -243,7 +243,7 @@ def run_insert_burst(args, dev):
   ms = e0.elapsed_time(e1) / args.steps
   peak, kind = peaks()
   gbs = nbytes / (ms * 1e-3) / 1e9
-  print(json.dumps({"only": "insert", "workload": "64 inserts x 32 layers, L in {128,256,512,1024,2048}, int8 paged "
+  print(json.dumps({"only": "insert", "layers": nl, "workload": "64 inserts x 32 layers (or --layers), L in {128,256,512,1024,2048}, int8 paged "
                     "cache (batch 128, page 64, 8 kv heads, D=128), quantise on insert", "launches_per_burst": int(launches),
                     "tokens_per_burst": int(lens.sum()), "ms_per_burst": ms, "algorithmic_bytes": nbytes,
                     "achieved_gbs": gbs, "peak": peak, "peak_kind": kind, "frac": gbs / peak,

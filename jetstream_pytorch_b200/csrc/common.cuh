@@ -113,10 +113,10 @@ __device__ __forceinline__ float insert_recip(float scale) {
 }
 template <typename T>
 __device__ __forceinline__ int8_t insert_code(float x, float recip) {
-  float t = round_to<T>(__fmul_rn(x, recip));
-  t = rintf(t);  // round half to even
-  t = fminf(fmaxf(t, -128.f), 127.f);
-  return (int8_t)(int)t;
+  const float t = round_to<T>(__fmul_rn(x, recip));
+  // one conversion instruction: round half to even, saturating; then the clamp on the integer
+  const int q = __float2int_rn(t);
+  return (int8_t)max(-128, min(127, q));
 }
 
 // Programmatic dependent launch: a kernel launched with launch_after_previous()
