@@ -715,11 +715,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       pending = true;
     } else {
       // ---------------- end of a piece: write the rows, or a partial for the merge
-      add_output(par, alpha, cmax);
       const bool is_final = piece_t0 == 0 && mt.t == mt.T - 1;
       const int slot = piece_t0 > 0 ? 0 : 1;
       const int64_t row_base = ((int64_t)mt.b * a.Hkv + mt.h) * R;
-      // denominators: sum the token shares of the 128 threads
+      // denominators: sum the token shares of the 128 threads (while the last O^T MMA runs)
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         float l = l_run[r];
@@ -728,6 +727,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
         if (lane == r) sm.red[warp][r] = l;
       }
       __syncthreads();
+      add_output(par, alpha, cmax);
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         if (r < R) {
