@@ -98,22 +98,28 @@ int jpt_kv_quant_append_dense(const void* xk, const void* xv, int in_dtype,
  * is order-independent).
  *
  * All ranks must call this the same number of times, in the same order, with
- * the same B.  A rank whose peer does not arrive within about half a second
- * goes on with the values it has and raises the status of its buffer
- * (jpt_peer_exchange_status); nothing waits without a limit.
+ * the same B.  A rank whose peer does not arrive within the wait limit (about
+ * half a second unless px->wait_cycles says otherwise) goes on with the values
+ * it has and raises the status of its buffer (jpt_peer_exchange_status);
+ * nothing waits without a limit.
  *
  * Setting up (once per process, any host-side transport for the handles):
  *   bytes = jpt_peer_exchange_bytes(B, world);
  *   jpt_peer_exchange_alloc(bytes, &own);            zero-filled device memory
  *   jpt_peer_exchange_export(own, handle);           64 bytes, send to the peers
  *   jpt_peer_exchange_import(handle_of_r, &buf[r]);  for every other rank r
- *   px = { rank, world, B, { buf[0..world-1] } } with buf[rank] = own.
+ *   px = { rank, world, B, { buf[0..world-1] }, 0 } with buf[rank] = own.
  * jpt_peer_exchange_release(buf[r]) and jpt_peer_exchange_free(own) undo it.
  */
 typedef struct jpt_peer_exchange {
   int rank, world; /* 1 <= world <= 8 */
   int batch;       /* the B the buffers were sized for */
   void* buffers[8];
+  /* How long a rank waits for a peer's word, in GPU clock cycles; 0 = the
+   * default (about half a second).  After a rank gave up, its status stays 1
+   * and the launch numbers of the ranks keep advancing together, so later
+   * launches pair up again. */
+  long long wait_cycles;
 } jpt_peer_exchange;
 
 size_t jpt_peer_exchange_bytes(int B, int world);
@@ -327,7 +333,10 @@ int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, void* stream)
  * positive code if a bounded wait inside a kernel ever gave up (the kernel then
  * returns early and its outputs are invalid).  Copies one int to the host and
  * SYNCHRONISES the stream: a diagnostic for tests, not for the step path.
- * (No counterpart in the reference.)
+ * workspace == NULL reads the word of the scratch built into the library (the
+ * one jpt_flash_decode_static uses) on the current device.  The word is sticky:
+ * it is only cleared by jpt_flash_decode_workspace_init (never, for the
+ * built-in scratch).  (No counterpart in the reference.)
  */
 int jpt_flash_decode_status(const void* workspace, void* stream);
 
@@ -347,10 +356,10 @@ int jpt_flash_decode_status(const void* workspace, void* stream);
  *     that first call outside any stream capture.
  *   - No cudaMalloc / cudaFree / allocating library routine is called, here or
  *     in anything this function calls.
- *   - All calls on a GPU share the one array and each call clears the header it
- *     relies on, so two calls that can overlap on the GPU (different streams
- *     without ordering, concurrent host threads) race.  Calls ordered on one
- *     stream are safe.
+ *   - All calls on a GPU share the one array and each call clears the arrival
+ *     counters it relies on, so two calls that can overlap on the GPU (different
+ *     streams without ordering, concurrent host threads) race.  Calls ordered on
+ *     one stream are safe.
  */
 int jpt_flash_decode_static(const jpt_attn_params* p, void* stream);
 

@@ -29,7 +29,8 @@ c_void_p, c_int, c_i64, c_size_t, c_float = (
 
 class PeerExchangeStruct(ctypes.Structure):
   """Mirror of `struct jpt_peer_exchange` (include/jpt_b200.h)."""
-  _fields_ = [("rank", c_int), ("world", c_int), ("batch", c_int), ("buffers", c_void_p * 8)]
+  _fields_ = [("rank", c_int), ("world", c_int), ("batch", c_int), ("buffers", c_void_p * 8),
+              ("wait_cycles", ctypes.c_longlong)]
 
 
 class AttnParams(ctypes.Structure):

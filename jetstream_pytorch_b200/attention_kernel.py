@@ -19,31 +19,60 @@ from jetstream_pytorch_b200 import _lib
 
 DEFAULT_MASK_VALUE = -0.7 * float(np.finfo(np.dtype("float32")).max)
 
-_workspaces = {}
+_workspaces = {}  # (device, stream handle) -> grow-only scratch tensor
 
 
 def _workspace(device, nbytes):
-  """Grow-only attention scratch per device (allocated by torch, owned here),
-  cleared once when it is created as the kernel's arrival counters require."""
-  ws = _workspaces.get(device)
+  """Grow-only attention scratch per (device, stream), allocated by torch and
+  owned here, cleared once when it is created as the kernel's arrival counters
+  require.  Two launches that share a workspace must not overlap on the GPU, so
+  every stream gets its own; a workspace cannot grow while its stream is being
+  captured into a CUDA graph (the allocation would land in the graph): run the
+  shape once before capturing."""
+  stream = torch.cuda.current_stream(device)
+  key = (device, stream.cuda_stream)
+  ws = _workspaces.get(key)
   if ws is None or ws.numel() < nbytes:
+    if torch.cuda.is_current_stream_capturing():
+      raise RuntimeError("the attention workspace of this stream is too small and cannot grow during CUDA graph "
+                         "capture; call the same shape once before capturing")
     ws = torch.empty(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
-    _lib.check(_lib.lib().jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), _lib.stream()))
-    _workspaces[device] = ws
+    _lib.check(_lib.lib().jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), stream.cuda_stream))
+    _workspaces[key] = ws
   return ws
 
 
 def kernel_status(device=None):
   """0 if no attention kernel on `device` ever gave up on a bounded wait, else
-  the code it recorded.  Synchronises the current stream (diagnostic only)."""
-  for dev, ws in _workspaces.items():
-    if device is None or torch.device(device) == dev:
-      rc = _lib.lib().jpt_flash_decode_status(_lib.ptr(ws), _lib.stream())
+  the code it recorded.  Covers every workspace this module handed out and the
+  scratch built into the library (`static_scratch=True`).  A workspace whose
+  status is raised is cleared again (its arrival counters may be left non-zero
+  by the launch that gave up).  Synchronises (diagnostic only)."""
+  lib = _lib.lib()
+  worst = 0
+  devices = set()
+  for (dev, stream), ws in _workspaces.items():
+    if device is not None and torch.device(device) != dev:
+      continue
+    devices.add(dev)
+    with torch.cuda.device(dev):
+      rc = lib.jpt_flash_decode_status(_lib.ptr(ws), stream)
       if rc < 0:
         _lib.check(rc)
       if rc:
-        return rc
-  return 0
+        worst = worst or rc
+        _lib.check(lib.jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), stream))
+  if device is not None:
+    devices.add(torch.device(device))
+  elif not devices and torch.cuda.is_available():
+    devices.add(torch.device("cuda", torch.cuda.current_device()))
+  for dev in devices:
+    with torch.cuda.device(dev):
+      rc = lib.jpt_flash_decode_status(None, _lib.stream())
+      if rc < 0:
+        _lib.check(rc)
+      worst = worst or rc
+  return worst
 
 
 def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale=None, v_scale=None,
@@ -60,6 +89,17 @@ def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale
   q = q.contiguous()
   b, hq, tq, d = q.shape
   dev = q.device
+  if dev.index is not None and dev.index != torch.cuda.current_device():
+    # launches go to the current device's stream and kernel attributes are per device
+    with torch.cuda.device(dev):
+      return _flash_decode(q, k, v, paged=paged, page_table=page_table, page_size=page_size, k_scale=k_scale,
+                           v_scale=v_scale, scale_strides=scale_strides, mask_mode=mask_mode, start=start, end=end,
+                           mask=mask, mask_strides=mask_strides, sm_scale=sm_scale, kv_strides=kv_strides,
+                           n_kv_heads=n_kv_heads, seq=seq, want_ml=want_ml, num_splits=num_splits,
+                           force_generic=force_generic, static_scratch=static_scratch)
+  for t in (k, v, k_scale, v_scale, mask):
+    if t is not None and t.device != dev:
+      raise ValueError(f"attention operands live on {t.device} and {dev}")
   p = _lib.AttnParams()
   p.q, p.q_dtype = _lib.ptr(q), _lib.dt(q)
   p.B, p.Hq, p.Hkv, p.Tq, p.D = b, hq, n_kv_heads, tq, d
@@ -158,11 +198,20 @@ def reshape_outputs(rep, o, m=None, d=None):
   return o, (m, d)
 
 
-def _mask_args(mask, q, s):
+def _mask_args(mask, q, s, n_kv_heads):
+  """Additive mask -> (mode, tensor, (batch stride, row stride)).  The kernels
+  read mask[b * mk_b + row * mk_r + s] for row in [0, rep * Tq): the batch
+  extent must be 1 or B and the row extent 1 or rep * Tq, exactly what
+  broadcasts against the grouped scores [B,Hkv,rep*Tq,S] in the reference
+  (attention_kernel.py:611-615), which raises for anything else."""
   if mask is None:
     return _lib.MASK_NONE, None, (0, 0)
+  b, hq, tq, _ = q.shape
+  rows = (hq // n_kv_heads) * tq
   if mask.ndim != 4 or mask.shape[1] != 1 or mask.shape[3] != s:
     raise ValueError(f"mask must be [B|1, 1, R|1, S]; got {tuple(mask.shape)}")
+  if mask.shape[0] not in (1, b) or mask.shape[2] not in (1, rows):
+    raise ValueError(f"mask {tuple(mask.shape)} does not broadcast against scores [{b}, {n_kv_heads}, {rows}, {s}]")
   if mask.dtype != q.dtype:
     mask = mask.to(q.dtype)
   if mask.stride(3) != 1:
@@ -177,7 +226,7 @@ def dense_attention(xq, keys, values, k_scaler=None, v_scaler=None, mask=None):
   row; `mask` holds 0 / -inf (or any additive values).  Returns [B,Hq,T,D]."""
   k, v, strides, hkv, s = _dense_kv(keys, values, 0)
   ks, vs, sst = _dense_scales(k_scaler, v_scaler, 0)
-  mode, mask, mst = _mask_args(mask, xq, s)
+  mode, mask, mst = _mask_args(mask, xq, s, hkv)
   o, _, _ = _flash_decode(xq, k, v, k_scale=ks, v_scale=vs, scale_strides=sst, mask_mode=mode, mask=mask,
                           mask_strides=mst, sm_scale=1.0 / math.sqrt(xq.shape[-1]), kv_strides=strides,
                           n_kv_heads=hkv, seq=s, want_ml=False)
@@ -190,7 +239,7 @@ def flash_attention(xq, keys, values, layer, k_scaler=None, v_scaler=None, mask=
   is applied to the numerator only)."""
   k, v, strides, hkv, s = _dense_kv(keys, values, layer)
   ks, vs, sst = _dense_scales(k_scaler, v_scaler, layer)
-  mode, mask, mst = _mask_args(mask, xq, s)
+  mode, mask, mst = _mask_args(mask, xq, s, hkv)
   sm = 1.0 / math.sqrt(k.shape[-1]) if normalize_var else 1.0
   o, m, l = _flash_decode(xq, k, v, k_scale=ks, v_scale=vs, scale_strides=sst, mask_mode=mode, mask=mask,
                           mask_strides=mst, sm_scale=sm, kv_strides=strides, n_kv_heads=hkv, seq=s)

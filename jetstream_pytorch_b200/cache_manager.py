@@ -253,6 +253,10 @@ class Int8KVCacheGenerate:
       vs = torch.empty((b, 1, 1, 1), dtype=xk.dtype, device=xk.device)
     else:
       kq, vq, ks, vs = outs
+      if ks.dtype != xk.dtype or vs.dtype != xk.dtype:  # the kernel writes the scale in the input's dtype
+        raise ValueError(f"scale buffers of dtype {ks.dtype} cannot take the scales of {xk.dtype} inputs")
+      if kq.dtype != torch.int8 or vq.dtype != torch.int8:
+        raise ValueError("the buffers for the quantised new token must be int8")
     p, n, host, keep = (None, 1, 0, None)
     s = 1
     cs = (0, 0, 0)
@@ -428,7 +432,9 @@ class PeerAmaxExchange:
   (`PeerAmaxExchange.with_torch_distributed` uses the default process group).
   All ranks must then make the same sequence of `update` calls."""
 
-  def __init__(self, batch_size, rank, world_size, handles_all_gather):
+  def __init__(self, batch_size, rank, world_size, handles_all_gather, wait_cycles=0):
+    """`wait_cycles`: how long a rank waits for a peer's word, in GPU clock
+    cycles (0 = the library default, about half a second)."""
     lib = _lib.lib()
     self.rank, self.world = rank, world_size
     nbytes = lib.jpt_peer_exchange_bytes(batch_size, world_size)
@@ -442,6 +448,7 @@ class PeerAmaxExchange:
     handles = handles_all_gather(handle.raw)
     self.struct = _lib.PeerExchangeStruct()
     self.struct.rank, self.struct.world, self.struct.batch = rank, world_size, batch_size
+    self.struct.wait_cycles = int(wait_cycles)
     self._opened = []
     for r in range(world_size):
       if r == rank:

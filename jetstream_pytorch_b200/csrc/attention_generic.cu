@@ -4,6 +4,8 @@
 // head_dim 128 lives in attention_mma.cu; this one covers every other shape.
 #include <math.h>
 
+#include <atomic>
+
 #include "attention_common.cuh"
 
 namespace jpt {
@@ -333,28 +335,35 @@ namespace {
 constexpr size_t kStaticScratchBytes = 16u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 constexpr int kMaxStaticDevices = 64;
-void* g_static_scratch_addr[kMaxStaticDevices] = {};  // device address of the array, per device ordinal
+std::atomic<void*> g_static_scratch_addr[kMaxStaticDevices];  // device address of the array, per device ordinal
+
+// Address of the built-in scratch on the current device (looked up once per device).
+int static_scratch_address(const char* who, void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail((int)e, "%s: cudaGetDevice: %s", who, cudaGetErrorString(e));
+  JPT_REQUIRE(dev >= 0 && dev < kMaxStaticDevices, JPT_ERANGE, "%s: device ordinal %d unsupported", who, dev);
+  void* ptr = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    // One-time set-up for the current device: `g_static_scratch` as written in
+    // host code is only a handle, the address the kernels need comes from here.
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      return fail(e != cudaSuccess ? (int)e : JPT_EINVAL, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
+    }
+    g_static_scratch_addr[dev].store(ptr, std::memory_order_release);  // every thread would store the same value
+  }
+  *out = ptr;
+  return 0;
+}
 }  // namespace
 
 extern "C" int jpt_flash_decode_static(const jpt_attn_params* pp, void* stream) {
   JPT_REQUIRE(pp, JPT_EINVAL, "flash_decode_static: null params");
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return fail((int)e, "flash_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
-  JPT_REQUIRE(dev >= 0 && dev < kMaxStaticDevices, JPT_ERANGE, "flash_decode_static: device ordinal %d unsupported", dev);
-  if (g_static_scratch_addr[dev] == nullptr) {
-    // One-time set-up for the current device: `g_static_scratch` as written in
-    // host code is only a handle, the address the kernels need comes from here.
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-    if (e != cudaSuccess || ptr == nullptr) {
-      return fail(e != cudaSuccess ? (int)e : JPT_EINVAL, "flash_decode_static: cudaGetSymbolAddress: %s",
-                  cudaGetErrorString(e));
-    }
-    g_static_scratch_addr[dev] = ptr;
-  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address("flash_decode_static", &scratch)) return rc;
   jpt_attn_params p = *pp;
-  p.workspace = g_static_scratch_addr[dev];
+  p.workspace = scratch;
   p.workspace_bytes = kStaticScratchBytes;
   if (int rc = validate(p)) return rc;
   const size_t need = jpt_flash_decode_workspace_bytes(&p);
@@ -364,15 +373,21 @@ extern "C" int jpt_flash_decode_static(const jpt_attn_params* pp, void* stream) 
               need, kStaticScratchBytes);
   if (need) {
     // The array keeps whatever the previous call left behind.  The arrival
-    // counters and the status word at its start must read zero on entry.
-    e = cudaMemsetAsync(p.workspace, 0, kWorkspaceCounterBytes, static_cast<cudaStream_t>(stream));
+    // counters at its start must read zero on entry; the status word behind
+    // them is left alone so that a wait that gave up stays visible to
+    // jpt_flash_decode_status(NULL, ...).
+    const cudaError_t e = cudaMemsetAsync(p.workspace, 0, kWorkspaceStatusOffset, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail((int)e, "flash_decode_static: clearing the scratch header: %s", cudaGetErrorString(e));
   }
   return jpt_flash_decode(&p, stream);
 }
 
 extern "C" int jpt_flash_decode_status(const void* workspace, void* stream) {
-  JPT_REQUIRE(workspace, JPT_EINVAL, "flash_decode_status: null workspace");
+  if (workspace == nullptr) {  // the scratch built into the library (jpt_flash_decode_static), current device
+    void* scratch = nullptr;
+    if (int rc = static_scratch_address("flash_decode_status", &scratch)) return rc;
+    workspace = scratch;
+  }
   int status = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemcpyAsync(&status, static_cast<const char*>(workspace) + kWorkspaceStatusOffset, sizeof(int),

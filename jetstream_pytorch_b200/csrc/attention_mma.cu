@@ -923,18 +923,22 @@ int launch_attention_mma(const jpt_attn_params& p, const AttnArgs& a, cudaStream
   x.part_o = reinterpret_cast<float*>(ws + lay.part_o);
   x.num_ctas = lay.num_ctas;
 
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(flash_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)sizeof(Smem<false, false>));
-    cudaFuncSetAttribute(flash_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)sizeof(Smem<true, false>));
-    cudaFuncSetAttribute(flash_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)sizeof(Smem<false, true>));
-    cudaFuncSetAttribute(flash_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)sizeof(Smem<true, true>));
-    configured = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  if (int rc = configure_once_per_device(configured, "flash_decode_kernel", [] {
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<false, false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem<false, false>));
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(flash_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)sizeof(Smem<true, false>));
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(flash_decode_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)sizeof(Smem<false, true>));
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(flash_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)sizeof(Smem<true, true>));
+        return e;
+      }))
+    return rc;
   if (a.mask_mode == JPT_MASK_ADD) {
     if (int rc = launch_mask_ranges(a, x, st)) return rc;
   }

@@ -6,6 +6,8 @@
 #include <limits.h>
 #include <math.h>
 
+#include <atomic>
+
 #include "attention_common.cuh"
 
 namespace jpt {
@@ -163,14 +165,38 @@ static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int
   }
 }
 
+// Per-device facts are kept per device ordinal: a process may drive several GPUs.
+constexpr int kMaxDevices = 64;
+
+inline int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
+
 inline int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  static std::atomic<int> n[kMaxDevices];
+  const int dev = current_device();
+  int v = n[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev].store(v, std::memory_order_relaxed);
   }
-  return n;
+  return v;
+}
+
+// Runs `configure` (which returns a cudaError_t) once per device, with that
+// device current; cudaFuncSetAttribute applies to the current device only.
+// Returns 0 or the positive CUDA error of a failed configuration (not cached,
+// so the next call tries again).
+template <typename F>
+inline int configure_once_per_device(std::atomic<bool> (&done)[kMaxDevices], const char* what, F configure) {
+  const int dev = current_device();
+  if (done[dev].load(std::memory_order_acquire)) return 0;
+  const cudaError_t e = configure();
+  if (e != cudaSuccess) return fail((int)e, "%s: configuring the kernel on device %d: %s", what, dev, cudaGetErrorString(e));
+  done[dev].store(true, std::memory_order_release);
+  return 0;
 }
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }

@@ -824,13 +824,16 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   int* status = reinterpret_cast<int*>(ws + kWorkspaceStatusOffset);
 
   constexpr int smem_bytes = (int)sizeof(SmemU);
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                         (int)cudaSharedmemCarveoutMaxShared);  // three CTAs of 75 KB per SM
-    configured = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  if (int rc = configure_once_per_device(configured, "flash_decode_i8_umma_kernel", [] {
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             smem_bytes);
+        if (e == cudaSuccess)  // three CTAs of 75 KB per SM
+          e = cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   (int)cudaSharedmemCarveoutMaxShared);
+        return e;
+      }))
+    return rc;
   if (a.mask_mode == JPT_MASK_ADD) {
     if (int rc = launch_mask_ranges(a, x, st)) return rc;
   }

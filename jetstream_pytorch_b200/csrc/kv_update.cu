@@ -75,6 +75,7 @@ struct QuantAppendArgs {
   unsigned long long* px_slots[kMaxPeers];  // slot area of each rank's exchange buffer (index = rank); null: off
   unsigned* px_state;                       // this rank's {launches done, CTAs done, gave up}
   int px_rank, px_world;
+  long long px_wait_cycles;                 // how long a rank waits for a peer's word
 };
 
 // Exchange buffer of one rank: kPeerStateBytes of state, then slots[parity][writer rank][2 B],
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(256) quant_append_kernel(QuantAppendArgs a) {
         const unsigned long long* p = a.px_slots[a.px_rank] + (row + r) * (2 * a.B) + idx;
         unsigned long long v = ld_peer(p);
         while ((unsigned)(v >> 32) != epoch) {
-          if (clock64() - t0 > kPeerWaitCycles) {  // the peer never came: report, go on with what is there
+          if (clock64() - t0 > a.px_wait_cycles) {  // the peer never came: report, go on with what is there
             atomicExch(&a.px_state[2], 1u);
             v = 0;
             break;
@@ -450,6 +451,7 @@ extern "C" int jpt_kv_quant_append_dense_peers(const void* xk, const void* xv, i
               "kv_quant_append_dense_peers: rank %d of %d", px->rank, px->world);
   JPT_REQUIRE(px->batch == B, JPT_EINVAL, "kv_quant_append_dense_peers: buffers are sized for batch %d, not %d",
               px->batch, B);
+  JPT_REQUIRE(px->wait_cycles >= 0, JPT_EINVAL, "kv_quant_append_dense_peers: negative wait limit");
   for (int r = 0; r < px->world; ++r)
     JPT_REQUIRE(px->buffers[r] && aligned(px->buffers[r], 8), JPT_EINVAL,
                 "kv_quant_append_dense_peers: buffer of rank %d missing or unaligned", r);
@@ -623,6 +625,7 @@ static int quant_append_dense(const void* xk, const void* xv, int in_dtype, int8
     a.px_state = static_cast<unsigned*>(px->buffers[px->rank]);
     a.px_rank = px->rank;
     a.px_world = px->world;
+    a.px_wait_cycles = px->wait_cycles > 0 ? px->wait_cycles : kPeerWaitCycles;
   }
   a.paged = 0;
   a.B = B; a.H = H; a.S = S; a.D = D; a.ps = 0;

@@ -67,6 +67,46 @@ def insert_mask_row(cache_len, pos, current_pos, wrap):
   return torch.where(cond, 0.0, float("-inf"))
 
 
+def engine_insert(ring_buffer, stacked, quantized, cache_len, current_position, seq_len, prefix_caches, caches,
+                  scales, slot):
+  """`PyTorchEngine.insert`, engine.py:627-648, with the two functions it
+  dispatches to.  Ring buffer: the no-wrap path when 0 <= cur - seq_len and
+  cur - seq_len + Lpad < S, else the modular one; left aligned: position 0.
+  prefix_caches [(k, v)] per layer ([1,H,Lpad,D]); caches [(k, v)] per layer or
+  one stacked pair; scales likewise (int8).  Returns (caches, scales, mask_row
+  fp32 [S], start, input_pos, lens) for the slot."""
+  lpad = prefix_caches[0][0].shape[2]
+  if ring_buffer:
+    start_insert = current_position - seq_len
+    wrap = not (start_insert >= 0 and start_insert + lpad < cache_len)
+    cur = current_position
+  else:
+    start_insert, wrap, cur = 0, False, seq_len
+  pos = start_insert % cache_len if wrap else start_insert
+  caches = [tuple(t.clone() for t in pair) for pair in caches]
+  scales = [tuple(t.clone() for t in pair) for pair in (scales or [])]
+  for i, new in enumerate(prefix_caches):
+    j = 0 if stacked else i
+    out_pair, out_scale = [], []
+    for t in range(2):
+      sc = scales[j][t] if quantized else None
+      if wrap:
+        r = insert_wrap(caches[j][t], new[t], slot, pos, scaler=sc, quantize=quantized)
+      else:
+        r = insert_no_wrap(caches[j][t], new[t], slot, pos, layer=i if stacked else None, scaler=sc,
+                           quantize=quantized)
+      if quantized:
+        out_pair.append(r[0])
+        out_scale.append(r[1])
+      else:
+        out_pair.append(r)
+    caches[j] = tuple(out_pair)
+    if quantized:
+      scales[j] = tuple(out_scale)
+  mask_row = insert_mask_row(cache_len, pos, cur, wrap)
+  return caches, scales, mask_row, pos % cache_len, seq_len, 1
+
+
 def insert_paged(cache, prefix, update_indexes, page_size):
   """engine.py:583-625 -> page_attention_manager.py:83-142."""
   return insert_prefill_pages(cache, prefix, update_indexes, page_size)

@@ -6,8 +6,11 @@ quantize.py), imported unmodified from a reference checkout.
 
 The reference needs jax and torch_xla2 only for array plumbing on this path
 (the arithmetic is torch / numpy), so `_refshim.py` supplies torch-backed
-stand-ins for those packages.  The Pallas-TPU ragged kernels and the JAX
-paged-attention kernel cannot be executed this way and have no fixture.
+stand-ins for those packages, including a sequential grid interpreter for
+`pallas_call` on which the reference's ragged-attention kernel bodies run as
+written, and placeholder modules that let `engine.py` import so that its insert
+functions can run.  The third-party JAX paged-attention kernel is not in the
+reference checkout and has no fixture.
 Inputs are drawn from torch generators with fixed seeds and stored with the
 outputs, so the tests never need the reference.
 """
@@ -21,6 +24,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import _refshim  # noqa: E402
+import golden_inputs  # noqa: E402
 from golden_io import save  # noqa: E402
 
 
@@ -249,6 +253,165 @@ def gen_attention(ak, q):
   save("attention", out)
 
 
+def gen_ragged(ak):
+  """`ragged_mha` (which maps `ragged_mqa_reference` over the KV heads with
+  jax.vmap and runs the kernel body of attention_kernel.py:255-329 through
+  pallas_call) for the left-aligned cases; the ring-buffer kernel body
+  `ragged_flash_attention_kernel` (attention_kernel.py:22-109) for the ring
+  cases.  The ring wrapper `ragged_mqa` passes its kernel one operand too few
+  in this snapshot (attention_kernel.py:207-218 omits `layer`), so the body is
+  driven here by a pallas_call over the same (batch, S // bk) grid with plain
+  block index maps, one KV head at a time as `ragged_mha` would."""
+  import functools
+  from jax.experimental import pallas as pl
+  from jax.experimental.pallas import tpu as pltpu
+  W = _refshim.JTensor.wrap
+  out = {}
+  for name in golden_inputs.RAGGED_CASES:
+    x = golden_inputs.ragged_inputs(name)
+    out[name + "_checksum"] = np.int64(golden_inputs.checksum(x))
+    q, k, v, ks, vs = x["q"], x["k"], x["v"], x["ks"], x["vs"]
+    stacked = k.ndim == 5
+    if not x["ring"]:
+      o, (m, l) = ak.ragged_mha(
+          W(q), W(k), W(v), x["layer"], W(x["start"]), W(x["end"]), None, None,
+          None if ks is None else W(ks), None if vs is None else W(vs), bk=x["bk"],
+          q_shard_axis=1, kv_shard_axis=2 if stacked else 1, testing=True)
+    else:
+      b, hq, t, d = q.shape
+      hkv, s = k.shape[1], k.shape[2]
+      rep = hq // hkv
+      qg = q.reshape(b, hkv, rep * t, d)
+      bk = min(x["bk"], s)
+      quantized = ks is not None
+      ksq = (ks if quantized else torch.ones(b, 1, s, 1, dtype=torch.bfloat16)).squeeze(-1)
+      vsq = (vs if quantized else torch.ones(b, 1, s, 1, dtype=torch.bfloat16)).squeeze(-1)
+      start, end = x["start"], x["end"]
+      line_end = torch.where(start < end, end, torch.full_like(end, s - 1))  # attention_kernel.py:189
+      body = functools.partial(ak.ragged_flash_attention_kernel, bk=bk, mask_value=ak.DEFAULT_MASK_VALUE,
+                               normalize_var=True, quantized=quantized)
+      row = pl.BlockSpec(index_map=lambda bb, i, *_: (bb, 0, 0), block_shape=(None, rep * t, d))
+      blk = pl.BlockSpec(index_map=lambda bb, i, *_: (bb, i, 0), block_shape=(None, bk, d))
+      sc = pl.BlockSpec(index_map=lambda bb, i, *_: (bb, 0, i), block_shape=(None, 1, bk))
+      os_, ms_, ls_ = [], [], []
+      for h in range(hkv):
+        qh = qg[:, h].contiguous()
+        res = pl.pallas_call(
+            body,
+            grid_spec=pltpu.PrefetchScalarGridSpec(
+                num_scalar_prefetch=6, in_specs=[row, blk, blk, sc, sc], out_specs=[row, row, row],
+                grid=(b, s // bk)),
+            out_shape=[qh, _refshim.ShapeDtypeStruct((b, rep * t, d), torch.float32),
+                       _refshim.ShapeDtypeStruct((b, rep * t, d), torch.float32)],
+        )(torch.tensor([0]), start, end, line_end, None, None, qh, k[:, h].contiguous(), v[:, h].contiguous(),
+          ksq, vsq)
+        os_.append(plain(res[0]))
+        ms_.append(plain(res[1])[..., 0])
+        ls_.append(plain(res[2])[..., 0])
+      o, m, l = torch.stack(os_, 1), torch.stack(ms_, 1), torch.stack(ls_, 1)
+    out[name + "_o"], out[name + "_m"], out[name + "_l"] = plain(o), plain(m), plain(l)
+  save("ragged", out)
+
+
+def gen_engine_insert(eng, pam_mod):
+  """`PyTorchEngine.insert` / `_insert_no_wrap` / `_insert_wrap`
+  (engine.py:371-648) and `insert_page_attention_with_reservation` (650-672),
+  called as unbound functions on a stand-in `self` that carries the fields they
+  read (env, shardings, the page manager)."""
+  W = _refshim.JTensor.wrap
+  out = {}
+  b, h, s, d, nl, lpad, seq_len = 4, 2, 32, 8, 2, 12, 10
+  cases = {  # name -> (ring_buffer, stacked, quantized, current_position)
+      "ring_nowrap_i8": (True, False, True, 20),
+      "ring_wrap_i8": (True, False, True, 5),
+      "ring_edge_i8": (True, False, True, 30),  # start 20, 20 + 12 == S: takes the wrap path without wrapping
+      "ring_nowrap_bf16": (True, False, False, 20),
+      "ring_wrap_bf16": (True, False, False, 5),
+      "left_i8": (False, False, True, 0),
+      "left_i8_stacked": (False, True, True, 0),
+      "left_bf16_stacked": (False, True, False, 0),
+  }
+  out["geometry"] = np.asarray([b, h, s, d, nl, lpad, seq_len])
+  for ci, (name, (ring, stacked, quant, cur)) in enumerate(cases.items()):
+    g = torch.Generator().manual_seed(200 + ci)
+    env = types.SimpleNamespace(
+        ring_buffer=ring, cache_sequence_length=s, generate_cache_stacked=stacked,
+        quant_config=types.SimpleNamespace(enable_kv_quantization=quant))
+    me = types.SimpleNamespace(env=env, cache_sharding=None, replicated=None)
+    me._insert_no_wrap = functools_partial(eng.PyTorchEngine._insert_no_wrap, me)
+    me._insert_wrap = functools_partial(eng.PyTorchEngine._insert_wrap, me)
+    shape = (nl, b, h, s, d) if stacked else (b, h, s, d)
+    sshape = (nl, b, 1, s, 1) if stacked else (b, 1, s, 1)
+    n_caches = 1 if stacked else nl
+    caches, scales = [], []
+    for _ in range(n_caches):
+      if quant:
+        caches.append((torch.randint(-127, 128, shape, generator=g).to(torch.int8),
+                       torch.randint(-127, 128, shape, generator=g).to(torch.int8)))
+        scales.append(((torch.rand(sshape, generator=g) + 0.01).to(torch.bfloat16),
+                       (torch.rand(sshape, generator=g) + 0.01).to(torch.bfloat16)))
+      else:
+        caches.append((randn(g, *shape), randn(g, *shape)))
+    prefix = [(randn(g, 1, h, lpad, d), randn(g, 1, h, lpad, d)) for _ in range(nl)]
+    prefix[0][0][0, :, 3, :] = 0  # an all-zero token
+    slot = 2
+    for i, (ck, cv) in enumerate(caches):
+      out[f"{name}_in_ck{i}"], out[f"{name}_in_cv{i}"] = ck.clone(), cv.clone()
+    for i, (a, c) in enumerate(scales):
+      out[f"{name}_in_ks{i}"], out[f"{name}_in_vs{i}"] = a.clone(), c.clone()
+    for i, (pk, pv) in enumerate(prefix):
+      out[f"{name}_prefix_k{i}"], out[f"{name}_prefix_v{i}"] = pk.clone(), pv.clone()
+    out[f"{name}_args"] = np.asarray([int(ring), int(stacked), int(quant), cur, slot])
+    state = eng.DecodeState(
+        W(torch.zeros(b, 1, dtype=torch.int32)), [(W(a.clone()), W(c.clone())) for a, c in caches],
+        [(W(a.clone()), W(c.clone())) for a, c in scales], cur, W(torch.full((b, 1), 9, dtype=torch.int32)),
+        W(torch.full((b, 1), 3, dtype=torch.int32)), W(torch.full((b, 1), 4, dtype=torch.int32)),
+        W(torch.full((b, s), float("-inf"))))
+    pre = eng.Prefix(W(torch.tensor([[7]], dtype=torch.int32)), [(W(a), W(c)) for a, c in prefix], seq_len)
+    res = eng.PyTorchEngine.insert(me, pre, state, slot)
+    for i, (ck, cv) in enumerate(res.caches):
+      out[f"{name}_out_ck{i}"], out[f"{name}_out_cv{i}"] = plain(ck), plain(cv)
+    for i, (a, c) in enumerate(res.cache_scales or []):
+      out[f"{name}_out_ks{i}"], out[f"{name}_out_vs{i}"] = plain(a), plain(c)
+    out[f"{name}_out_mask"] = plain(res.mask)
+    out[f"{name}_out_start"], out[f"{name}_out_input_pos"] = plain(res.start), plain(res.input_pos)
+    out[f"{name}_out_lens"], out[f"{name}_out_tokens"] = plain(res.lens), plain(res.tokens)
+
+  # paged insert with reservation (bf16 pools; the reference has no int8 paged cache)
+  g = torch.Generator().manual_seed(260)
+  p, ps, maxp = 24, 4, 6
+  pam = pam_mod.PageAttentionManager(b, p, ps, maxp)
+  pam.reserve_pages_insert(0, 6)  # pages 0, 1 are taken before the insert under test
+  env = types.SimpleNamespace(ring_buffer=False, cache_sequence_length=s, generate_cache_stacked=False,
+                              quant_config=types.SimpleNamespace(enable_kv_quantization=False))
+  me = types.SimpleNamespace(env=env, cache_sharding=None, replicated=None, page_attention_manager=pam,
+                             default_dtype=torch.bfloat16, prefill_cache_sharding=None)
+  me._insert_page_attention_jit = functools_partial(eng.PyTorchEngine._insert_page_attention, me)
+  pools = [(randn(g, h, p, ps, d), randn(g, h, p, ps, d)) for _ in range(nl)]
+  prefix = [(randn(g, 1, h, lpad, d), randn(g, 1, h, lpad, d)) for _ in range(nl)]
+  for i in range(nl):
+    out[f"paged_in_ck{i}"], out[f"paged_in_cv{i}"] = pools[i][0].clone(), pools[i][1].clone()
+    out[f"paged_prefix_k{i}"], out[f"paged_prefix_v{i}"] = prefix[i][0].clone(), prefix[i][1].clone()
+  state = eng.DecodeState(
+      W(torch.zeros(b, 1, dtype=torch.int32)), [(W(a.clone()), W(c.clone())) for a, c in pools], [], 0,
+      W(torch.full((b, 1), 9, dtype=torch.int32)), W(torch.full((b, 1), 3, dtype=torch.int32)),
+      W(torch.full((b, 1), 4, dtype=torch.int32)), W(torch.full((b, s), float("-inf"))))
+  pre = eng.Prefix(W(torch.tensor([[7]], dtype=torch.int32)), [(W(a), W(c)) for a, c in prefix], seq_len)
+  res = eng.PyTorchEngine.insert_page_attention_with_reservation(me, pre, state, 3)
+  for i, (ck, cv) in enumerate(res.caches):
+    out[f"paged_out_ck{i}"], out[f"paged_out_cv{i}"] = plain(ck), plain(cv)
+  out["paged_geometry"] = np.asarray([p, ps, maxp, 3, seq_len])
+  out["paged_out_page_indices"] = pam.page_indices.copy()
+  out["paged_out_lengths"] = np.asarray(pam.lengths).copy()
+  out["paged_out_mask"], out["paged_out_start"] = plain(res.mask), plain(res.start)
+  out["paged_out_input_pos"], out["paged_out_lens"] = plain(res.input_pos), plain(res.lens)
+  save("engine_insert", out)
+
+
+def functools_partial(fn, first):
+  return lambda *a: fn(first, *a)
+
+
 def main():
   if len(sys.argv) < 2:
     raise SystemExit("usage: make_golden.py <path of a jetstream-pytorch checkout>")
@@ -259,6 +422,8 @@ def main():
   gen_float_cache(cm)
   gen_pages(cm, pam)
   gen_attention(ak, q)
+  gen_ragged(ak)
+  gen_engine_insert(_refshim.import_reference_engine(ref), pam)
   print("golden fixtures written")
 
 

@@ -166,6 +166,62 @@ def test_attention_against_reference_outputs():
       assert torch.allclose(l.float(), g[pre + "flash_int8_l"].float(), atol=1e-4, rtol=1e-4)
 
 
+def test_ragged_restatement_against_the_reference_kernel_bodies():
+  """`ragged.npz` holds what the reference's own `ragged_mha` (left aligned,
+  attention_kernel.py:255-329 through pallas_call and vmap) and ring kernel body
+  (attention_kernel.py:22-109) return when executed on a sequential grid
+  interpreter.  The restatement runs the same fp32 op sequence on the same
+  library, so it must agree to fp32 round-off."""
+  import golden_inputs
+
+  g = load("ragged")
+  for name in golden_inputs.RAGGED_CASES:
+    x = golden_inputs.ragged_inputs(name)
+    assert golden_inputs.checksum(x) == int(g[name + "_checksum"]), "seeded inputs differ from the fixture's"
+    o, (m, l) = oa.ragged_mha(x["q"], x["k"], x["v"], x["layer"], x["start"], x["end"], x["ks"], x["vs"],
+                              bk=x["bk"], wrap=x["ring"])
+    tol = 1e-6 if x["q"].dtype == torch.float32 else 0.0
+    assert torch.allclose(o.float(), g[name + "_o"].float(), atol=tol, rtol=tol), name
+    assert torch.allclose(m, g[name + "_m"], atol=1e-6, rtol=1e-6), name
+    assert torch.allclose(l, g[name + "_l"], atol=1e-6, rtol=1e-6), name
+
+
+def test_engine_insert_bit_exact():
+  """`engine_insert.npz`: the reference's `PyTorchEngine.insert` (engine.py:
+  371-648) executed on ring / left-aligned, stacked / per-layer, int8 / bf16
+  caches, and its paged insert with reservation (650-672)."""
+  g = load("engine_insert")
+  b, h, s, d, nl, lpad, seq_len = (int(v) for v in g["geometry"])
+  for name in ("ring_nowrap_i8", "ring_wrap_i8", "ring_edge_i8", "ring_nowrap_bf16", "ring_wrap_bf16", "left_i8",
+               "left_i8_stacked", "left_bf16_stacked"):
+    ring, stacked, quant, cur, slot = (int(v) for v in g[name + "_args"])
+    n = 1 if stacked else nl
+    caches = [(g[f"{name}_in_ck{i}"], g[f"{name}_in_cv{i}"]) for i in range(n)]
+    scales = [(g[f"{name}_in_ks{i}"], g[f"{name}_in_vs{i}"]) for i in range(n)] if quant else []
+    prefix = [(g[f"{name}_prefix_k{i}"], g[f"{name}_prefix_v{i}"]) for i in range(nl)]
+    oc_, os_, mask, start, ipos, lens = oi.engine_insert(bool(ring), bool(stacked), bool(quant), s, cur, seq_len,
+                                                         prefix, caches, scales, slot)
+    for i in range(n):
+      assert torch.equal(oc_[i][0], g[f"{name}_out_ck{i}"]) and torch.equal(oc_[i][1], g[f"{name}_out_cv{i}"]), name
+      if quant:
+        assert torch.equal(os_[i][0], g[f"{name}_out_ks{i}"]) and torch.equal(os_[i][1], g[f"{name}_out_vs{i}"]), name
+    assert torch.equal(mask, g[f"{name}_out_mask"][slot]), name
+    assert int(g[f"{name}_out_start"][slot]) == start and int(g[f"{name}_out_input_pos"][slot]) == ipos
+    assert int(g[f"{name}_out_lens"][slot]) == lens
+    other = [i for i in range(b) if i != slot]
+    assert torch.isinf(g[f"{name}_out_mask"][other]).all()  # rows of the other slots are untouched
+  p, ps, maxp, slot, seq_len = (int(v) for v in g["paged_geometry"])
+  table = op.PageTableOracle(b, p, ps, maxp)
+  table.reserve_pages_insert(0, 6)
+  _, idx = table.reserve_pages_insert(slot, seq_len)
+  for i in range(nl):
+    assert torch.equal(oi.insert_paged(g[f"paged_in_ck{i}"], g[f"paged_prefix_k{i}"], idx, ps), g[f"paged_out_ck{i}"])
+    assert torch.equal(oi.insert_paged(g[f"paged_in_cv{i}"], g[f"paged_prefix_v{i}"], idx, ps), g[f"paged_out_cv{i}"])
+  assert np.array_equal(table.page_indices, g["paged_out_page_indices"].numpy())
+  assert np.array_equal(table.lengths, g["paged_out_lengths"].numpy())
+  assert torch.equal(oi.insert_mask_row(s, 0, seq_len, False), g["paged_out_mask"][slot])
+
+
 def test_ragged_restatement_consistent_with_pinned_dense():
   """The unpinned ragged restatements agree with the pinned flash_attention on
   the same valid set (left aligned and ring wrap)."""

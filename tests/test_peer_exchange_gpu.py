@@ -110,3 +110,34 @@ def test_two_ranks_equal_the_unsharded_update(tmp_path):
     assert torch.equal(ck, ref[0][:, rank * hs:(rank + 1) * hs])
     assert torch.equal(cv, ref[1][:, rank * hs:(rank + 1) * hs])
     assert torch.equal(ks, ref[2]) and torch.equal(vs, ref[3])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_gpus():
+  """Kernel attributes (the dynamic shared-memory opt-in) and the SM count are
+  per device: the tensor-core attention kernels must work on cuda:1 after their
+  first use on cuda:0, from one process."""
+  from jetstream_pytorch_b200 import attention_kernel as ak
+  from oracle import attention as oa
+  from oracle.quant import quantize_insert
+  from parity_tools import attention_close, describe
+
+  g = torch.Generator().manual_seed(77)
+  b, hq, hkv, s, d = 4, 32, 4, 512, 128
+  q = torch.randn(b, hq, 1, d, generator=g).to(torch.bfloat16)
+  kf = torch.randn(b, hkv, s, d, generator=g).to(torch.bfloat16)
+  vf = torch.randn(b, hkv, s, d, generator=g).to(torch.bfloat16)
+  k, ks = quantize_insert(kf, (-3, -1))
+  v, vs = quantize_insert(vf, (-3, -1))
+  end = torch.tensor([512, 1, 300, 77])
+  start = torch.zeros(b, dtype=torch.int64)
+  eo_i8, _ = oa.ragged_mha(q, k, v, 0, start, end, ks, vs, bk=512)
+  eo_bf, _ = oa.ragged_mha(q, kf, vf, 0, start, end, None, None, bk=512)
+  for index in (0, 1):  # the current device stays cuda:0 throughout
+    dev = torch.device("cuda", index)
+    o, _ = ak.ragged_mha(q.to(dev), k.to(dev), v.to(dev), 0, start.to(dev), end.to(dev), None, None, ks.to(dev),
+                         vs.to(dev))
+    assert o.device == dev and attention_close(o, eo_i8), describe(o, eo_i8)
+    o, _ = ak.ragged_mha(q.to(dev), kf.to(dev), vf.to(dev), 0, start.to(dev), end.to(dev), None, None, None, None)
+    assert attention_close(o, eo_bf), describe(o, eo_bf)
+  assert ak.kernel_status() == 0

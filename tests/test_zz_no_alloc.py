@@ -16,9 +16,9 @@ contents).
 import pytest
 import torch
 
-pytestmark = pytest.mark.gpu
+from parity_tools import attention_close, describe
 
-ATOL, RTOL = 2e-2, 1e-2
+pytestmark = pytest.mark.gpu
 
 
 def _case(seed, b, hq, hkv, s, d):
@@ -34,8 +34,19 @@ def _case(seed, b, hq, hkv, s, d):
   return [t.cuda() for t in (q, k, v, ks, vs, start, end)]
 
 
+def _check(o, m, l, o_ref, m_ref, l_ref, what):
+  assert attention_close(o, o_ref), f"{what}: {describe(o, o_ref)}"
+  live = torch.isfinite(m_ref)
+  assert torch.equal(torch.isfinite(m.cpu()), live.cpu()), what
+  assert torch.allclose(m.cpu()[live.cpu()], m_ref.cpu()[live.cpu()], atol=1e-3, rtol=1e-3), what
+  assert torch.allclose(l.cpu()[live.cpu()], l_ref.cpu()[live.cpu()], atol=1e-3, rtol=1e-3), what
+
+
 def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
+  """Two calls in a row through `jpt_flash_decode_static`, each checked against
+  the workspace entry point AND against the CPU oracle."""
   from jetstream_pytorch_b200 import attention_kernel as ak
+  from oracle import attention as oa
 
   for call, (seed, shape) in enumerate(((91, (24, 64, 8, 1024, 128)), (92, (9, 32, 8, 640, 128)))):
     q, k, v, ks, vs, start, end = _case(seed, *shape)
@@ -44,14 +55,36 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
     before = torch.cuda.memory_allocated()
     o, (m, l) = ak.ragged_mha(*args, ring=True, static_scratch=True)
     torch.cuda.synchronize()
-    assert torch.allclose(o.float(), o_ref.float(), atol=ATOL, rtol=RTOL), f"call {call}: outputs differ"
-    live = torch.isfinite(m_ref)
-    assert torch.equal(torch.isfinite(m), live)
-    assert torch.allclose(m[live], m_ref[live], atol=1e-3, rtol=1e-3)
-    assert torch.allclose(l[live], l_ref[live], atol=1e-3, rtol=1e-3)
     # only the three result tensors were created by the call
     grown = torch.cuda.memory_allocated() - before
     assert grown <= o.numel() * 2 + (m.numel() + l.numel()) * 4 + 3 * 512, f"call {call}: {grown} bytes"
+    _check(o, m, l, o_ref, m_ref, l_ref, f"call {call} vs the workspace entry point")
+    eo, (em, el) = oa.ragged_mha(q.cpu(), k.cpu(), v.cpu(), 0, start.cpu(), end.cpu(), ks.cpu(), vs.cpu(),
+                                 bk=min(512, k.shape[-2]), wrap=True)
+    _check(o, m, l, eo, em, el, f"call {call} vs the oracle")
+  assert ak.kernel_status() == 0
+
+
+def test_static_scratch_holds_split_k_partials_of_the_scalar_kernel():
+  """A float32 cache takes the scalar kernel; with three splits its partial
+  results live in the built-in array behind the header."""
+  from jetstream_pytorch_b200 import attention_kernel as ak
+  from oracle import attention as oa
+
+  g = torch.Generator().manual_seed(93)
+  b, hq, hkv, s, d = 5, 8, 2, 300, 64
+  q = torch.randn(b, hq, 1, d, generator=g)
+  k = torch.randn(b, hkv, s, d, generator=g)
+  v = torch.randn(b, hkv, s, d, generator=g)
+  end = torch.tensor([300, 1, 0, 150, 299])
+  start = torch.zeros(b, dtype=torch.int64)
+  for _ in range(2):
+    o, (m, l) = ak.ragged_mha(q.cuda(), k.cuda(), v.cuda(), 0, start.cuda(), end.cuda(), None, None, None, None,
+                              num_splits=3, static_scratch=True)
+    eo, (em, el) = oa.ragged_mha(q, k, v, 0, start, end, None, None, bk=300)
+    assert attention_close(o, eo, 1e-4, 1e-4), describe(o, eo)
+    live = torch.isfinite(em)
+    assert torch.allclose(l.cpu()[live], el[live], atol=1e-3, rtol=1e-3)
 
 
 def test_static_scratch_rejects_shapes_beyond_its_size():
