@@ -78,9 +78,13 @@ def kernel_status(device=None):
 def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale=None, v_scale=None,
                   scale_strides=(0, 0), mask_mode=_lib.MASK_NONE, start=None, end=None, mask=None,
                   mask_strides=(0, 0), sm_scale=1.0, kv_strides=(0, 0, 0), n_kv_heads=None, seq=None,
-                  want_ml=True, num_splits=0, force_generic=False, static_scratch=False):
+                  want_ml=True, num_splits=0, force_generic=False, static_scratch=False, out=None):
   """q [B,Hq,Tq,D] contiguous.  Returns o (q's shape and dtype), m, l float32
   [B,Hq,Tq] (or None, None).
+
+  `out=(o, m, l)` (m, l may be None) makes the call write into tensors the
+  caller already owns instead of creating new ones: a step loop that keeps its
+  buffers, or a CUDA graph whose outputs must stay at fixed addresses.
 
   `static_scratch=True` routes the call through `jpt_flash_decode_static`: no
   workspace tensor is created or passed, the kernels use the scratch array
@@ -96,7 +100,7 @@ def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale
                            v_scale=v_scale, scale_strides=scale_strides, mask_mode=mask_mode, start=start, end=end,
                            mask=mask, mask_strides=mask_strides, sm_scale=sm_scale, kv_strides=kv_strides,
                            n_kv_heads=n_kv_heads, seq=seq, want_ml=want_ml, num_splits=num_splits,
-                           force_generic=force_generic, static_scratch=static_scratch)
+                           force_generic=force_generic, static_scratch=static_scratch, out=out)
   for t in (k, v, k_scale, v_scale, mask):
     if t is not None and t.device != dev:
       raise ValueError(f"attention operands live on {t.device} and {dev}")
@@ -135,12 +139,22 @@ def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale
     p.mk_b, p.mk_r = mask_strides
     keep.append(mask)
   p.sm_scale = sm_scale
-  o = torch.empty_like(q)
-  p.o = _lib.ptr(o)
   m = l = None
-  if want_ml:
-    m = torch.empty((b, hq, tq), dtype=torch.float32, device=dev)
-    l = torch.empty((b, hq, tq), dtype=torch.float32, device=dev)
+  if out is not None:
+    o, m, l = out
+    if o.shape != q.shape or o.dtype != q.dtype or o.device != dev or not o.is_contiguous():
+      raise ValueError("out[0] must be a contiguous tensor of the query's shape, dtype and device")
+    for t in (m, l):
+      if t is not None and (t.numel() != b * hq * tq or t.dtype != torch.float32 or t.device != dev
+                            or not t.is_contiguous()):
+        raise ValueError("out[1], out[2] must be contiguous float32 tensors of B*Hq*Tq elements")
+  else:
+    o = torch.empty_like(q)
+    if want_ml:
+      m = torch.empty((b, hq, tq), dtype=torch.float32, device=dev)
+      l = torch.empty((b, hq, tq), dtype=torch.float32, device=dev)
+  p.o = _lib.ptr(o)
+  if m is not None and l is not None:
     p.m, p.l = _lib.ptr(m), _lib.ptr(l)
   p.num_splits, p.force_generic = num_splits, int(force_generic)
   lib = _lib.lib()
@@ -313,6 +327,8 @@ def ragged_mha(q, k, v, layer, start, end, ragged_batch_index=None, ragged_block
                           start=start if ring else None, end=end, sm_scale=sm, kv_strides=strides,
                           n_kv_heads=hkv, seq=s, **kw)
   rt = (hq // hkv) * tq
+  if m is None:  # out=(o, None, None): the caller does not want the softmax statistics
+    return o.reshape(bq, hkv, rt, dq), (None, None)
   return o.reshape(bq, hkv, rt, dq), (m.reshape(bq, hkv, rt), l.reshape(bq, hkv, rt))
 
 

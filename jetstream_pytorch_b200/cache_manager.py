@@ -378,7 +378,11 @@ class PageKVCacheGenerate:
   here as an extension (quantise-on-append like Int8KVCacheGenerate)."""
 
   def __init__(self, cache_k, cache_v, page_attention_manager: PageAttentionManager, page_token_indices,
-               sharding=None, env=None, k_scaler=None, v_scaler=None):
+               sharding=None, env=None, k_scaler=None, v_scaler=None, n_active_dev=None):
+    """`n_active_dev` (int32 device tensor [1], optional): the number of valid
+    columns of `page_token_indices` when the table was computed on the device
+    (`PageAttentionManager.get_page_token_indices_device`) and is B columns wide."""
+    self.n_active_dev = n_active_dev
     self.cache_k = cache_k
     self.cache_v = cache_v
     self.page_attention_manager = page_attention_manager
@@ -399,7 +403,7 @@ class PageKVCacheGenerate:
     _lib.check(_lib.lib().jpt_kv_append_paged(
         _lib.ptr(key.contiguous()), _lib.ptr(value.contiguous()), _lib.dt(key), _lib.ptr(self.cache_k),
         _lib.ptr(self.cache_v), _lib.dt(self.cache_k), _lib.ptr(self.k_scaler), _lib.ptr(self.v_scaler),
-        _lib.ptr(pti), n, n, None, b, h, p, ps, d, _lib.stream()))
+        _lib.ptr(pti), n, n, _lib.ptr(self.n_active_dev), b, h, p, ps, d, _lib.stream()))
     return self.cache_k, self.cache_v
 
   def state(self):

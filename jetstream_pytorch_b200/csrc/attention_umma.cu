@@ -3,10 +3,12 @@
 //
 // The int8 codes never pass through registers: both contractions run as
 // integer MMAs that read K, V and the small second operands straight from
-// shared memory and accumulate int32 in tensor memory (TMEM).
+// shared memory and accumulate int32 in tensor memory (TMEM).  A round handles
+// a tile of 256 consecutive valid tokens of one (sequence, KV head) segment as
+// two halves of 128 tokens (128 = the M extent of one MMA = the TMEM lanes):
 //
-//   S^T[128 tok x 16] = K[128 tok x 128 d] . Ql^T       kind::i8, K-major A and B
-//   O^T[128 d  x 32] = V^T[128 d x 128 tok] . Pl^T      kind::i8, MN-major A, K-major B
+//   S^T_h[128 tok x 16] = K_h[128 tok x 128 d] . Ql^T     kind::i8, K-major A and B   (h = 0, 1)
+//   O^T[128 d x 16]    += V_h^T[128 d x 128 tok] . Pl_h^T kind::i8, MN-major A, K-major B
 //
 // "Levels" make the small operands 8-bit without losing the precision of the
 // bf16 / fp32 values they stand for:
@@ -16,52 +18,73 @@
 //     S = s (S_h + S_l / 254) is exact to 2^-16 of the row's amax;
 //   * a probability p in [0, 1] (the running maximum is exact here), times the
 //     token's V scale relative to the largest V scale of the tile, becomes a
-//     24-bit fixed-point number whose three bytes are the unsigned levels
-//     Pl[8 l + r]; O = (O_0 + 2^8 O_1 + 2^16 O_2) c / (2^24 - 1).
-// Every int32 sum is exact (|sum| <= 128 * 127 * 255), so the only roundings
-// are the two splits above and the fp32 online-softmax arithmetic.
+//     16-bit fixed-point number whose two bytes are the unsigned levels
+//     Pl[8 l + r]; O = (O_0 + 2^8 O_1) c / (2^16 - 1).  The rounding error of a
+//     probability is at most 2^-17 of the row's largest one.
+// Every int32 sum is exact (|O_0 + 2^8 O_1| <= 256 * 127 * 65535 < 2^31), so
+// the only roundings are the two splits above and the fp32 online-softmax
+// arithmetic.
 //
-// A tile is 128 consecutive valid tokens of one (sequence, KV head) segment;
-// tiles are scheduled exactly as in the mma.sync kernel (equal contiguous
-// shares of one global tile list, pieces, last-arriver merge).  K and V rows
-// of a tile land in shared memory as 128-byte rows, 16-byte chunks XORed with
-// (row & 7): that is the canonical 128-byte-swizzle layout of the tensor core
-// for both operand roles (K-major for K, MN-major for V), so nothing is
-// rearranged.  In the softmax phase thread t owns token t of the tile (TMEM
-// lane t of S^T); in the output phase thread t owns head-dim index t (TMEM
-// lane t of O^T), which also removes the cross-warp merge of the accumulators.
+// Thread t of the 128 owns tokens t and 128 + t of the tile in the softmax
+// phase (TMEM lane t of S^T_0 and S^T_1: two independent dependency chains per
+// thread, one exchange of row maxima and one rescale of the accumulators per
+// 256 tokens) and head-dim index t in the output phase (TMEM lane t of O^T),
+// which also removes the cross-warp merge of the accumulators.
+//
+// Tiles are scheduled as in the mma.sync kernel (equal contiguous shares of one
+// global tile list, pieces, last-arriver merge).  K and V rows land in shared
+// memory as 128-byte rows, 16-byte chunks XORed with (row & 7): the canonical
+// 128-byte-swizzle layout of the tensor core for both operand roles (K-major
+// for K, MN-major for V), so nothing is rearranged.  K has ONE buffer (the
+// S^T MMAs of a round are issued a round ahead and are long finished when the
+// next K rows are requested), V has two.  The rows are moved by the copy engine
+// where the cache can be described by a tensor map (cp.async.bulk.tensor boxes
+// of 256 or 32 rows with the 128-byte swizzle, issued by one thread, completion
+// counted in bytes on an mbarrier); caches that cannot (row strides that are not
+// multiples of 16 bytes, page sizes that are not multiples of 32) are copied 16
+// bytes at a time by all threads.  A segment whose valid range wraps around the
+// ring is cut into tiles run by run, so a tile is always one range of rows.
 //
 // Every wait on an mbarrier is bounded; a CTA that gives up raises the status
 // word of the workspace, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
 #include "attention_tiles.cuh"
 
 namespace jpt {
 namespace {
 
-constexpr int kTileU = 128;     // tokens per tile = TMEM lanes = threads per CTA
-constexpr int kStagesU = 2;     // K/V ring depth
-constexpr int kTmemCols = 64;   // S^T: columns 0..15, O^T: columns 16..47
-constexpr int kColO = 16;
-constexpr int kCtasPerSm = 3;
+constexpr int kHalfU = 128;           // tokens per MMA = TMEM lanes = threads per CTA
+constexpr int kTileU = 2 * kHalfU;    // tokens per round
+constexpr int kTmemCols = 64;         // S^T_0: columns 0..15, S^T_1: 16..31, O^T: 32..47
+constexpr int kColS1 = 16, kColO = 32;
+constexpr int kCtasPerSm = 2;
 #ifndef JPT_PIECE_COST_U
 #define JPT_PIECE_COST_U 1
 #endif
-constexpr int kPieceCostU = JPT_PIECE_COST_U;  // overhead slots charged per segment, in 128-token tiles
+constexpr int kPieceCostU = JPT_PIECE_COST_U;  // overhead slots charged per segment, in 256-token tiles
 constexpr long long kWaitCycles = 1000000000ll;  // about half a second: far beyond any wait of a healthy run
 
 struct __align__(1024) SmemU {
-  uint8_t kv[kStagesU][2][kTileU * kD];  // [stage][K, V][token][128 bytes], swizzled
-  uint8_t qlev[16 * kD];                 // query levels: rows 0..7 high bytes, 8..15 low bytes
-  uint8_t plev[32 * kTileU];             // probability levels: row 8 l + r, one byte per token
-  uint8_t qraw[8 * kD * 2];              // bf16 query rows of the piece whose first tile is in flight
-  float xch[4][12];                      // per warp: row maxima of the tile [8], largest V scale [1]
-  float red[4][8];                       // per warp: denominators at the end of a piece
-  float qsc[8];                          // s_r * sm_scale * log2(e) / 254
-  uint64_t bar[2];                       // MMA completion: S^T, O^T
+  uint8_t k[kTileU * kD];        // [token][128 bytes], swizzled; halves 16 KB apart
+  uint8_t v[2][kTileU * kD];     // [stage][token][128 bytes], swizzled
+  uint8_t qlev[16 * kD];         // query levels: rows 0..7 high bytes, 8..15 low bytes
+  uint8_t plev[2][16 * kHalfU];  // probability levels per half: row 8 l + r, one byte per token
+  uint8_t qraw[8 * kD * 2];      // bf16 query rows of the piece whose first tile is in flight
+  float xch[4][12];              // per warp: row maxima of the tile [8], largest V scale [1]
+  float red[4][8];               // per warp: denominators at the end of a piece
+  float qsc[8];                  // s_r * sm_scale * log2(e) / 254
+  uint64_t bar[2];               // MMA completion: S^T (both halves), O^T
+  uint64_t bar_in[3];            // rows landed (copy-engine path): K, V stage 0, V stage 1
   uint32_t tmem_base;
   int start[3];
   int flag;
-  TileMeta meta[kStagesU];
+  TileMeta meta[2];
 };
 
 // 16-byte copy with compile-time offsets on both addresses (one pair of base registers per tensor)
@@ -71,40 +94,70 @@ __device__ __forceinline__ void cp_async16_at(uint32_t dst, const void* src) {
 }
 template <int kI>
 __device__ __forceinline__ void cp_async_tile_rows(uint32_t kdst, uint32_t vdst, const void* kp, const void* vp) {
-  if constexpr (kI < 8) {
+  if constexpr (kI < 16) {
     cp_async16_at<2048 * kI>(kdst, kp);
     cp_async16_at<2048 * kI>(vdst, vp);
     cp_async_tile_rows<kI + 1>(kdst, vdst, kp, vp);
   }
 }
-// The three bytes of y into level rows r, 8 + r, 16 + r (kRowOff = 128 r) of the probability levels.
+// The two bytes of y into level rows r, 8 + r (kRowOff = 128 r) of the probability levels.
 template <int kRowOff>
 __device__ __forceinline__ void store_levels(uint32_t addr, uint32_t y) {
   asm volatile("st.shared.u8 [%0 + %2], %1;" ::"r"(addr), "r"(y), "n"(kRowOff) : "memory");
   asm volatile("st.shared.u8 [%0 + %2], %1;" ::"r"(addr), "r"(y >> 8), "n"(kRowOff + 1024) : "memory");
-  asm volatile("st.shared.u8 [%0 + %2], %1;" ::"r"(addr), "r"(y >> 16), "n"(kRowOff + 2048) : "memory");
 }
 constexpr float kNoMax = -1.0e30f;  // "no logit seen yet": finite, far below any logit
-// Rows kRow .. 7 of one token: new running maximum, rescale factor, probability,
-// denominator share, and the probability's three level bytes.  m_run starts at
-// kNoMax (finite), so exp2(old - new) and exp2(-inf - new) need no special case.
-template <int kRow>
+__device__ __forceinline__ float ex2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(x));
+  return r;
+}
+// Rows kRow .. 7 of the thread's two tokens: new running maximum, rescale
+// factor, probabilities, denominator share, and the probabilities' level bytes.
+// m_run starts at kNoMax (finite), so exp2(old - new) and exp2(-inf - new) need
+// no special case.  kTwo = false: the second half of the tile holds no token.
+template <int kRow, bool kTwo>
 __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8], float (&alpha)[8], const float (&tm)[8],
-                                             const float (&xv)[8], float pscale, const uint32_t (&p_row)[8]) {
+                                             const float (&x0)[8], const float (&x1)[8], float ps0, float ps1,
+                                             const uint32_t (&p_row)[8]) {
   if constexpr (kRow < 8) {
     const float mn = fmaxf(m_run[kRow], tm[kRow]);
-    float al, p;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(al) : "f"(m_run[kRow] - mn));
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(p) : "f"(xv[kRow] - mn));
+    const float al = ex2(m_run[kRow] - mn);
+    const float p0 = ex2(x0[kRow] - mn);
     alpha[kRow] = al;
     m_run[kRow] = mn;
-    l_run[kRow] = l_run[kRow] * al + p;
-    store_levels<128 * kRow>(p_row[kRow], __float2uint_rn(p * pscale));
-    softmax_rows<kRow + 1>(m_run, l_run, alpha, tm, xv, pscale, p_row);
+    store_levels<128 * kRow>(p_row[kRow], __float2uint_rn(p0 * ps0));
+    if constexpr (kTwo) {
+      const float p1 = ex2(x1[kRow] - mn);
+      l_run[kRow] = fmaf(l_run[kRow], al, p0 + p1);
+      store_levels<128 * kRow + 2048>(p_row[kRow], __float2uint_rn(p1 * ps1));
+    } else {
+      l_run[kRow] = fmaf(l_run[kRow], al, p0);
+    }
+    softmax_rows<kRow + 1, kTwo>(m_run, l_run, alpha, tm, x0, x1, ps0, ps1, p_row);
   }
 }
-__device__ __forceinline__ int tiles_u(int n) { return (n + kTileU - 1) / kTileU; }
-__device__ __forceinline__ int slots_u(int n) { return n > 0 ? tiles_u(n) + kPieceCostU : 0; }
+// A segment's valid tokens form one run of consecutive rows, or two when the
+// ring wraps: [first, first + nA) and [0, n - nA).  Tiles never straddle the
+// wrap: run A is cut into tiles of 256 rows (the last one partial), then run B.
+__device__ __forceinline__ int run_a(const SeqRange& r, int S) { return min(r.n, S - r.first); }
+__device__ __forceinline__ int tiles_run(int n) { return (n + kTileU - 1) / kTileU; }
+__device__ __forceinline__ int tiles_u(const SeqRange& r, int S) {
+  const int na = run_a(r, S);
+  return tiles_run(na) + tiles_run(r.n - na);
+}
+__device__ __forceinline__ int slots_u(const SeqRange& r, int S) { return r.n > 0 ? tiles_u(r, S) + kPieceCostU : 0; }
+// Tile t of the segment: physical position of its first row and its number of valid rows.
+__device__ __forceinline__ void tile_rows(const SeqRange& r, int S, int t, int* pos, int* cnt) {
+  const int na = run_a(r, S), ta = tiles_run(na);
+  if (t < ta) {
+    *pos = r.first + t * kTileU;
+    *cnt = min(kTileU, na - t * kTileU);
+  } else {
+    *pos = (t - ta) * kTileU;
+    *cnt = min(kTileU, r.n - na - (t - ta) * kTileU);
+  }
+}
 
 // Byte offset of (row, byte) in a tile of 128-byte rows with 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz(int row, int byte) {
@@ -121,10 +174,10 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
   d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
   return d;
 }
-// Instruction descriptors: int32 accumulators, M = 128.
-constexpr uint32_t kIdescS = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);  // s8 x s8, N = 16
+// Instruction descriptors: int32 accumulators, M = 128, N = 16.
+constexpr uint32_t kIdescS = (2u << 4) | (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);  // s8 x s8
 constexpr uint32_t kIdescO =
-    (2u << 4) | (1u << 7) | (0u << 10) | (1u << 15) | ((32u >> 3) << 17) | ((128u >> 4) << 24);  // s8 (MN-major) x u8, N = 32
+    (2u << 4) | (1u << 7) | (0u << 10) | (1u << 15) | ((16u >> 3) << 17) | ((128u >> 4) << 24);  // s8 (MN-major) x u8
 
 __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -151,13 +204,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i) {
-      uint32_t ok;
-      asm volatile(
-          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
-          : "=r"(ok)
-          : "r"(bar), "r"(parity)
-          : "memory");
-      if (ok) return true;
+      if (mbar_probe(bar, parity)) return true;
     }
     if (clock64() - t0 > kWaitCycles) return false;
   }
@@ -175,11 +222,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr));
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // maximum over the 32 lanes in one instruction
 __device__ __forceinline__ float warp_max(float x) {
@@ -187,6 +229,26 @@ __device__ __forceinline__ float warp_max(float x) {
   asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
   return r;
 }
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One box of a 4-d tensor map (128 bytes x rows x 1 x 1) into swizzled shared memory of this CTA.
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int row, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+
+// Tensor maps of the K and V tensors: dense [B, Hkv, S, 128 bytes] with the
+// caller's strides, or the page pool [Hkv, pages, page_size, 128 bytes]; one
+// map per box height (big: a whole tile of a dense cache or a whole page,
+// 32 rows: tails).
+struct TmaMaps {
+  CUtensorMap k_big, v_big, k_rows32, v_rows32;
+};
+constexpr int kTmaNone = 0, kTmaDense = 1, kTmaPaged = 2;
 
 #ifdef JPT_UMMA_SPANS
 // Debug builds only: per CTA, nanosecond stamps of the phases of its life.
@@ -204,7 +266,9 @@ __device__ __forceinline__ unsigned long long gtimer_ns() {
 #define JPT_SPAN(k) do {} while (0)
 #endif
 
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_kernel(AttnArgs a, MmaScratch x, int* status) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+    flash_decode_i8_umma_kernel(AttnArgs a, MmaScratch x, int* status, const __grid_constant__ TmaMaps maps, int tma_mode,
+                                int big_rows) {
   // The swizzled tiles need a 1024-byte aligned base.  The array is declared
   // with that alignment (and used in place, so that every access compiles to a
   // shared-memory instruction); a base that is not aligned after all is reported.
@@ -230,6 +294,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   if (tid == 32) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[0])));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[1])));
+    for (int z = 0; z < 3; ++z) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar_in[z])));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -248,13 +313,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   // Slots per sequence (tiles + overhead) -> exclusive prefix over sequences;
   // each thread owns a slice of ceil(B/128) sequences.  The scan scratch
   // aliases the probability levels, which are not in use yet.
-  int* scan = reinterpret_cast<int*>(&sm.plev[0]);  // 129 ints
+  int* scan = reinterpret_cast<int*>(&sm.plev[0][0]);  // 129 ints
   const int per = (a.B + kThreads - 1) / kThreads;
   const int b_lo = min(a.B, tid * per), b_hi = min(a.B, b_lo + per);
   int mine = 0;
   for (int b = b_lo; b < b_hi; ++b) {
     int ua;
-    mine += slots_u(seq_range_x(a, x, b, &ua).n);
+    mine += slots_u(seq_range_x(a, x, b, &ua), a.S);
   }
   scan[tid] = mine;
   __syncthreads();
@@ -291,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       int run = lo;
       for (int b = b_lo; b < b_hi; ++b) {
         int ua;
-        const int sl = slots_u(seq_range_x(a, x, b, &ua).n);
+        const int sl = slots_u(seq_range_x(a, x, b, &ua), a.S);
         const int nxt = run + sl * a.Hkv;
         if (G0 < nxt) {
           const int rem = G0 - run;
@@ -358,31 +423,32 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   const int kv_s32 = (int)a.kv_s, sc_s32 = (int)a.sc_s;
   const int8_t *kseg, *vseg;  // segment base + this thread's column
   int64_t scseg;
-  int ppos;                   // physical position of row 0 of tile pt
+  int ppos, pcnt;             // physical position of row 0 of tile pt, its valid rows
   int pfirst_cta, pparts;
+  SeqRange prange;
 
   auto load_seq = [&]() {
-    const SeqRange r = seq_range_x(a, x, pb, &puse_add);
-    pn = r.n;
-    pfirst = r.first;
-    pT = tiles_u(r.n);
+    prange = seq_range_x(a, x, pb, &puse_add);
+    pn = prange.n;
+    pfirst = prange.first;
+    pT = tiles_u(prange, a.S);
   };
   auto seg_setup = [&]() {  // pt, pslot are set
     const int64_t seg = a.paged ? (int64_t)ph * a.kv_h : (int64_t)pb * a.kv_b + (int64_t)ph * a.kv_h;
     kseg = kbase + seg + pcol * 16;
     vseg = vbase + seg + pcol * 16;
     scseg = a.paged ? 0 : (int64_t)pb * a.sc_b;
-    ppos = pfirst + pt * kTileU;
-    if (ppos >= a.S) ppos -= a.S;
+    tile_rows(prange, a.S, pt, &ppos, &pcnt);
     const int t0slot = pslot - pt;  // slot of tile 0 of this segment
     pfirst_cta = t0slot / share;
     pparts = (t0slot + pT - 1) / share - pfirst_cta + 1;
   };
   auto advance = [&]() {
     ++pslot;
-    ppos += kTileU;
-    if (ppos >= a.S) ppos -= a.S;
-    if (++pt < pT) return;
+    if (++pt < pT) {
+      tile_rows(prange, a.S, pt, &ppos, &pcnt);
+      return;
+    }
     pt = 0;
     pslot += kPieceCostU;  // the overhead slots of the next segment
     if (++ph == a.Hkv) {
@@ -410,36 +476,86 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     seg_setup();
   }
 
-  float nks = 1.f, nvs = 0.f;  // scales of this thread's token in the tile fetched last
+  // scales of this thread's two tokens (tid, 128 + tid) in the tile fetched last
+  float nks0 = 1.f, nvs0 = 0.f, nks1 = 1.f, nvs1 = 0.f;
   bool first_issue = true;
+  bool dead = false;  // a wait ran out
 
-  auto issue_tile = [&](int stage) {
-    const int j0 = pt * kTileU;
+  auto token_scales = [&](int r, float& ksc, float& vsc) {  // r: row of the tile
+    ksc = 1.f;
+    vsc = 0.f;
+    if (r < pcnt) {
+      vsc = 1.f;
+      if (quant) {
+        const int pos = ppos + r;
+        int64_t sidx;
+        if (a.paged) {
+          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
+          sidx = (int64_t)pg * a.page_size + pos % a.page_size;
+        } else {
+          sidx = scseg + (int64_t)pos * sc_s32;
+        }
+        ksc = load_scale(a.k_scale, sidx, a.scale_is_f32);
+        vsc = load_scale(a.v_scale, sidx, a.scale_is_f32);
+      }
+    }
+  };
+  // K rows of tile pt into the K buffer, V rows into V stage `vstage`, the record into meta[mslot].
+  auto issue_tile = [&](int vstage, int mslot) {
     const bool piece_start = first_issue || pt == 0;
     first_issue = false;
     if (tid == 0) {
       TileMeta mt;
       mt.b = pb; mt.h = ph; mt.t = pt; mt.T = pT; mt.n = pn; mt.first = pfirst; mt.use_add = puse_add;
       mt.first_cta = pfirst_cta; mt.parts = pparts;
-      mt.pad[0] = mt.pad[1] = 0;
+      mt.pad[0] = pcnt;             // valid rows of the tile
+      mt.pad[1] = ppos;             // physical position of its first row
       mt.pad[2] = pslot + 1 >= G1;  // no tile follows in this CTA's share
-      sm.meta[stage] = mt;
+      sm.meta[mslot] = mt;
     }
-    const uint32_t kdst = smem_u32(&sm.kv[stage][0][0]) + pdst;
-    const uint32_t vdst = smem_u32(&sm.kv[stage][1][0]) + pdst;
-    if (rows_packed && j0 + kTileU <= pn && ppos + kTileU <= a.S) {
-      // whole tile valid, no ring wrap, rows kD bytes apart: one address per tensor
+    const uint32_t kdst = smem_u32(&sm.k[0]) + pdst;
+    const uint32_t vdst = smem_u32(&sm.v[vstage][0]) + pdst;
+    const int passes = (pcnt + 15) >> 4;  // 16-row passes that hold a valid row
+    if (tma_mode != kTmaNone) {
+      // One thread hands the rows to the copy engine: boxes of `big_rows` rows while that many
+      // valid rows remain (a whole dense tile, a whole page), boxes of 32 rows for the rest.  Rows
+      // of the last box past the valid ones are whatever follows in the cache (or zeros past its
+      // end); their logits are masked and their probabilities are zero.
+      if (tid == 0) {
+        const uint32_t kbar = smem_u32(&sm.bar_in[0]), vbar = smem_u32(&sm.bar_in[1 + vstage]);
+        const uint32_t k0 = smem_u32(&sm.k[0]), v0 = smem_u32(&sm.v[vstage][0]);
+        const int n_big = pcnt / big_rows;
+        const int n_32 = (pcnt - n_big * big_rows + 31) >> 5;
+        const uint32_t bytes = (uint32_t)(n_big * big_rows + n_32 * 32) * kD;
+        mbar_arrive_expect_tx(kbar, bytes);
+        mbar_arrive_expect_tx(vbar, bytes);
+        int r = 0;
+        for (int bx = 0; bx < n_big + n_32; ++bx) {
+          const bool big = bx < n_big;
+          int row = ppos + r, c2 = ph, c3 = pb;
+          if (tma_mode == kTmaPaged) {
+            c2 = a.page_table[(int64_t)pb * a.max_pages + row / a.page_size];
+            c3 = ph;
+            row = row % a.page_size;
+          }
+          tma_load_rows(k0 + r * kD, big ? &maps.k_big : &maps.k_rows32, row, c2, c3, kbar);
+          tma_load_rows(v0 + r * kD, big ? &maps.v_big : &maps.v_rows32, row, c2, c3, vbar);
+          r += big ? big_rows : 32;
+        }
+      }
+    } else if (rows_packed && pcnt == kTileU) {
+      // whole tile valid, rows kD bytes apart: one address per tensor
       const int64_t off = (int64_t)(ppos + prow) * kD;
       const int8_t* kp = kseg + off;
       const int8_t* vp = vseg + off;
       cp_async_tile_rows<0>(kdst, vdst, kp, vp);
     } else if (pass_pages) {
       // paged caches start at position 0: pass i (rows 16 i ..) lies inside one page
-      int pi = j0 / a.page_size, within = (j0 % a.page_size) / 16;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const bool valid = j0 + 16 * i + prow < pn;
-        const int page = (j0 + 16 * i) < pn ? a.page_table[(int64_t)pb * a.max_pages + pi] : 0;
+      int pi = ppos / a.page_size, within = (ppos % a.page_size) / 16;
+#pragma unroll 4
+      for (int i = 0; i < passes; ++i) {
+        const bool valid = 16 * i + prow < pcnt;
+        const int page = a.page_table[(int64_t)pb * a.max_pages + pi];
         const int64_t off = (int64_t)page * a.kv_page + (int64_t)(within * 16 + prow) * kD;
         cp_async16(kdst + 2048 * i, kseg + off, valid);
         cp_async16(vdst + 2048 * i, vseg + off, valid);
@@ -449,12 +565,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
         }
       }
     } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
+#pragma unroll 4
+      for (int i = 0; i < passes; ++i) {
         const int r = prow + 16 * i;
-        const bool valid = j0 + r < pn;
-        int pos = valid ? ppos + r : ppos;
-        if (pos >= a.S) pos -= a.S;
+        const bool valid = r < pcnt;
+        const int pos = valid ? ppos + r : ppos;
         int64_t off;
         if (a.paged) {
           const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
@@ -470,56 +585,48 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       const __nv_bfloat16* q = qbase + ((int64_t)pb * a.Hkv + ph) * R * kD;
       for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.qraw[0]) + ch * 16, q + ch * 8, true);
     }
-    // scales of token `tid` of the tile, consumed by this same thread
-    nks = 1.f;
-    nvs = 0.f;
-    if (j0 + tid < pn) {
-      nvs = 1.f;
-      if (quant) {
-        int pos = ppos + tid;
-        if (pos >= a.S) pos -= a.S;
-        int64_t sidx;
-        if (a.paged) {
-          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
-          sidx = (int64_t)pg * a.page_size + pos % a.page_size;
-        } else {
-          sidx = scseg + (int64_t)pos * sc_s32;
-        }
-        nks = load_scale(a.k_scale, sidx, a.scale_is_f32);
-        nvs = load_scale(a.v_scale, sidx, a.scale_is_f32);
-      }
-    }
+    token_scales(tid, nks0, nvs0);
+    token_scales(kHalfU + tid, nks1, nvs1);
   };
-  // Fetch the next tile of the share into `stage`, or mark the stage as empty.
-  auto produce = [&](int stage) {
-    if (pslot < G1) {
-      issue_tile(stage);
+  // Fetch the next tile of the share, or mark the record as empty.
+  auto produce = [&](int vstage, int mslot) {
+    const bool more = pslot < G1;
+    if (more) {
+      issue_tile(vstage, mslot);
       advance();
     } else if (tid == 0) {
-      sm.meta[stage].t = -1;
+      sm.meta[mslot].t = -1;
     }
     cp_async_commit();
+    return more;
+  };
+  // The K rows of round `round` (and everything else requested with them by the
+  // threads themselves) have landed.
+  auto rows_landed = [&](int round) {
+    if (tma_mode != kTmaNone && !mbar_wait(smem_u32(&sm.bar_in[0]), (uint32_t)round & 1u)) dead = true;
+    cp_async_wait<0>();
   };
 
   // ------------------------------------------------------------------ consumer state
   float m_run[8], l_run[8], o[8];  // l_run: this thread's token share of the denominators; o: head-dim index tid
   int piece_t0 = 0;
-  bool dead = false;  // a wait ran out
   const float unit2 = a.sm_scale * kLog2e;
   const uint32_t bar_s = smem_u32(&sm.bar[0]), bar_o = smem_u32(&sm.bar[1]);
-  const uint32_t q_desc_addr = smem_u32(&sm.qlev[0]), p_desc_addr = smem_u32(&sm.plev[0]);
+  const uint32_t q_desc_addr = smem_u32(&sm.qlev[0]), p_desc_addr = smem_u32(&sm.plev[0][0]);
+  const uint32_t k_addr = smem_u32(&sm.k[0]);
   // this thread's byte of row r of the probability levels: ((tid / 16) ^ r) * 16 + tid % 16.
   // plev is 1024-byte aligned, so the XOR with r << 4 can be applied to the whole address.
   uint32_t p_row[8];
 #pragma unroll
   for (int r = 0; r < 8; ++r)
-    p_row[r] = (smem_u32(&sm.plev[0]) + (tid & 15) + ((uint32_t)(tid >> 4) << 4)) ^ (uint32_t)(r << 4);
+    p_row[r] = (smem_u32(&sm.plev[0][0]) + (tid & 15) + ((uint32_t)(tid >> 4) << 4)) ^ (uint32_t)(r << 4);
 
-  // Query levels of the piece that starts with the tile in `st` (when it
-  // starts one), then S^T of that tile on the tensor core.  Called by the whole
-  // CTA once the tile's rows have landed and a barrier has made them (and the
-  // record) visible; the logits of the tile before are out of tensor memory.
-  auto prepare = [&](int st, const TileMeta& mt, bool first) {
+  // Query levels of the piece that starts with the tile of record `mt` (when it
+  // starts one), then S^T of that tile (one MMA group per half that holds a
+  // token) on the tensor core.  Called by the whole CTA once the tile's K rows
+  // have landed and a barrier has made them (and the record) visible; the
+  // logits of the tile before are out of tensor memory.
+  auto prepare = [&](const TileMeta& mt, bool first) {
     if (first || mt.t == 0) {
       // thread (row = tid / 16, chunk = tid % 16) converts 8 values of one query row
       const int row = tid >> 4, ch = tid & 15;
@@ -561,10 +668,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     }
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t k_addr = smem_u32(&sm.kv[st][0][0]);
+      const bool two = mt.pad[0] > kHalfU;
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma_i8(tmem, umma_desc(k_addr + 32 * ks), umma_desc(q_desc_addr + 32 * ks), kIdescS, ks > 0);
+      if (two) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_i8(tmem + kColS1, umma_desc(k_addr + kHalfU * kD + 32 * ks), umma_desc(q_desc_addr + 32 * ks), kIdescS,
+                  ks > 0);
+      }
       umma_commit(bar_s);
     }
   };
@@ -572,40 +685,38 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
   auto add_output = [&](uint32_t parity, const float (&alpha)[8], float cmax) {
     if (!mbar_wait(bar_o, parity)) dead = true;
     tc_fence_after();
-    uint32_t o01[16], o2[8];
-    tmem_ld16(tmem_lane + kColO, o01);
-    tmem_ld8(tmem_lane + kColO + 16, o2);
+    uint32_t oo[16];
+    tmem_ld16(tmem_lane + kColO, oo);
     tmem_ld_wait();
     tc_fence_before();
-    const float oscale = cmax * (1.f / 16777215.f);
+    const float oscale = cmax * (1.f / 65535.f);
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const float t01 = (float)((int)o01[r] + ((int)o01[8 + r] << 8));
-      o[r] = fmaf(o[r], alpha[r], fmaf((float)(int)o2[r], oscale * 65536.f, t01 * oscale));
-    }
+    for (int r = 0; r < 8; ++r)
+      o[r] = fmaf(o[r], alpha[r], (float)((int)oo[r] + ((int)oo[8 + r] << 8)) * oscale);
   };
 
   // The tensor core works one step ahead of the threads: S^T of tile i+1 is
   // issued at the end of iteration i, and O^T of tile i is collected in
   // iteration i+1 (at once only when tile i ends a piece), so neither MMA is
   // waited for right after it was issued.
-  produce(0);
-  cp_async_wait<0>();
+  bool more = produce(0, 0);
+  if (more) rows_landed(0);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   TileMeta mt = sm.meta[0];
   JPT_SPAN(3);
-  if (mt.t >= 0) prepare(0, mt, true);
+  if (mt.t >= 0) prepare(mt, true);
 
   float alpha_prev[8], cmax_prev = 0.f;
   bool pending = false;  // O^T of the tile before has not been added yet
-  int stage = 0;
   for (int i = 0; mt.t >= 0; ++i) {
-    const float cks = nks, cvs = nvs;  // scales of this thread's token in the tile of `stage`
-    const int next_stage = stage ^ 1;
+    const float cks0 = nks0, cvs0 = nvs0, cks1 = nks1, cvs1 = nvs1;  // scales of this thread's tokens in this tile
+    const int vstage = i & 1;
     const bool last_of_share = mt.pad[2] != 0;
     const uint32_t par = (uint32_t)i & 1u;
+    const int left = mt.pad[0];  // valid rows of this tile
+    const bool two = left > kHalfU;
     if (i == 0 || mt.t == 0) {  // a piece starts (the one before was flushed when it ended)
       piece_t0 = mt.t;
 #pragma unroll
@@ -617,51 +728,52 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
     }
 
     // ---------------- the output of the tile before and the logits of this one leave
-    // tensor memory in one round trip; the stage of the tile before is free after that
+    // tensor memory in one round trip; the K buffer and the V stage of the tile before
+    // are free after that
     if (!mbar_wait(bar_s, par)) dead = true;
     if (pending && !mbar_wait(bar_o, par ^ 1u)) dead = true;
     tc_fence_after();
-    float xv[8];
+    float x0[8], x1[8];
     {
-      uint32_t s[16];
+      uint32_t s0[16], s1[16];
       if (pending) {
-        uint32_t o01[16], o2[8];
-        tmem_ld16(tmem_lane + kColO, o01);
-        tmem_ld8(tmem_lane + kColO + 16, o2);
-        tmem_ld16(tmem_lane, s);
+        uint32_t oo[16];
+        tmem_ld16(tmem_lane + kColO, oo);
+        tmem_ld16(tmem_lane, s0);
+        if (two) tmem_ld16(tmem_lane + kColS1, s1);
         tmem_ld_wait();
-        const float oscale = cmax_prev * (1.f / 16777215.f), oscale2 = oscale * 65536.f;
+        const float oscale = cmax_prev * (1.f / 65535.f);
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          // levels 0 and 1 combine exactly in int32 (|O_0 + 256 O_1| < 2^31)
-          const float t01 = (float)((int)o01[r] + ((int)o01[8 + r] << 8));
-          o[r] = fmaf(o[r], alpha_prev[r], fmaf((float)(int)o2[r], oscale2, t01 * oscale));
-        }
+        for (int r = 0; r < 8; ++r)  // the two levels combine exactly in int32
+          o[r] = fmaf(o[r], alpha_prev[r], (float)((int)oo[r] + ((int)oo[8 + r] << 8)) * oscale);
         pending = false;
       } else {
-        tmem_ld16(tmem_lane, s);
+        tmem_ld16(tmem_lane, s0);
+        if (two) tmem_ld16(tmem_lane + kColS1, s1);
         tmem_ld_wait();
       }
-      produce(next_stage);
-      const bool valid = mt.t * kTileU + tid < mt.n;
-      float mk = valid ? 0.f : -INFINITY;  // a token past the end: finite dot product + (-inf)
-      if (mt.use_add && valid) {  // additive mask that is not a plain 0 / -inf range (rare)
-        SeqRange rg;
-        rg.n = mt.n;
-        rg.first = mt.first;
-        mk = kLog2e * __bfloat162float(mask[(int64_t)mt.b * a.mk_b + physical_pos(a, rg, mt.t * kTileU + tid)]);
+      more = produce(vstage ^ 1, (i + 1) & 1);
+      const bool valid0 = tid < left, valid1 = kHalfU + tid < left;
+      float mk0 = valid0 ? 0.f : -INFINITY, mk1 = valid1 ? 0.f : -INFINITY;  // past the end: finite dot product + (-inf)
+      if (mt.use_add) {  // additive mask that is not a plain 0 / -inf range (rare)
+        const int64_t mrow = (int64_t)mt.b * a.mk_b + mt.pad[1];
+        if (valid0) mk0 = kLog2e * __bfloat162float(mask[mrow + tid]);
+        if (valid1) mk1 = kLog2e * __bfloat162float(mask[mrow + kHalfU + tid]);
       }
       const float4 q0 = *reinterpret_cast<const float4*>(&sm.qsc[0]), q1 = *reinterpret_cast<const float4*>(&sm.qsc[4]);
-      const float qc[8] = {q0.x * cks, q0.y * cks, q0.z * cks, q0.w * cks, q1.x * cks, q1.y * cks, q1.z * cks, q1.w * cks};
+      const float qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-      for (int r = 0; r < 8; ++r) xv[r] = fmaf((float)((int)s[r] * 254 + (int)s[8 + r]), qc[r], mk);
+      for (int r = 0; r < 8; ++r) {
+        x0[r] = fmaf((float)((int)s0[r] * 254 + (int)s0[8 + r]), qs[r] * cks0, mk0);
+        x1[r] = two ? fmaf((float)((int)s1[r] * 254 + (int)s1[8 + r]), qs[r] * cks1, mk1) : -INFINITY;
+      }
     }
-    // tile maxima per row (and the largest V scale) across the 128 tokens
+    // tile maxima per row (and the largest V scale) across the 256 tokens
     {
       float wm[9];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) wm[r] = warp_max(xv[r]);
-      wm[8] = warp_max(cvs);
+      for (int r = 0; r < 8; ++r) wm[r] = warp_max(fmaxf(x0[r], x1[r]));
+      wm[8] = warp_max(fmaxf(cvs0, cvs1));
       if (lane == 0) {
         *reinterpret_cast<float4*>(&sm.xch[warp][0]) = make_float4(wm[0], wm[1], wm[2], wm[3]);
         *reinterpret_cast<float4*>(&sm.xch[warp][4]) = make_float4(wm[4], wm[5], wm[6], wm[7]);
@@ -691,20 +803,33 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
       tm[6] = fmaxf(fmaxf(t1[0].z, t1[1].z), fmaxf(t1[2].z, t1[3].z));
       tm[7] = fmaxf(fmaxf(t1[0].w, t1[1].w), fmaxf(t1[2].w, t1[3].w));
       // p <= 1 and the ratio is held at 1 (the fast division may land one ulp above), so
-      // the product stays below 2^24 without a clamp per row
-      const float pscale = cmax > 0.f ? fminf(__fdividef(cvs, cmax), 1.f) * 16777215.f : 0.f;
-      softmax_rows<0>(m_run, l_run, alpha, tm, xv, pscale, p_row);
+      // the product stays below 2^16 without a clamp per row
+      const float rc = cmax > 0.f ? __fdividef(65535.f, cmax) : 0.f;
+      const float ps0 = fminf(cvs0 * rc, 65535.f), ps1 = fminf(cvs1 * rc, 65535.f);
+      if (two) {
+        softmax_rows<0, true>(m_run, l_run, alpha, tm, x0, x1, ps0, ps1, p_row);
+      } else {
+        softmax_rows<0, false>(m_run, l_run, alpha, tm, x0, x1, ps0, ps1, p_row);
+      }
     }
     fence_async_smem();
     __syncthreads();
 
     // ---------------- O^T = V^T Pl^T on the tensor core
     if (tid == 0) {
+      // V rows of this tile were requested a round ago (stage `vstage` takes rounds vstage, vstage + 2, ...)
+      if (tma_mode != kTmaNone && !mbar_wait(smem_u32(&sm.bar_in[1 + vstage]), (uint32_t)(i >> 1) & 1u)) dead = true;
       tc_fence_after();
-      const uint32_t v_addr = smem_u32(&sm.kv[stage][1][0]);
+      const uint32_t v_addr = smem_u32(&sm.v[vstage][0]);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma_i8(tmem + kColO, umma_desc(v_addr + 4096 * ks), umma_desc(p_desc_addr + 32 * ks), kIdescO, ks > 0);
+      if (two) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_i8(tmem + kColO, umma_desc(v_addr + kHalfU * kD + 4096 * ks), umma_desc(p_desc_addr + 2048 + 32 * ks),
+                  kIdescO, 1u);
+      }
       umma_commit(bar_o);
     }
 
@@ -763,34 +888,36 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
         __syncthreads();
         if (sm.flag) {
           __threadfence();
-          // both MMAs of this stage are complete, so its K rows (16 KB) are free
-          merge_segment(a, x, mt.first_cta, mt.parts, row_base, reinterpret_cast<float*>(&sm.kv[stage][0][0]));
+          // the O^T MMA of this tile is complete, so its V stage (64 KB) is free; the next
+          // tile's V rows go to the other stage
+          merge_segment(a, x, mt.first_cta, mt.parts, row_base, reinterpret_cast<float*>(&sm.v[vstage][0]));
         }
       }
     }
 
     // ---------------- the next tile: its rows have had the iteration to land
-    cp_async_wait<0>();
+    if (more) rows_landed(i + 1);
     fence_async_smem();
     tc_fence_before();
     if (__syncthreads_or(dead)) {
       if (tid == 0) atomicExch(status, 1);
+      // give a copy-engine request that may still be in flight its (bounded) time to finish
+      if (more && tma_mode != kTmaNone) {
+        mbar_wait(smem_u32(&sm.bar_in[0]), (uint32_t)(i + 1) & 1u);
+        mbar_wait(smem_u32(&sm.bar_in[1 + ((i + 1) & 1)]), (uint32_t)((i + 1) >> 1) & 1u);
+      }
       break;
     }
-    mt = sm.meta[next_stage];
-    if (mt.t >= 0) prepare(next_stage, mt, false);
-    stage = next_stage;
+    mt = sm.meta[(i + 1) & 1];
+    if (mt.t >= 0) prepare(mt, false);
     if (i == 0) JPT_SPAN(4);
 #ifdef JPT_UMMA_SPANS
-    if (threadIdx.x == 0 && blockIdx.x < 1024) {
-      g_umma_spans[8 * blockIdx.x + 6] += 1;                                  // tiles
-      if (i == 0 || sm.meta[stage ^ 1].t >= 0) g_umma_spans[8 * blockIdx.x + 7] += (mt.t == 0);  // pieces started after the first
-    }
+    if (threadIdx.x == 0 && blockIdx.x < 1024) g_umma_spans[8 * blockIdx.x + 6] += 1;  // tiles
 #endif
   }
   JPT_SPAN(5);
   clear_empty_rows();
-  cp_async_wait<0>();
+  cp_async_wait<0>();  // (a copy-engine request is never left in flight: every issued tile was waited for)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -799,6 +926,98 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) flash_decode_i8_umma_ker
 }
 
 int umma_num_ctas() { return sm_count() * kCtasPerSm; }
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// [dims[3]][dims[2]][dims[1]][128] bytes with byte strides str[0..2] between rows / dims[2] / dims[3].
+bool encode_rows_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&str)[3], int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint32_t box[4] = {(cuuint32_t)kD, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, str, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+  const void *k, *v;
+  int64_t d1, d2, d3, s0, s1, s2;
+  int mode, big_rows, device;
+  bool operator==(const MapKey& o) const {
+    return k == o.k && v == o.v && d1 == o.d1 && d2 == o.d2 && d3 == o.d3 && s0 == o.s0 && s1 == o.s1 && s2 == o.s2 &&
+           mode == o.mode && big_rows == o.big_rows && device == o.device;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  TmaMaps maps;
+};
+
+// Tensor maps for this call (cached per tensor pair and geometry); kTmaNone when
+// the layout cannot be described (the kernel then copies the rows with its threads).
+int tensor_maps_for(const jpt_attn_params& p, TmaMaps* out, int* big_rows) {
+  static const bool off = [] {
+    const char* e = getenv("JPT_NO_TMA");
+    return e && e[0] == '1';
+  }();
+  if (off) return kTmaNone;
+  MapKey key{};
+  key.k = p.k;
+  key.v = p.v;
+  key.device = current_device();
+  if (p.paged) {
+    if (p.page_size % 32 != 0 || p.kv_page != (int64_t)p.page_size * kD || p.kv_h <= 0 || p.kv_h % p.kv_page != 0) return kTmaNone;
+    if ((kTileU % p.page_size) != 0 && (p.page_size % kTileU) != 0) return kTmaNone;
+    key.mode = kTmaPaged;
+    key.big_rows = p.page_size < kTileU ? p.page_size : kTileU;
+    key.d1 = p.page_size; key.d2 = p.kv_h / p.kv_page; key.d3 = p.Hkv;
+    key.s0 = kD; key.s1 = p.kv_page; key.s2 = p.kv_h;
+  } else {
+    key.mode = kTmaDense;
+    key.big_rows = kTileU;
+    key.d1 = p.S; key.d2 = p.Hkv; key.d3 = p.B;
+    key.s0 = p.kv_s; key.s1 = p.kv_h; key.s2 = p.kv_b;
+    if (p.Hkv == 1 && key.s1 <= 0) key.s1 = key.s0 * p.S;  // a single head: its stride is never used
+    if (p.B == 1 && key.s2 <= 0) key.s2 = key.s1 * p.Hkv;
+  }
+  if (key.s0 % 16 || key.s1 % 16 || key.s2 % 16 || key.s0 < kD || key.s1 <= 0 || key.s2 <= 0) return kTmaNone;
+  if (!aligned(p.k, 16) || !aligned(p.v, 16)) return kTmaNone;
+  *big_rows = key.big_rows;
+  static std::mutex mu;
+  static std::vector<MapEntry> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const MapEntry& e : cache) {
+    if (e.key == key) {
+      *out = e.maps;
+      return key.mode;
+    }
+  }
+  const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)key.d1, (cuuint64_t)key.d2, (cuuint64_t)key.d3};
+  const cuuint64_t str[3] = {(cuuint64_t)key.s0, (cuuint64_t)key.s1, (cuuint64_t)key.s2};
+  MapEntry e;
+  e.key = key;
+  if (!encode_rows_map(&e.maps.k_big, p.k, dims, str, key.big_rows) || !encode_rows_map(&e.maps.v_big, p.v, dims, str, key.big_rows) ||
+      !encode_rows_map(&e.maps.k_rows32, p.k, dims, str, 32) || !encode_rows_map(&e.maps.v_rows32, p.v, dims, str, 32))
+    return kTmaNone;
+  if (cache.size() >= 4096) cache.clear();
+  cache.push_back(e);
+  *out = e.maps;
+  return key.mode;
+}
 
 }  // namespace
 
@@ -828,7 +1047,7 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   if (int rc = configure_once_per_device(configured, "flash_decode_i8_umma_kernel", [] {
         cudaError_t e = cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              smem_bytes);
-        if (e == cudaSuccess)  // three CTAs of 75 KB per SM
+        if (e == cudaSuccess)  // two CTAs of 105 KB per SM
           e = cudaFuncSetAttribute(flash_decode_i8_umma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                    (int)cudaSharedmemCarveoutMaxShared);
         return e;
@@ -837,7 +1056,12 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   if (a.mask_mode == JPT_MASK_ADD) {
     if (int rc = launch_mask_ranges(a, x, st)) return rc;
   }
-  launch_after_previous(flash_decode_i8_umma_kernel, dim3(lay.num_ctas), dim3(kThreads), smem_bytes, st, a, x, status);
+  TmaMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  int big_rows = kTileU;
+  const int tma_mode = tensor_maps_for(p, &maps, &big_rows);
+  launch_after_previous(flash_decode_i8_umma_kernel, dim3(lay.num_ctas), dim3(kThreads), smem_bytes, st, a, x, status, maps,
+                        tma_mode, big_rows);
   return check_launch("flash_decode_i8_umma_kernel");
 }
 

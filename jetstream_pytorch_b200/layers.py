@@ -49,9 +49,13 @@ class _AttentionKernelBase:
           xq=xq, keys=keys, values=values, layer=self.layer_id, k_scaler=k_scaler, v_scaler=v_scaler,
           mask=local_mask)
     elif paged and seqlen == 1:
+      # the engine's paged driver leaves device copies of the tables behind (no host copy per layer)
+      pam = cache.page_attention_manager
+      lengths = getattr(pam, "lengths_device", None)
+      table = getattr(pam, "page_indices_device", None)
       local_output = self.page_attention(env, torch.squeeze(xq, 2), keys, values,
-                                         cache.page_attention_manager.lengths,
-                                         cache.page_attention_manager.page_indices)
+                                         pam.lengths if lengths is None else lengths,
+                                         pam.page_indices if table is None else table)
     else:
       local_output = self.dense_attention(xq=xq, keys=keys, values=values, k_scaler=k_scaler,
                                           v_scaler=v_scaler, mask=local_mask)

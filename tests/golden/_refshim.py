@@ -367,7 +367,14 @@ def install():
   jnp.squeeze = lambda x, axis=None: JTensor.wrap(
       x.squeeze() if axis is None else x.squeeze(axis)
   )
-  jnp.expand_dims = lambda x, axis: JTensor.wrap(x.unsqueeze(axis))
+  def expand_dims(x, axis):
+    for ax in sorted(axis) if isinstance(axis, (tuple, list)) else (axis,):
+      x = x.unsqueeze(ax)
+    return JTensor.wrap(x)
+
+  jnp.expand_dims = expand_dims
+  jnp.broadcast_to = lambda x, shape: JTensor.wrap(x.expand(*shape))
+  jnp.ones_like = lambda x, **k: JTensor.wrap(torch.ones_like(_t(x)))
   jnp.transpose = lambda x, axes: JTensor.wrap(x.permute(*axes))
   def _t(x):
     return x.value if isinstance(x, Ref) else x

@@ -408,6 +408,54 @@ def gen_engine_insert(eng, pam_mod):
   save("engine_insert", out)
 
 
+def gen_engine_step(eng):
+  """`PyTorchEngine.generate_impl` (engine.py:751-848) and
+  `precompute_ragged_block_indices` (674-729) for three consecutive steps, with
+  the model call replaced by a stand-in that returns fixed logits: what is
+  recorded is the bookkeeping around the model (mask, positions, lengths, the
+  result-token block, the block-skipping tables) and what the model was given."""
+  W = _refshim.JTensor.wrap
+  out = {}
+  b, s, bk, vocab, steps = 4, 32, 8, 10, 3
+  eng.engine_api.ResultTokens = lambda **kw: types.SimpleNamespace(**kw)
+  out["geometry"] = np.asarray([b, s, bk, vocab, steps])
+  for name, ring in (("ring", True), ("left", False)):
+    env = types.SimpleNamespace(
+        ring_buffer=ring, cache_sequence_length=s, cache_len=s, block_size=bk, batch_size=b,
+        lazy_cache_update=not ring, page_attention=False, generate_cache_stacked=False,
+        quant_config=types.SimpleNamespace(enable_kv_quantization=False))
+    me = types.SimpleNamespace(env=env)
+    me.precompute_ragged_block_indices = functools_partial(eng.PyTorchEngine.precompute_ragged_block_indices, me)
+    seen = []
+
+    def call_model(params, tokens, input_indexes, caches, scales, mask, start, input_pos, rbi, rbk, pti):
+      seen.append((plain(torch.as_tensor(input_indexes)), plain(mask), plain(rbi), plain(rbk)))
+      logits = torch.zeros(b, 1, vocab)
+      logits[torch.arange(b), 0, (tokens[:, 0].long() * 3 + 1) % vocab] = 1
+      return W(logits), caches, scales
+
+    me._call_model_generate = call_model
+    state = eng.DecodeState(
+        W(torch.tensor([[1], [2], [3], [4]], dtype=torch.int32)), [], [], 30,
+        W(torch.tensor([[1], [0], [3], [2]], dtype=torch.int32)), W(torch.tensor([30, 0, 3, 7], dtype=torch.int32)),
+        W(torch.tensor([6, 0, 29, 9], dtype=torch.int32)), W(torch.full((b, s), float("-inf"))))
+    for n, t in (("tokens", state.tokens), ("lens", state.lens), ("start", state.start),
+                 ("input_pos", state.input_pos), ("mask", state.mask)):
+      out[f"{name}_in_{n}"] = plain(t)
+    out[f"{name}_in_current_position"] = np.int64(state.current_position)
+    sampler = lambda logits: W(logits.argmax(-1).reshape(b, 1).to(torch.int32))
+    for step in range(steps):
+      state, res = eng.PyTorchEngine.generate_impl(me, None, state, sampler=sampler)
+      pre = f"{name}_step{step}_"
+      out[pre + "tokens"], out[pre + "lens"] = plain(state.tokens), plain(state.lens)
+      out[pre + "input_pos"], out[pre + "mask"] = plain(state.input_pos), plain(state.mask)
+      out[pre + "current_position"] = np.int64(state.current_position)
+      out[pre + "data"] = plain(res.data)
+      out[pre + "model_input_indexes"], out[pre + "model_mask"] = seen[-1][0], seen[-1][1]
+      out[pre + "ragged_batch_index"], out[pre + "ragged_block_index"] = seen[-1][2], seen[-1][3]
+  save("engine_step", out)
+
+
 def functools_partial(fn, first):
   return lambda *a: fn(first, *a)
 
@@ -423,7 +471,9 @@ def main():
   gen_pages(cm, pam)
   gen_attention(ak, q)
   gen_ragged(ak)
-  gen_engine_insert(_refshim.import_reference_engine(ref), pam)
+  eng = _refshim.import_reference_engine(ref)
+  gen_engine_insert(eng, pam)
+  gen_engine_step(eng)
   print("golden fixtures written")
 
 

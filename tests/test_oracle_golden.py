@@ -222,6 +222,33 @@ def test_engine_insert_bit_exact():
   assert torch.equal(oi.insert_mask_row(s, 0, seq_len, False), g["paged_out_mask"][slot])
 
 
+def test_engine_step_bookkeeping_matches_reference():
+  """`engine_step.npz`: three decode steps of the reference's `generate_impl`
+  with a stand-in model, ring buffer and left aligned."""
+  from oracle import engine as oe
+
+  g = load("engine_step")
+  b, s, bk, vocab, steps = (int(v) for v in g["geometry"])
+  for name, ring in (("ring", True), ("left", False)):
+    tokens, lens = g[f"{name}_in_tokens"].numpy(), g[f"{name}_in_lens"].numpy()
+    start, ipos = g[f"{name}_in_start"].numpy(), g[f"{name}_in_input_pos"].numpy()
+    mask, cur = g[f"{name}_in_mask"].numpy(), int(g[f"{name}_in_current_position"])
+    for step in range(steps):
+      pre = f"{name}_step{step}_"
+      rb, ri = oe.ragged_block_indices(start, ipos, s, bk)
+      assert np.array_equal(rb.reshape(-1), g[pre + "ragged_batch_index"].numpy())
+      assert np.array_equal(ri.reshape(-1), g[pre + "ragged_block_index"].numpy())
+      nxt = g[pre + "tokens"].numpy()
+      model_mask, mask, ipos, lens, cur, data = oe.decode_step_bookkeeping(ring, not ring, s, tokens, lens, ipos, mask,
+                                                                           cur, nxt)
+      assert np.array_equal(model_mask, g[pre + "model_mask"].numpy().reshape(b, s))
+      assert np.array_equal(mask, g[pre + "mask"].numpy())
+      assert np.array_equal(ipos, g[pre + "input_pos"].numpy()) and np.array_equal(lens, g[pre + "lens"].numpy())
+      assert cur == int(g[pre + "current_position"])
+      assert np.array_equal(data, g[pre + "data"].numpy())
+      tokens = nxt
+
+
 def test_ragged_restatement_consistent_with_pinned_dense():
   """The unpinned ragged restatements agree with the pinned flash_attention on
   the same valid set (left aligned and ring wrap)."""
