@@ -305,6 +305,11 @@ typedef struct jpt_attn_params {
   size_t workspace_bytes;
   int num_splits;       /* split-K factor; 0 = choose automatically */
   int force_generic;    /* testing: 1 = always the scalar kernel, 2 = the mma.sync kernel instead of the tcgen05 one */
+  /* 1: round every logit to bf16 after each step of dense_attention's chain
+   * (q.k, / sqrt(D), * k_scale, + mask), as the reference's bf16 tensors do
+   * (jetstream_pt/attention_kernel.py:611-616); the softmax stays in fp32.
+   * 0: fp32 logits (flash_attention, the ragged kernels, paged attention). */
+  int logit_rounding;
 } jpt_attn_params;
 
 /*
@@ -362,6 +367,49 @@ int jpt_flash_decode_status(const void* workspace, void* stream);
  *     one stream are safe.
  */
 int jpt_flash_decode_static(const jpt_attn_params* p, void* stream);
+
+/*
+ * One launch for a decode step's cache update AND attention: the new token of
+ * every slot is quantised with the decode quantiser (as
+ * jpt_kv_quant_append_dense does), written to the cache row / scale cache and
+ * the stash outputs, and attended to together with the tokens already in the
+ * cache.  Replaces the pair Int8KVCacheGenerate.update + ragged attention that
+ * Int8KVAttentionKernel issues per layer (jetstream_pt/layers.py:676-706), and
+ * with write_cache = 0 the lazy form of it (stash only, existing + new merged,
+ * layers.py:708-718).
+ *
+ *   p        as for jpt_flash_decode; int8 dense cache, head_dim 128, at most 8
+ *            grouped query rows, JPT_MASK_LENGTH or JPT_MASK_RING, scales
+ *            given.  start / end describe the tokens ALREADY in the cache (the
+ *            new token is not part of that range).  p->k, p->v, p->k_scale,
+ *            p->v_scale are written at `pos` when write_cache is set.
+ *   nt       the new token.  px = NULL: unsharded cache (the amax passes through
+ *            the workspace); px != NULL: KV heads sharded over px->world GPUs,
+ *            the amax is max-reduced over NVLink inside the launch exactly as
+ *            jpt_kv_quant_append_dense_peers does, but the round trip is hidden
+ *            under the attention over the existing tokens.  A launch of this
+ *            function and a launch of jpt_kv_quant_append_dense_peers on the same
+ *            exchange buffers both count as one step of the exchange.
+ * Returns JPT_EINVAL for shapes the fused kernel does not take (use the two
+ * separate calls then).  Codes, scales and cache contents are bit-identical to
+ * the separate update; attention rows agree within rounding.
+ */
+typedef struct jpt_new_token {
+  const void* xk;   /* [B,Hkv,1,D] contiguous, in_dtype */
+  const void* xv;
+  int in_dtype;     /* JPT_BF16 or JPT_F32: also the dtype of the scale caches and scale outputs */
+  int write_cache;  /* 1: write codes and scale at pos; 0: only the stash outputs */
+  int8_t* k_quant;  /* [B,Hkv,1,D] out, may be NULL */
+  int8_t* v_quant;
+  void* k_scale;    /* [B] out (in_dtype), may be NULL */
+  void* v_scale;
+  const int32_t* pos; /* as in jpt_kv_quant_append_dense */
+  int pos_count;
+  int pos_host;
+  const jpt_peer_exchange* px;
+} jpt_new_token;
+
+int jpt_decode_update_attend(const jpt_attn_params* p, const jpt_new_token* nt, void* stream);
 
 /*
  * Merge two softmax partials: g = max(m1,m2); o = (l1 e^{m1-g} o1 + l2 e^{m2-g}

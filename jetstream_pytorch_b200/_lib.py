@@ -51,8 +51,16 @@ class AttnParams(ctypes.Structure):
       ("sm_scale", c_float),
       ("o", c_void_p), ("m", c_void_p), ("l", c_void_p),
       ("workspace", c_void_p), ("workspace_bytes", c_size_t),
-      ("num_splits", c_int), ("force_generic", c_int),
+      ("num_splits", c_int), ("force_generic", c_int), ("logit_rounding", c_int),
   ]
+
+
+class NewTokenStruct(ctypes.Structure):
+  """Mirror of `struct jpt_new_token`."""
+  _fields_ = [("xk", c_void_p), ("xv", c_void_p), ("in_dtype", c_int), ("write_cache", c_int),
+              ("k_quant", c_void_p), ("v_quant", c_void_p), ("k_scale", c_void_p), ("v_scale", c_void_p),
+              ("pos", c_void_p), ("pos_count", c_int), ("pos_host", c_int),
+              ("px", ctypes.POINTER(PeerExchangeStruct))]
 
 
 _SIGNATURES = {
@@ -85,6 +93,7 @@ _SIGNATURES = {
     "jpt_quantize_tokens": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "jpt_flash_decode": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
     "jpt_flash_decode_static": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
+    "jpt_decode_update_attend": (c_int, [ctypes.POINTER(AttnParams), ctypes.POINTER(NewTokenStruct), c_void_p]),
     "jpt_flash_decode_workspace_bytes": (c_size_t, [ctypes.POINTER(AttnParams)]),
     "jpt_flash_decode_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "jpt_flash_decode_status": (c_int, [c_void_p, c_void_p]),

@@ -19,27 +19,32 @@ from jetstream_pytorch_b200 import _lib
 
 DEFAULT_MASK_VALUE = -0.7 * float(np.finfo(np.dtype("float32")).max)
 
-_workspaces = {}  # (device, stream handle) -> grow-only scratch tensor
+_workspaces = {}  # (device, stream handle or None) -> grow-only scratch tensor
 
 
 def _workspace(device, nbytes):
-  """Grow-only attention scratch per (device, stream), allocated by torch and
-  owned here, cleared once when it is created as the kernel's arrival counters
-  require.  Two launches that share a workspace must not overlap on the GPU, so
-  every stream gets its own; a workspace cannot grow while its stream is being
-  captured into a CUDA graph (the allocation would land in the graph): run the
-  shape once before capturing."""
+  """Grow-only attention scratch, allocated by torch and owned here, cleared
+  once when it is created as the kernel's arrival counters require.
+
+  Two launches that share a workspace must not overlap on the GPU, so every
+  stream gets its own.  CUDA graph captures run on a stream of their own and
+  must not allocate: they use one more workspace per device (key `None`) that
+  every eager call keeps at least as large as its own, so a shape that ran once
+  eagerly can be captured.  Graphs captured on one device share that
+  workspace: replay them on one stream, or on streams ordered by events."""
+  capturing = torch.cuda.is_current_stream_capturing()
   stream = torch.cuda.current_stream(device)
-  key = (device, stream.cuda_stream)
-  ws = _workspaces.get(key)
-  if ws is None or ws.numel() < nbytes:
-    if torch.cuda.is_current_stream_capturing():
-      raise RuntimeError("the attention workspace of this stream is too small and cannot grow during CUDA graph "
-                         "capture; call the same shape once before capturing")
-    ws = torch.empty(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
-    _lib.check(_lib.lib().jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), stream.cuda_stream))
-    _workspaces[key] = ws
-  return ws
+  keys = [(device, None)] if capturing else [(device, stream.cuda_stream), (device, None)]
+  for key in keys:
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+      if capturing:
+        raise RuntimeError("the attention workspace for CUDA graphs is too small and cannot grow during capture; "
+                           "call the same shape once before capturing")
+      ws = torch.empty(max(nbytes, 8 << 20), dtype=torch.uint8, device=device)
+      _lib.check(_lib.lib().jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), stream.cuda_stream))
+      _workspaces[key] = ws
+  return _workspaces[keys[0]]
 
 
 def kernel_status(device=None):
@@ -56,12 +61,14 @@ def kernel_status(device=None):
       continue
     devices.add(dev)
     with torch.cuda.device(dev):
-      rc = lib.jpt_flash_decode_status(_lib.ptr(ws), stream)
+      torch.cuda.synchronize(dev)  # launches of any stream (and graph replays) have finished
+      on = stream if stream is not None else _lib.stream()
+      rc = lib.jpt_flash_decode_status(_lib.ptr(ws), on)
       if rc < 0:
         _lib.check(rc)
       if rc:
         worst = worst or rc
-        _lib.check(lib.jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), stream))
+        _lib.check(lib.jpt_flash_decode_workspace_init(_lib.ptr(ws), ws.numel(), on))
   if device is not None:
     devices.add(torch.device(device))
   elif not devices and torch.cuda.is_available():
@@ -78,9 +85,14 @@ def kernel_status(device=None):
 def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale=None, v_scale=None,
                   scale_strides=(0, 0), mask_mode=_lib.MASK_NONE, start=None, end=None, mask=None,
                   mask_strides=(0, 0), sm_scale=1.0, kv_strides=(0, 0, 0), n_kv_heads=None, seq=None,
-                  want_ml=True, num_splits=0, force_generic=False, static_scratch=False, out=None):
+                  want_ml=True, num_splits=0, force_generic=False, static_scratch=False, out=None,
+                  logit_rounding=False, new_token=None):
   """q [B,Hq,Tq,D] contiguous.  Returns o (q's shape and dtype), m, l float32
   [B,Hq,Tq] (or None, None).
+
+  `new_token` (a `_lib.NewTokenStruct`, optional) routes the call through
+  `jpt_decode_update_attend`: the step's new K/V token is quantised, written
+  and attended to in the same launch (see `Int8KVCacheGenerate.update_and_attend`).
 
   `out=(o, m, l)` (m, l may be None) makes the call write into tensors the
   caller already owns instead of creating new ones: a step loop that keeps its
@@ -100,7 +112,8 @@ def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale
                            v_scale=v_scale, scale_strides=scale_strides, mask_mode=mask_mode, start=start, end=end,
                            mask=mask, mask_strides=mask_strides, sm_scale=sm_scale, kv_strides=kv_strides,
                            n_kv_heads=n_kv_heads, seq=seq, want_ml=want_ml, num_splits=num_splits,
-                           force_generic=force_generic, static_scratch=static_scratch, out=out)
+                           force_generic=force_generic, static_scratch=static_scratch, out=out,
+                           logit_rounding=logit_rounding, new_token=new_token)
   for t in (k, v, k_scale, v_scale, mask):
     if t is not None and t.device != dev:
       raise ValueError(f"attention operands live on {t.device} and {dev}")
@@ -157,15 +170,21 @@ def _flash_decode(q, k, v, *, paged=False, page_table=None, page_size=0, k_scale
   if m is not None and l is not None:
     p.m, p.l = _lib.ptr(m), _lib.ptr(l)
   p.num_splits, p.force_generic = num_splits, int(force_generic)
+  p.logit_rounding = int(logit_rounding)
   lib = _lib.lib()
   if static_scratch:
+    if new_token is not None:
+      raise ValueError("the fused update needs a workspace that keeps its contents between calls")
     _lib.check(lib.jpt_flash_decode_static(ctypes.byref(p), _lib.stream()))
   else:
     need = lib.jpt_flash_decode_workspace_bytes(ctypes.byref(p))
     if need:
       ws = _workspace(dev, need)
       p.workspace, p.workspace_bytes = _lib.ptr(ws), ws.numel()
-    _lib.check(lib.jpt_flash_decode(ctypes.byref(p), _lib.stream()))
+    if new_token is not None:
+      _lib.check(lib.jpt_decode_update_attend(ctypes.byref(p), ctypes.byref(new_token), _lib.stream()))
+    else:
+      _lib.check(lib.jpt_flash_decode(ctypes.byref(p), _lib.stream()))
   del keep
   return o, m, l
 
@@ -235,15 +254,19 @@ def _mask_args(mask, q, s, n_kv_heads):
   return _lib.MASK_ADD, mask, (mk_b, mk_r)
 
 
-def dense_attention(xq, keys, values, k_scaler=None, v_scaler=None, mask=None):
+def dense_attention(xq, keys, values, k_scaler=None, v_scaler=None, mask=None, **kw):
   """attention_kernel.py:605-633: masked softmax attention over the whole cache
   row; `mask` holds 0 / -inf (or any additive values).  Returns [B,Hq,T,D]."""
   k, v, strides, hkv, s = _dense_kv(keys, values, 0)
   ks, vs, sst = _dense_scales(k_scaler, v_scaler, 0)
   mode, mask, mst = _mask_args(mask, xq, s, hkv)
+  # The reference computes the logits of this function as bf16 tensor operations when its
+  # inputs are bf16 (matmul, / sqrt(D), * k_scaler, + mask: four roundings); the kernels
+  # reproduce those roundings so that the softmax sees the same numbers.
   o, _, _ = _flash_decode(xq, k, v, k_scale=ks, v_scale=vs, scale_strides=sst, mask_mode=mode, mask=mask,
                           mask_strides=mst, sm_scale=1.0 / math.sqrt(xq.shape[-1]), kv_strides=strides,
-                          n_kv_heads=hkv, seq=s, want_ml=False)
+                          n_kv_heads=hkv, seq=s, want_ml=False, logit_rounding=xq.dtype == torch.bfloat16,
+                          **kw)
   return o
 
 

@@ -344,6 +344,85 @@ class Int8KVCacheGenerate:
           xk, xv, self.cache_k, self.cache_v, self.k_scaler, self.v_scaler, None, amax, peers)
     return (self.cache_k, self.cache_v, k_quant, v_quant, self.k_scaler, self.v_scaler, kscale, vscale)
 
+  def fused_step_supported(self, xq, xk):
+    """True when `update_and_attend` can run as ONE launch: dense int8 cache
+    (not the lazily finalised stacked stash of several layers at once), head_dim
+    128, one new token, at most 8 query rows per KV head."""
+    b, hq, tq, d = xq.shape
+    h = xk.shape[1]
+    return (d == 128 and tq == 1 and xk.shape[2] == 1 and hq % h == 0 and hq // h <= 8
+            and xk.dtype in (torch.bfloat16, torch.float32) and xq.dtype == torch.bfloat16
+            and self.k_scaler is not None and self.k_scaler.dtype == xk.dtype)
+
+  def update_and_attend(self, xq, xk, xv, layer_id: int, start, end, ring=False, peers=None, out=None):
+    """`update(xk, xv, layer_id)` and ragged attention of `xq` over the cache
+    INCLUDING the new token, as one kernel launch.
+
+    start, end: the valid range of the tokens already in the cache (the new
+    token is not part of it): [0, end) when `ring` is false, the ring range
+    [start, end) otherwise.  The new token is written at `input_pos` exactly as
+    `update` does (ring buffer: the shared position; left aligned: one position
+    per slot); with `env.lazy_cache_update` only the stash (`new_ks`, ...) is
+    written and `finalize` moves it into the cache later, as in the reference.
+    `peers` (a `PeerAmaxExchange`) shards the KV heads over GPUs; the amax
+    exchange then runs inside the same launch, hidden under the attention over
+    the existing tokens.
+
+    Returns (the 8-tuple `update` returns, (o [B,Hkv,rep,D], m, l [B,Hkv,rep])).
+    Codes, scales and cache contents equal those of `update` bit for bit; the
+    attention rows equal those of `update` followed by `ragged_mha` over the
+    extended range within rounding (the reference pair is
+    jetstream_pt/layers.py:676-718).  Falls back to those two calls for shapes
+    the fused kernel does not take."""
+    from jetstream_pytorch_b200 import attention_kernel as ak
+
+    env = self.env
+    if not self.fused_step_supported(xq, xk):
+      r = self.update(xk, xv, layer_id, peers=peers)
+      if env.lazy_cache_update:
+        raise ValueError("the unfused lazy step is the caller's: attend to the cache and to the new token, then merge")
+      end_all = torch.as_tensor(end).to(xq.device) + 1
+      o, ml = ak.ragged_mha(xq, r[0], r[1], layer_id, start, end_all, None, None, r[4], r[5], ring=ring, out=out)
+      return r, (o, ml[0], ml[1])
+    b, h, _, d = xk.shape
+    xk, xv = xk.contiguous(), xv.contiguous()
+    lazy = env.lazy_cache_update
+    stash = None
+    if lazy and env.new_cache_stacked:
+      stash = (self.new_ks[layer_id], self.new_vs[layer_id], self.new_k_scaler[layer_id], self.new_v_scaler[layer_id])
+      if stash[2].dtype != xk.dtype:
+        raise ValueError(f"scale buffers of dtype {stash[2].dtype} cannot take the scales of {xk.dtype} inputs")
+    if stash is None:
+      stash = (torch.empty((b, h, 1, d), dtype=torch.int8, device=xk.device),
+               torch.empty((b, h, 1, d), dtype=torch.int8, device=xk.device),
+               torch.empty((b, 1, 1, 1), dtype=xk.dtype, device=xk.device),
+               torch.empty((b, 1, 1, 1), dtype=xk.dtype, device=xk.device))
+    kq, vq, ks, vs = stash
+    cache_k, cache_v, k_scaler, v_scaler = self.cache_k, self.cache_v, self.k_scaler, self.v_scaler
+    if cache_k.ndim == 5:
+      cache_k, cache_v, k_scaler, v_scaler = cache_k[layer_id], cache_v[layer_id], k_scaler[layer_id], v_scaler[layer_id]
+    nt = _lib.NewTokenStruct()
+    nt.xk, nt.xv, nt.in_dtype = _lib.ptr(xk), _lib.ptr(xv), _lib.dt(xk)
+    nt.write_cache = 0 if lazy else 1
+    nt.k_quant, nt.v_quant, nt.k_scale, nt.v_scale = _lib.ptr(kq), _lib.ptr(vq), _lib.ptr(ks), _lib.ptr(vs)
+    p, n, host, keep = _pos_args(self.input_pos, xk.device, b)
+    nt.pos, nt.pos_count, nt.pos_host = p, n, host
+    if peers is not None:
+      nt.px = ctypes.pointer(peers.struct)
+    o, (m, l) = ak.ragged_mha(xq, cache_k, cache_v, 0, start, end, None, None, k_scaler, v_scaler, ring=ring, out=out,
+                              new_token=nt)
+    del keep
+    if lazy:
+      if not env.new_cache_stacked:
+        if env.generate_cache_stacked:
+          self.new_ks.append(kq)
+          self.new_vs.append(vq)
+          self.new_k_scaler.append(ks)
+          self.new_v_scaler.append(vs)
+        else:
+          self.new_ks, self.new_vs, self.new_k_scaler, self.new_v_scaler = kq, vq, ks, vs
+    return (self.cache_k, self.cache_v, kq, vq, self.k_scaler, self.v_scaler, ks, vs), (o, m, l)
+
   def finalize(self):
     """cache_manager.py:584-657."""
     env = self.env

@@ -31,7 +31,21 @@ struct AttnArgs {
   int mask_mode, scale_is_f32;
   int nsplit;
   float sm_scale;
+  int round_logits;  // dense_attention with bf16 tensors: every step of the logit chain is rounded to bf16
 };
+
+// dense_attention's logit chain on bf16 tensors (jetstream_pt/attention_kernel.py:611-616): the dot
+// product, the division by sqrt(D), the product with the K scale and the sum with the mask are
+// separate bf16 tensor operations there, each rounding its result.  `dot` is the fp32 dot product of
+// the unscaled query row and the K row, `ks` the K scale (1 when unquantised), `mask_value` the
+// additive mask entry (0 when there is none).
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float rounded_logit(float dot, float sqrt_d, float ks, bool quantised, float mask_value) {
+  float s = bf16_round(dot);
+  s = bf16_round(__fdiv_rn(s, sqrt_d));
+  if (quantised) s = bf16_round(s * ks);
+  return bf16_round(s + mask_value);
+}
 
 // Valid range of one sequence in "logical" token order: logical token j
 // (0 <= j < n) lives at physical position (first + j) mod S.
@@ -86,6 +100,26 @@ constexpr size_t kWorkspaceCounterBytes = 256 * 1024;  // header: counters, then
 constexpr size_t kWorkspaceStatusOffset = kWorkspaceCounterBytes - 256;
 constexpr size_t kWorkspaceMaxSegments = kWorkspaceStatusOffset / sizeof(unsigned);  // (sequence, head) pairs
 
+// The new token of a decode step, handed to the attention launch itself
+// (jpt_decode_update_attend): quantised with the decode quantiser, written to
+// the cache row and / or the stash outputs, and attended to together with the
+// existing tokens.  The per-token amax over all heads travels through exchange
+// slots: one 64-bit word (launch number << 32 | amax bits) per (K|V, slot) and
+// writer rank, in the buffers of a jpt_peer_exchange or (one GPU) in the
+// workspace.
+struct NewTokenArgs {
+  const void* x[2];        // xk, xv [B,Hkv,1,D]
+  int8_t* quant[2];        // [B,Hkv,1,D] out, may be null
+  void* scale_out[2];      // [B] out (input dtype), may be null
+  const int32_t* pos;      // where the token is written
+  int pos_count, pos_host;
+  unsigned long long* px_slots[8];  // slot area of each rank's exchange buffer (index = rank)
+  unsigned* px_state;               // this rank's {launches done, CTAs done, gave up}
+  int px_rank, px_world;
+  long long px_wait_cycles;
+  int enabled, in_f32, write_cache;
+};
+
 // Host-side launchers implemented by the individual kernels.
 int launch_attention_generic(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
 bool attention_mma_eligible(const jpt_attn_params& p);
@@ -96,7 +130,7 @@ int launch_attention_mma(const jpt_attn_params& p, const AttnArgs& a, cudaStream
 // int8 caches with up to 8 grouped query rows: the tcgen05 kernel.  Its scratch
 // fits in attention_mma_workspace_bytes().
 bool attention_umma_eligible(const jpt_attn_params& p);
-int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
+int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st, const NewTokenArgs* nt = nullptr);
 int launch_splitk_merge(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st);
 
 }  // namespace jpt

@@ -6,7 +6,7 @@
 
 #include <atomic>
 
-#include "attention_common.cuh"
+#include "attention_tiles.cuh"
 
 namespace jpt {
 namespace {
@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(kWarps * 32) flash_decode_generic_kernel(AttnA
   const TQ* q = static_cast<const TQ*>(a.q) + row_base * D;
   for (int i = threadIdx.x; i < kRowTile * D; i += blockDim.x) {
     const int r = i / D;
-    q_s[i] = r < nrows ? to_f32<TQ>(q[i]) * a.sm_scale : 0.f;
+    q_s[i] = r < nrows ? to_f32<TQ>(q[i]) * (a.round_logits ? 1.f : a.sm_scale) : 0.f;
   }
   __syncthreads();
 
@@ -81,9 +81,13 @@ __global__ void __launch_bounds__(kWarps * 32) flash_decode_generic_kernel(AttnA
         const int d = lane + 32 * i;
         if (d < D) s += q_s[r * D + d] * kk[i];
       }
-      s = warp_sum(s) * ks;
-      if (a.mask_mode == JPT_MASK_ADD) {
-        s += to_f32<TQ>(mask[(int64_t)b * a.mk_b + (int64_t)(r0 + r) * a.mk_r + p]);
+      s = warp_sum(s);
+      const float mask_value =
+          a.mask_mode == JPT_MASK_ADD ? to_f32<TQ>(mask[(int64_t)b * a.mk_b + (int64_t)(r0 + r) * a.mk_r + p]) : 0.f;
+      if (a.round_logits) {
+        s = rounded_logit(s, __frcp_rn(a.sm_scale), ks, a.k_scale != nullptr, mask_value);
+      } else {
+        s = s * ks + mask_value;
       }
       if (s == -INFINITY) continue;  // fully masked position
       const float mn = fmaxf(m[r], s);
@@ -277,22 +281,72 @@ extern "C" size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p) {
   return kWorkspaceCounterBytes + rows * ns * (p->D + 2) * sizeof(float);
 }
 
+static AttnArgs attn_args_of(const jpt_attn_params& p) {
+  AttnArgs a{};
+  a.q = p.q; a.k = p.k; a.v = p.v; a.k_scale = p.k_scale; a.v_scale = p.v_scale;
+  a.page_table = p.page_table; a.start = p.start; a.end = p.end; a.mask = p.mask;
+  a.o = p.o; a.m = p.m; a.l = p.l;
+  a.B = p.B; a.Hq = p.Hq; a.Hkv = p.Hkv; a.Tq = p.Tq; a.D = p.D; a.R = (p.Hq / p.Hkv) * p.Tq;
+  a.S = p.S; a.paged = p.paged; a.page_size = p.page_size; a.max_pages = p.max_pages;
+  a.kv_b = p.kv_b; a.kv_h = p.kv_h; a.kv_s = p.kv_s; a.kv_page = p.kv_page;
+  a.sc_b = p.sc_b; a.sc_s = p.sc_s; a.mk_b = p.mk_b; a.mk_r = p.mk_r;
+  a.mask_mode = p.mask_mode; a.scale_is_f32 = p.scale_dtype == JPT_F32;
+  a.sm_scale = p.sm_scale;
+  a.round_logits = p.logit_rounding != 0 && p.q_dtype == JPT_BF16;
+  return a;
+}
+
+extern "C" int jpt_decode_update_attend(const jpt_attn_params* pp, const jpt_new_token* nt, void* stream) {
+  JPT_REQUIRE(pp && nt, JPT_EINVAL, "decode_update_attend: null argument");
+  const jpt_attn_params& p = *pp;
+  if (int rc = validate(p)) return rc;
+  JPT_REQUIRE(p.force_generic == 0 && attention_umma_eligible(p) && !p.paged, JPT_EINVAL,
+              "decode_update_attend: needs a dense int8 cache with head_dim 128 and at most 8 grouped query rows");
+  JPT_REQUIRE(p.mask_mode == JPT_MASK_LENGTH || p.mask_mode == JPT_MASK_RING, JPT_EINVAL,
+              "decode_update_attend: the existing tokens are a length or a ring range");
+  JPT_REQUIRE(p.k_scale && p.v_scale, JPT_EINVAL, "decode_update_attend: an int8 cache needs its scales");
+  JPT_REQUIRE(nt->xk && nt->xv, JPT_EINVAL, "decode_update_attend: null new token");
+  JPT_REQUIRE(nt->in_dtype == JPT_BF16 || nt->in_dtype == JPT_F32, JPT_EINVAL,
+              "decode_update_attend: the new token must be bf16 or f32");
+  JPT_REQUIRE(p.scale_dtype == nt->in_dtype || !nt->write_cache, JPT_EINVAL,
+              "decode_update_attend: the scale caches must have the new token's dtype");
+  JPT_REQUIRE(nt->pos == nullptr || nt->pos_count == 1 || nt->pos_count == p.B, JPT_EINVAL,
+              "decode_update_attend: pos_count must be 1 or B");
+  NewTokenArgs n{};
+  n.x[0] = nt->xk; n.x[1] = nt->xv;
+  n.quant[0] = nt->k_quant; n.quant[1] = nt->v_quant;
+  n.scale_out[0] = nt->k_scale; n.scale_out[1] = nt->v_scale;
+  n.pos = nt->pos; n.pos_count = nt->pos_count; n.pos_host = nt->pos_host;
+  n.in_f32 = nt->in_dtype == JPT_F32;
+  n.write_cache = nt->write_cache != 0;
+  if (const jpt_peer_exchange* px = nt->px) {
+    JPT_REQUIRE(px->world >= 1 && px->world <= 8 && px->rank >= 0 && px->rank < px->world, JPT_EINVAL,
+                "decode_update_attend: rank %d of %d", px->rank, px->world);
+    JPT_REQUIRE(px->batch == p.B, JPT_EINVAL, "decode_update_attend: exchange buffers are sized for batch %d, not %d",
+                px->batch, p.B);
+    JPT_REQUIRE(px->wait_cycles >= 0, JPT_EINVAL, "decode_update_attend: negative wait limit");
+    for (int r = 0; r < px->world; ++r) {
+      JPT_REQUIRE(px->buffers[r] && aligned(px->buffers[r], 8), JPT_EINVAL,
+                  "decode_update_attend: buffer of rank %d missing or unaligned", r);
+      n.px_slots[r] = reinterpret_cast<unsigned long long*>(static_cast<char*>(px->buffers[r]) + kExchangeStateBytes);
+    }
+    n.px_state = static_cast<unsigned*>(px->buffers[px->rank]);
+    n.px_rank = px->rank;
+    n.px_world = px->world;
+    n.px_wait_cycles = px->wait_cycles;
+  }
+  AttnArgs a = attn_args_of(p);
+  a.nsplit = 1;
+  return launch_attention_umma(p, a, static_cast<cudaStream_t>(stream), &n);
+}
+
 extern "C" int jpt_flash_decode(const jpt_attn_params* pp, void* stream) {
   JPT_REQUIRE(pp, JPT_EINVAL, "flash_decode: null params");
   const jpt_attn_params& p = *pp;
   if (int rc = validate(p)) return rc;
   const int R = (p.Hq / p.Hkv) * p.Tq;
   const bool use_mma = p.force_generic != 1 && attention_mma_eligible(p);
-  AttnArgs a{};
-  a.q = p.q; a.k = p.k; a.v = p.v; a.k_scale = p.k_scale; a.v_scale = p.v_scale;
-  a.page_table = p.page_table; a.start = p.start; a.end = p.end; a.mask = p.mask;
-  a.o = p.o; a.m = p.m; a.l = p.l;
-  a.B = p.B; a.Hq = p.Hq; a.Hkv = p.Hkv; a.Tq = p.Tq; a.D = p.D; a.R = R;
-  a.S = p.S; a.paged = p.paged; a.page_size = p.page_size; a.max_pages = p.max_pages;
-  a.kv_b = p.kv_b; a.kv_h = p.kv_h; a.kv_s = p.kv_s; a.kv_page = p.kv_page;
-  a.sc_b = p.sc_b; a.sc_s = p.sc_s; a.mk_b = p.mk_b; a.mk_r = p.mk_r;
-  a.mask_mode = p.mask_mode; a.scale_is_f32 = p.scale_dtype == JPT_F32;
-  a.sm_scale = p.sm_scale;
+  AttnArgs a = attn_args_of(p);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (use_mma) {
     a.nsplit = 1;

@@ -428,6 +428,7 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : (kBf16 ? 3 : 4))
   float m_run[NT][2], m_true[NT][2], l_run[NT][2];
   int piece_t0 = 0;
   const float unit2 = a.sm_scale * kLog2e;
+  const float inv_unit2 = 1.f / unit2, sqrt_d = __frcp_rn(a.sm_scale);  // used when the logit chain is rounded
   // shared-memory offsets of this thread's operands inside a stage
   const int tok0 = warp * 16;
   uint32_t koff[2][2], voff[4];
@@ -594,7 +595,12 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : (kBf16 ? 3 : 4))
       for (int e = 0; e < 4; ++e) {
         const float s = sc[nt][0][e] + sc[nt][1][e];
         const bool hi = e >= 2;
-        const float v = (s - bias[nt][e & 1]) * (hi ? sk_hi : sk_lo) + (hi ? mk_hi : mk_lo);
+        float v = (s - bias[nt][e & 1]) * (hi ? sk_hi : sk_lo) + (hi ? mk_hi : mk_lo);
+        if (a.round_logits) {
+          // the K scale is a bf16 value: rounding undoes the error of dividing it back out
+          const float ks = quant ? bf16_round((hi ? sk_hi : sk_lo) * inv_unit2) : 1.f;
+          v = kLog2e * rounded_logit(s - bias[nt][e & 1], sqrt_d, ks, quant, (hi ? mk_hi : mk_lo) * kLn2);
+        }
         xv[e] = (hi ? valid_hi : valid_lo) ? v : -INFINITY;
       }
       float mx0 = fmaxf(xv[0], xv[2]), mx1 = fmaxf(xv[1], xv[3]);

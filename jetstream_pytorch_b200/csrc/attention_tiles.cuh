@@ -86,11 +86,20 @@ __device__ __forceinline__ void group_sync() {
 }
 
 // Combine the `parts` partials of one segment (CTAs first .. first+parts-1) and
-// write its R final rows.  `scratch` is at least (parts + 3) * 16 floats of
+// write its R final rows.  `scratch` is at least (parts + 4) * 16 floats of
 // shared memory.  Called by 128 threads (threadIdx.x 0..127).
-template <bool kWorkerGroup = false>
+struct NoMergeHook {
+  __device__ __forceinline__ void operator()(float*, float*, float (&)[kMaxRows]) const {}
+};
+
+// `hook(M, L, acc)` runs after the pieces are combined and before the rows are
+// written: M[r] the maximum (log2 domain) and L[r] the denominator of row r (in
+// shared memory, read by every thread), acc[r] this thread's head-dim component
+// of the unnormalised output.  It may change all three (the tcgen05 kernel adds
+// the decode step's new token there) and is called by all 128 threads.
+template <bool kWorkerGroup = false, typename Hook = NoMergeHook>
 static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int first, int parts, int64_t row_base,
-                                     float* scratch) {
+                                     float* scratch, Hook hook = Hook()) {
   const int tid = threadIdx.x, R = a.R;
   float* s_w = scratch;                     // [parts][16] weights
   float* s_M = scratch + parts * kMaxRows;  // [16] reference maximum
@@ -119,10 +128,10 @@ static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int
       L += s_w[pi * kMaxRows + tid] * __ldcg(&x.part_l[pr]);
       mt = fmaxf(mt, __ldcg(&x.part_t[pr]));
     }
-    s_L[tid] = L;
-    // report the true maximum and the denominator relative to it
-    if (a.m) a.m[row_base + tid] = mt * kLn2;
-    if (a.l) a.l[row_base + tid] = L > 0.f ? L * fast_exp2(s_M[tid] - mt) : 0.f;
+    // keep the denominator relative to the true maximum, which is what gets reported
+    s_L[tid] = L > 0.f ? L * fast_exp2(s_M[tid] - mt) : 0.f;
+    s_w[parts * kMaxRows + 2 * kMaxRows + tid] = L > 0.f ? fast_exp2(s_M[tid] - mt) : 0.f;  // rescale of acc
+    s_M[tid] = mt;
   }
   group_sync<kWorkerGroup>();
   float acc[kMaxRows];
@@ -154,6 +163,16 @@ static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int
         if (r < R) acc[r] += s_w[pi * kMaxRows + r] * __ldcg(src + r * kD);
       }
     }
+  }
+  float* s_c = s_L + kMaxRows;  // [16] factor that brings acc to the true maximum
+#pragma unroll
+  for (int r = 0; r < kMaxRows; ++r) {
+    if (r < R) acc[r] *= s_c[r];
+  }
+  hook(s_M, s_L, acc);
+  if (tid < R) {
+    if (a.m) a.m[row_base + tid] = s_M[tid] * kLn2;
+    if (a.l) a.l[row_base + tid] = s_L[tid];
   }
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
 #pragma unroll
@@ -202,9 +221,17 @@ inline int configure_once_per_device(std::atomic<bool> (&done)[kMaxDevices], con
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct ScratchLayout {
-  size_t counters, seqinfo, part_m, part_l, part_t, part_o, total;
+  size_t counters, seqinfo, exchange, part_m, part_l, part_t, part_o, total;
   int num_ctas;
 };
+
+// Exchange area of one rank for the per-token amax of a decode step: 64 bytes of
+// state {launches done, CTAs done, gave up}, then slots[parity][writer rank][2 B]
+// of 64-bit words.  The same layout serves jpt_peer_exchange buffers.
+constexpr size_t kExchangeStateBytes = 64;
+inline size_t exchange_bytes(int B, int world) {
+  return kExchangeStateBytes + (size_t)2 * world * 2 * B * sizeof(unsigned long long);
+}
 
 // Layout of the scratch of a persistent launch of `num_ctas` CTAs.
 inline ScratchLayout scratch_layout(const jpt_attn_params& p, int num_ctas) {
@@ -215,6 +242,8 @@ inline ScratchLayout scratch_layout(const jpt_attn_params& p, int num_ctas) {
   off = kWorkspaceCounterBytes;
   s.seqinfo = off;
   off = align_up(off + sizeof(int32_t) * 4 * p.B, 256);
+  s.exchange = off;  // one-GPU exchange slots of the fused update (zero after workspace init, kept consistent by the kernel)
+  off = align_up(off + exchange_bytes(p.B, 1), 256);
   s.part_m = off;
   off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
   s.part_l = off;

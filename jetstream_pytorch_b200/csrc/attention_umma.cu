@@ -25,11 +25,12 @@
 // the only roundings are the two splits above and the fp32 online-softmax
 // arithmetic.
 //
-// Thread t of the 128 owns tokens t and 128 + t of the tile in the softmax
-// phase (TMEM lane t of S^T_0 and S^T_1: two independent dependency chains per
-// thread, one exchange of row maxima and one rescale of the accumulators per
-// 256 tokens) and head-dim index t in the output phase (TMEM lane t of O^T),
-// which also removes the cross-warp merge of the accumulators.
+// A CTA has 256 threads, one per token of the tile: thread (g, t) of group g
+// (warps 4 g .. 4 g + 3) owns token 128 g + t in the softmax phase (TMEM lane t
+// of S^T_g) and head-dim index t of rows 4 g .. 4 g + 3 in the output phase
+// (TMEM lane t of O^T), which also removes the cross-warp merge of the
+// accumulators.  One exchange of row maxima, one MMA issue and one rescale of
+// the accumulators serve 256 tokens; two CTAs of 8 warps share an SM.
 //
 // Tiles are scheduled as in the mma.sync kernel (equal contiguous shares of one
 // global tile list, pieces, last-arriver merge).  K and V rows land in shared
@@ -45,13 +46,24 @@
 // bytes at a time by all threads.  A segment whose valid range wraps around the
 // ring is cut into tiles run by run, so a tile is always one range of rows.
 //
-// Every wait on an mbarrier is bounded; a CTA that gives up raises the status
-// word of the workspace, frees its tensor memory and returns.
+// Fused decode update (jpt_decode_update_attend): the launch also takes the
+// step's new K/V token.  CTA b mod grid computes the token's amax over this
+// GPU's heads first thing and stores it into the exchange slots of every rank
+// (NVLink peer stores when the KV heads are sharded); the tiles of the existing
+// tokens stream as usual; the CTA that writes a segment's final rows reads the
+// ranks' words (long there by then), quantises the token's row for its head
+// with the decode quantiser, writes cache row, scale and stash, and folds the
+// token into the result as one more softmax term.  One launch per layer, the
+// exchange's round trip hidden under the existing tokens.
+//
+// Every wait (mbarriers, exchange words) is bounded; a CTA that gives up raises
+// the status word of the workspace, frees its tensor memory and returns.
 #include <cuda.h>
 #include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
+#include <type_traits>
 #include <vector>
 
 #include "attention_tiles.cuh"
@@ -59,8 +71,9 @@
 namespace jpt {
 namespace {
 
-constexpr int kHalfU = 128;           // tokens per MMA = TMEM lanes = threads per CTA
+constexpr int kHalfU = 128;           // tokens per MMA = TMEM lanes
 constexpr int kTileU = 2 * kHalfU;    // tokens per round
+constexpr int kThreadsU = kTileU;     // one thread per token of a round
 constexpr int kTmemCols = 64;         // S^T_0: columns 0..15, S^T_1: 16..31, O^T: 32..47
 constexpr int kColS1 = 16, kColO = 32;
 constexpr int kCtasPerSm = 2;
@@ -76,9 +89,12 @@ struct __align__(1024) SmemU {
   uint8_t qlev[16 * kD];         // query levels: rows 0..7 high bytes, 8..15 low bytes
   uint8_t plev[2][16 * kHalfU];  // probability levels per half: row 8 l + r, one byte per token
   uint8_t qraw[8 * kD * 2];      // bf16 query rows of the piece whose first tile is in flight
-  float xch[4][12];              // per warp: row maxima of the tile [8], largest V scale [1]
-  float red[4][8];               // per warp: denominators at the end of a piece
+  float xch[8][12];              // per warp: row maxima of the tile [8], largest V scale [1]
+  float red[8][8];               // per warp: denominators at the end of a piece
+  float ntx[2][4];               // new token, per 128-thread group: K amax, V amax
+  float dot[2][4][8];            // new token, per group and warp: partial logits of up to 8 rows
   float qsc[8];                  // s_r * sm_scale * log2(e) / 254
+  float qsr[8];                  // s_r / 254 (the chain of rounded logits starts from the plain dot product)
   uint64_t bar[2];               // MMA completion: S^T (both halves), O^T
   uint64_t bar_in[3];            // rows landed (copy-engine path): K, V stage 0, V stage 1
   uint32_t tmem_base;
@@ -94,9 +110,9 @@ __device__ __forceinline__ void cp_async16_at(uint32_t dst, const void* src) {
 }
 template <int kI>
 __device__ __forceinline__ void cp_async_tile_rows(uint32_t kdst, uint32_t vdst, const void* kp, const void* vp) {
-  if constexpr (kI < 16) {
-    cp_async16_at<2048 * kI>(kdst, kp);
-    cp_async16_at<2048 * kI>(vdst, vp);
+  if constexpr (kI < 8) {  // 8 passes of 32 rows
+    cp_async16_at<4096 * kI>(kdst, kp);
+    cp_async16_at<4096 * kI>(vdst, vp);
     cp_async_tile_rows<kI + 1>(kdst, vdst, kp, vp);
   }
 }
@@ -112,29 +128,23 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(x));
   return r;
 }
-// Rows kRow .. 7 of the thread's two tokens: new running maximum, rescale
-// factor, probabilities, denominator share, and the probabilities' level bytes.
+// Rows kRow .. 7 of the thread's token: new running maximum, rescale factor,
+// probability, denominator share, and the probability's two level bytes.
 // m_run starts at kNoMax (finite), so exp2(old - new) and exp2(-inf - new) need
-// no special case.  kTwo = false: the second half of the tile holds no token.
-template <int kRow, bool kTwo>
+// no special case.
+template <int kRow>
 __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8], float (&alpha)[8], const float (&tm)[8],
-                                             const float (&x0)[8], const float (&x1)[8], float ps0, float ps1,
-                                             const uint32_t (&p_row)[8]) {
+                                             const float (&x)[8], float ps, uint32_t p_base) {
   if constexpr (kRow < 8) {
     const float mn = fmaxf(m_run[kRow], tm[kRow]);
     const float al = ex2(m_run[kRow] - mn);
-    const float p0 = ex2(x0[kRow] - mn);
+    const float p = ex2(x[kRow] - mn);
     alpha[kRow] = al;
     m_run[kRow] = mn;
-    store_levels<128 * kRow>(p_row[kRow], __float2uint_rn(p0 * ps0));
-    if constexpr (kTwo) {
-      const float p1 = ex2(x1[kRow] - mn);
-      l_run[kRow] = fmaf(l_run[kRow], al, p0 + p1);
-      store_levels<128 * kRow + 2048>(p_row[kRow], __float2uint_rn(p1 * ps1));
-    } else {
-      l_run[kRow] = fmaf(l_run[kRow], al, p0);
-    }
-    softmax_rows<kRow + 1, kTwo>(m_run, l_run, alpha, tm, x0, x1, ps0, ps1, p_row);
+    l_run[kRow] = fmaf(l_run[kRow], al, p);
+    // the byte of row r: 16-byte chunk (t / 16) ^ r of that row (the XOR folds into the address)
+    store_levels<128 * kRow>(p_base ^ (uint32_t)(kRow << 4), __float2uint_rn(p * ps));
+    softmax_rows<kRow + 1>(m_run, l_run, alpha, tm, x, ps, p_base);
   }
 }
 // A segment's valid tokens form one run of consecutive rows, or two when the
@@ -222,7 +232,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// barrier of one 128-thread group of the CTA (ids 3 and 4; 0 is __syncthreads, 2 the merge's)
+__device__ __forceinline__ void group_barrier(int g) {
+  if (g == 0) {
+    asm volatile("bar.sync 3, 128;" ::: "memory");
+  } else {
+    asm volatile("bar.sync 4, 128;" ::: "memory");
+  }
+}
 // maximum over the 32 lanes in one instruction
 __device__ __forceinline__ float warp_max(float x) {
   float r;
@@ -266,9 +289,9 @@ __device__ __forceinline__ unsigned long long gtimer_ns() {
 #define JPT_SPAN(k) do {} while (0)
 #endif
 
-__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+__global__ void __launch_bounds__(kThreadsU, kCtasPerSm)
     flash_decode_i8_umma_kernel(AttnArgs a, MmaScratch x, int* status, const __grid_constant__ TmaMaps maps, int tma_mode,
-                                int big_rows) {
+                                int big_rows, const __grid_constant__ NewTokenArgs nt) {
   // The swizzled tiles need a 1024-byte aligned base.  The array is declared
   // with that alignment (and used in place, so that every access compiles to a
   // shared-memory instruction); a base that is not aligned after all is reported.
@@ -279,7 +302,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     return;
   }
 
+  // Thread tid owns token tid of the tile in the softmax phase.  The two groups of 128
+  // threads (warps 0..3, warps 4..7) own the two halves, i.e. S^T_0 and S^T_1, whose TMEM
+  // lane is t = tid mod 128.  In the output phase thread (g, t) owns head-dim index t of
+  // rows 4 g .. 4 g + 3.
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = tid >> 7, t = tid & (kHalfU - 1);
   const int R = a.R;
   const bool quant = a.k_scale != nullptr;
   const int cta = blockIdx.x;
@@ -305,23 +333,75 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     tc_fence_before();
   }
   // Up to here nothing of global memory was touched: with a programmatic launch all of
-  // it ran under the kernel before this one (the append of the new token).
+  // it ran under the kernel before this one.
   grid_dependency_wait();
   grid_dependency_trigger();
 
+  // ------------------------------------------------------------------ new token: amax to every rank
+  unsigned nt_epoch = 0;
+  if (nt.enabled) {
+    nt_epoch = *reinterpret_cast<volatile unsigned*>(&nt.px_state[0]) + 1u;
+    const int HD = a.Hkv * kD;
+    for (int b = cta; b < a.B; b += gridDim.x) {
+      float am[2];
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        float v = 0.f;
+        for (int e = tid; e < HD; e += kThreadsU) {
+          const int64_t idx = (int64_t)b * HD + e;
+          const float xv = nt.in_f32 ? static_cast<const float*>(nt.x[which])[idx]
+                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(nt.x[which])[idx]);
+          v = fmaxf(v, fabsf(xv));
+        }
+        am[which] = warp_max(v);
+      }
+      __syncthreads();  // the scratch may still be read for the slot before
+      if (lane == 0) {
+        sm.xch[warp][0] = am[0];
+        sm.xch[warp][1] = am[1];
+      }
+      __syncthreads();
+      if (tid < 2) {
+        float m8 = sm.xch[0][tid];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m8 = fmaxf(m8, sm.xch[w][tid]);
+        const size_t row = (size_t)(nt_epoch & 1u) * nt.px_world + nt.px_rank;
+        const unsigned long long word = ((unsigned long long)nt_epoch << 32) | __float_as_uint(m8);
+        for (int r = 0; r < nt.px_world; ++r)
+          asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(nt.px_slots[r] + row * (2 * a.B) + tid * a.B + b), "l"(word)
+                       : "memory");
+      }
+    }
+    __syncthreads();
+  }
+  // Counts this CTA as done with the exchange of this launch; the last one advances the launch number.
+  auto exchange_done = [&]() {
+    if (nt.enabled && tid == 0) {
+      __threadfence();
+      const unsigned done = atomicAdd(&nt.px_state[1], 1u);
+      if (done == gridDim.x - 1) {
+        nt.px_state[1] = 0;
+        __threadfence();
+        atomicAdd(&nt.px_state[0], 1u);
+      }
+    }
+  };
+
   // ------------------------------------------------------------------ schedule
   // Slots per sequence (tiles + overhead) -> exclusive prefix over sequences;
-  // each thread owns a slice of ceil(B/128) sequences.  The scan scratch
-  // aliases the probability levels, which are not in use yet.
+  // each of the first 128 threads owns a slice of ceil(B/128) sequences.  The scan
+  // scratch aliases the probability levels, which are not in use yet.
   int* scan = reinterpret_cast<int*>(&sm.plev[0][0]);  // 129 ints
   const int per = (a.B + kThreads - 1) / kThreads;
-  const int b_lo = min(a.B, tid * per), b_hi = min(a.B, b_lo + per);
-  int mine = 0;
-  for (int b = b_lo; b < b_hi; ++b) {
-    int ua;
-    mine += slots_u(seq_range_x(a, x, b, &ua), a.S);
+  const int b_lo = min(a.B, t * per), b_hi = min(a.B, b_lo + per);
+  if (g == 0) {
+    int mine = 0;
+    for (int b = b_lo; b < b_hi; ++b) {
+      int ua;
+      mine += slots_u(seq_range_x(a, x, b, &ua), a.S);
+    }
+    scan[tid] = mine;
   }
-  scan[tid] = mine;
   __syncthreads();
   if (warp == 0) {
     int v4[4], s = 0;
@@ -349,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   const int share = (total + x.num_ctas - 1) / x.num_ctas;
   const int G0 = cta * share;
   const int G1 = min(total, G0 + share);
-  {
+  if (g == 0) {
     // the thread whose slice holds slot G0 walks it and publishes (b, h, slot in segment)
     const int lo = scan[tid] * a.Hkv, hi = scan[tid + 1] * a.Hkv;
     if (G0 < G1 && G0 >= lo && G0 < hi) {
@@ -373,16 +453,137 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   JPT_SPAN(1);
-  // Rows of empty sequences are nobody's tile: sequence b is cleared by CTA b mod grid
-  // (at the end of the CTA's life, off the path to its first tile).
+
+  const __nv_bfloat16* qbase = static_cast<const __nv_bfloat16*>(a.q);
+  bool dead = false;  // a wait ran out
+  // The decode step's new token of slot b, KV head h, folded into rows r0 .. r0 + kRows - 1 by
+  // the 128-thread group `grp` (thread t: head-dim index t): all-ranks amax -> scale -> codes of
+  // this head's row -> (group 0) cache row, scale, stash -> one more softmax term on top of
+  // (M, L, acc): M[j] maximum in the log2 domain (-inf: no token yet), L[j] denominator, acc[j]
+  // this thread's component of the unnormalised output.  Every thread of the group calls it.
+  auto add_new_token = [&](auto rows_tag, int grp, int b, int h, int r0, float* M, float* L, float* acc) {
+    constexpr int kRows = decltype(rows_tag)::value;
+    group_barrier(grp);  // the group's scratch is free
+    if (t < 2) {         // K amax, V amax: largest partial over the ranks
+      const size_t row = (size_t)(nt_epoch & 1u) * nt.px_world;
+      float m = 0.f;
+      const long long t0 = clock64();
+      for (int r = 0; r < nt.px_world; ++r) {
+        const unsigned long long* p = nt.px_slots[nt.px_rank] + (row + r) * (2 * a.B) + t * a.B + b;
+        unsigned long long w;
+        for (;;) {
+          asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+          if ((unsigned)(w >> 32) == nt_epoch) break;
+          if (clock64() - t0 > nt.px_wait_cycles) {  // a rank never came: report, go on with what is there
+            atomicExch(&nt.px_state[2], 1u);
+            w = 0;
+            break;
+          }
+        }
+        m = fmaxf(m, __uint_as_float((unsigned)w));
+      }
+      sm.ntx[grp][t] = m;
+    }
+    group_barrier(grp);
+    const float amax_k = sm.ntx[grp][0], amax_v = sm.ntx[grp][1];
+    const float sc_k = nt.in_f32 ? decode_scale<float>(amax_k) : decode_scale<__nv_bfloat16>(amax_k);
+    const float sc_v = nt.in_f32 ? decode_scale<float>(amax_v) : decode_scale<__nv_bfloat16>(amax_v);
+    const int64_t xi = ((int64_t)b * a.Hkv + h) * kD + t;
+    float xk, xv;
+    if (nt.in_f32) {
+      xk = static_cast<const float*>(nt.x[0])[xi];
+      xv = static_cast<const float*>(nt.x[1])[xi];
+    } else {
+      xk = __bfloat162float(static_cast<const __nv_bfloat16*>(nt.x[0])[xi]);
+      xv = __bfloat162float(static_cast<const __nv_bfloat16*>(nt.x[1])[xi]);
+    }
+    const int8_t ck = nt.in_f32 ? decode_code<float>(xk, sc_k) : decode_code<__nv_bfloat16>(xk, sc_k);
+    const int8_t cv = nt.in_f32 ? decode_code<float>(xv, sc_v) : decode_code<__nv_bfloat16>(xv, sc_v);
+    if (grp == 0) {
+      if (nt.quant[0]) nt.quant[0][xi] = ck;
+      if (nt.quant[1]) nt.quant[1][xi] = cv;
+      int pos = nt.pos ? nt.pos[nt.pos_count == 1 ? 0 : b] : nt.pos_host;
+      if (pos < 0) pos += a.S;
+      const bool write = nt.write_cache && pos >= 0 && pos < a.S;
+      if (write) {
+        const int64_t off = (int64_t)b * a.kv_b + (int64_t)h * a.kv_h + (int64_t)pos * a.kv_s + t;
+        static_cast<int8_t*>(const_cast<void*>(a.k))[off] = ck;
+        static_cast<int8_t*>(const_cast<void*>(a.v))[off] = cv;
+      }
+      if (t < 2) {  // every head's CTA writes the same scale: harmless, and no CTA has to wait for another
+        const float sc = t == 0 ? sc_k : sc_v;
+        void* out = nt.scale_out[t];
+        void* cache = const_cast<void*>(t == 0 ? a.k_scale : a.v_scale);
+        const int64_t sidx = (int64_t)b * a.sc_b + (int64_t)pos * a.sc_s;
+        if (nt.in_f32) {
+          if (out) static_cast<float*>(out)[b] = sc;
+          if (write) static_cast<float*>(cache)[sidx] = sc;
+        } else {
+          if (out) static_cast<__nv_bfloat16*>(out)[b] = __float2bfloat16_rn(sc);
+          if (write) static_cast<__nv_bfloat16*>(cache)[sidx] = __float2bfloat16_rn(sc);
+        }
+      }
+    }
+    // logits of the query rows against the new key: sum over the 128 head-dim indices of the group
+    const __nv_bfloat16* q = qbase + ((int64_t)b * a.Hkv + h) * R * kD;
+    const float kf = (float)ck;
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+      float d = r0 + j < R ? __bfloat162float(q[(r0 + j) * kD + t]) * kf : 0.f;
+#pragma unroll
+      for (int sh = 1; sh <= 16; sh <<= 1) d += __shfl_xor_sync(0xffffffffu, d, sh);
+      if (lane == j) sm.dot[grp][warp & 3][j] = d;
+    }
+    group_barrier(grp);
+    const float unit = sc_k * a.sm_scale * kLog2e;
+    const float vf = (float)cv * sc_v;
+#pragma unroll
+    for (int j = 0; j < kRows; ++j) {
+      if (r0 + j < R) {
+        const float xn = ((sm.dot[grp][0][j] + sm.dot[grp][1][j]) + (sm.dot[grp][2][j] + sm.dot[grp][3][j])) * unit;
+        const float mn = fmaxf(M[j], xn);
+        const float al = M[j] == -INFINITY ? 0.f : ex2(M[j] - mn);
+        const float pn = ex2(xn - mn);
+        acc[j] = fmaf(acc[j], al, pn * vf);
+        L[j] = fmaf(L[j], al, pn);
+        M[j] = mn;
+      }
+    }
+  };
+  // Rows of empty sequences are nobody's tile: sequence b is handled by CTA b mod grid (at the end of
+  // the CTA's life, off the path to its first tile): zero rows, or the new token alone.
   auto clear_empty_rows = [&]() {
     for (int b = cta; b < a.B; b += gridDim.x) {
       int ua;
       if (seq_range_x(a, x, b, &ua).n == 0) {
         const int64_t r0 = (int64_t)b * a.Hkv * R;
         __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
-        for (int i = tid; i < a.Hkv * R * kD; i += kThreads) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
-        for (int i = tid; i < a.Hkv * R; i += kThreads) {
+        if (nt.enabled) {
+          for (int h = 0; h < a.Hkv; ++h) {
+            float M[4], L[4], acc[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              M[j] = -INFINITY;
+              L[j] = 0.f;
+              acc[j] = 0.f;
+            }
+            add_new_token(std::integral_constant<int, 4>(), g, b, h, 4 * g, M, L, acc);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (4 * g + j < R) {
+                const int64_t row = r0 + (int64_t)h * R + 4 * g + j;
+                o[row * kD + t] = __float2bfloat16_rn(acc[j] / L[j]);
+                if (t == 0) {
+                  if (a.m) a.m[row] = M[j] * kLn2;
+                  if (a.l) a.l[row] = L[j];
+                }
+              }
+            }
+          }
+          continue;
+        }
+        for (int i = tid; i < a.Hkv * R * kD; i += kThreadsU) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
+        for (int i = tid; i < a.Hkv * R; i += kThreadsU) {
           if (a.m) a.m[r0 + i] = -INFINITY;
           if (a.l) a.l[r0 + i] = 0.f;
         }
@@ -391,6 +592,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   };
   if (G0 >= G1) {  // no tile for this CTA
     clear_empty_rows();
+    exchange_done();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -399,26 +601,24 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     return;
   }
   JPT_SPAN(2);
-  const uint32_t tmem_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+  // this warp's 32 lanes; the group's logits are in S^T_g
+  const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+  const uint32_t tmem_s = tmem_lane + (uint32_t)(g * kColS1);
+  const uint32_t tmem_o = tmem_lane + (uint32_t)(kColO + 4 * g);  // level 0 of rows 4 g ..; level 1 is 8 columns on
 
   const int8_t* kbase = static_cast<const int8_t*>(a.k);
   const int8_t* vbase = static_cast<const int8_t*>(a.v);
-  const __nv_bfloat16* qbase = static_cast<const __nv_bfloat16*>(a.q);
   const __nv_bfloat16* mask = static_cast<const __nv_bfloat16*>(a.mask);
 
   // ------------------------------------------------------------------ producer
   // Position of the next tile to fetch (uniform across the CTA) ...
   int pb = sm.start[0], ph = sm.start[1], pt, pslot = G0;  // pslot: global slot index of tile pt
   int pT, pn, pfirst, puse_add;
-  // ... and what follows from it for this thread: 16-byte column tid % 8 of
-  // rows tid / 8 + 16 i of a tile.  The swizzled shared-memory offset of row
-  // + 16 i is that of row plus 2048 i.
+  // ... and what follows from it for this thread when the threads copy the rows themselves:
+  // 16-byte column tid % 8 of rows tid / 8 + 32 i of a tile.  The swizzled shared-memory offset
+  // of row + 32 i is that of row plus 4096 i.
   const int prow = tid >> 3, pcol = tid & 7;
   const uint32_t pdst = (uint32_t)(prow * kD + ((pcol ^ (prow & 7)) << 4));
-  // pages that hold whole 16-row copy passes: one table entry per pass
-  const bool pass_pages = a.paged && (a.page_size % 16) == 0 &&
-                          ((kTileU % a.page_size) == 0 || (a.page_size % kTileU) == 0);
-  const int passes_per_page = pass_pages ? a.page_size / 16 : 1;
   const bool rows_packed = !a.paged && a.kv_s == kD;  // rows of a tile kD bytes apart
   const int kv_s32 = (int)a.kv_s, sc_s32 = (int)a.sc_s;
   const int8_t *kseg, *vseg;  // segment base + this thread's column
@@ -476,30 +676,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     seg_setup();
   }
 
-  // scales of this thread's two tokens (tid, 128 + tid) in the tile fetched last
-  float nks0 = 1.f, nvs0 = 0.f, nks1 = 1.f, nvs1 = 0.f;
+  float nks = 1.f, nvs = 0.f;  // scales of this thread's token in the tile fetched last
   bool first_issue = true;
-  bool dead = false;  // a wait ran out
 
-  auto token_scales = [&](int r, float& ksc, float& vsc) {  // r: row of the tile
-    ksc = 1.f;
-    vsc = 0.f;
-    if (r < pcnt) {
-      vsc = 1.f;
-      if (quant) {
-        const int pos = ppos + r;
-        int64_t sidx;
-        if (a.paged) {
-          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
-          sidx = (int64_t)pg * a.page_size + pos % a.page_size;
-        } else {
-          sidx = scseg + (int64_t)pos * sc_s32;
-        }
-        ksc = load_scale(a.k_scale, sidx, a.scale_is_f32);
-        vsc = load_scale(a.v_scale, sidx, a.scale_is_f32);
-      }
-    }
-  };
   // K rows of tile pt into the K buffer, V rows into V stage `vstage`, the record into meta[mslot].
   auto issue_tile = [&](int vstage, int mslot) {
     const bool piece_start = first_issue || pt == 0;
@@ -513,9 +692,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       mt.pad[2] = pslot + 1 >= G1;  // no tile follows in this CTA's share
       sm.meta[mslot] = mt;
     }
-    const uint32_t kdst = smem_u32(&sm.k[0]) + pdst;
-    const uint32_t vdst = smem_u32(&sm.v[vstage][0]) + pdst;
-    const int passes = (pcnt + 15) >> 4;  // 16-row passes that hold a valid row
     if (tma_mode != kTmaNone) {
       // One thread hands the rows to the copy engine: boxes of `big_rows` rows while that many
       // valid rows remain (a whole dense tile, a whole page), boxes of 32 rows for the rest.  Rows
@@ -543,50 +719,54 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
           r += big ? big_rows : 32;
         }
       }
-    } else if (rows_packed && pcnt == kTileU) {
-      // whole tile valid, rows kD bytes apart: one address per tensor
-      const int64_t off = (int64_t)(ppos + prow) * kD;
-      const int8_t* kp = kseg + off;
-      const int8_t* vp = vseg + off;
-      cp_async_tile_rows<0>(kdst, vdst, kp, vp);
-    } else if (pass_pages) {
-      // paged caches start at position 0: pass i (rows 16 i ..) lies inside one page
-      int pi = ppos / a.page_size, within = (ppos % a.page_size) / 16;
-#pragma unroll 4
-      for (int i = 0; i < passes; ++i) {
-        const bool valid = 16 * i + prow < pcnt;
-        const int page = a.page_table[(int64_t)pb * a.max_pages + pi];
-        const int64_t off = (int64_t)page * a.kv_page + (int64_t)(within * 16 + prow) * kD;
-        cp_async16(kdst + 2048 * i, kseg + off, valid);
-        cp_async16(vdst + 2048 * i, vseg + off, valid);
-        if (++within == passes_per_page) {
-          within = 0;
-          ++pi;
-        }
-      }
     } else {
-#pragma unroll 4
-      for (int i = 0; i < passes; ++i) {
-        const int r = prow + 16 * i;
-        const bool valid = r < pcnt;
-        const int pos = valid ? ppos + r : ppos;
-        int64_t off;
-        if (a.paged) {
-          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
-          off = (int64_t)pg * a.kv_page + (int64_t)(pos % a.page_size) * kD;
-        } else {
-          off = (int64_t)pos * kv_s32;
+      const uint32_t kdst = smem_u32(&sm.k[0]) + pdst;
+      const uint32_t vdst = smem_u32(&sm.v[vstage][0]) + pdst;
+      if (rows_packed && pcnt == kTileU) {
+        // whole tile valid, rows kD bytes apart: one address per tensor
+        const int64_t off = (int64_t)(ppos + prow) * kD;
+        cp_async_tile_rows<0>(kdst, vdst, kseg + off, vseg + off);
+      } else {
+        const int passes = (pcnt + 31) >> 5;  // 32-row passes that hold a valid row
+#pragma unroll 2
+        for (int i = 0; i < passes; ++i) {
+          const int r = prow + 32 * i;
+          const bool valid = r < pcnt;
+          const int pos = valid ? ppos + r : ppos;
+          int64_t off;
+          if (a.paged) {
+            const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
+            off = (int64_t)pg * a.kv_page + (int64_t)(pos % a.page_size) * kD;
+          } else {
+            off = (int64_t)pos * kv_s32;
+          }
+          cp_async16(kdst + 4096 * i, kseg + off, valid);
+          cp_async16(vdst + 4096 * i, vseg + off, valid);
         }
-        cp_async16(kdst + 2048 * i, kseg + off, valid);
-        cp_async16(vdst + 2048 * i, vseg + off, valid);
       }
     }
     if (piece_start) {
       const __nv_bfloat16* q = qbase + ((int64_t)pb * a.Hkv + ph) * R * kD;
-      for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.qraw[0]) + ch * 16, q + ch * 8, true);
+      for (int ch = tid; ch < R * 16; ch += kThreadsU) cp_async16(smem_u32(&sm.qraw[0]) + ch * 16, q + ch * 8, true);
     }
-    token_scales(tid, nks0, nvs0);
-    token_scales(kHalfU + tid, nks1, nvs1);
+    // scales of token `tid` of the tile, consumed by this same thread
+    nks = 1.f;
+    nvs = 0.f;
+    if (tid < pcnt) {
+      nvs = 1.f;
+      if (quant) {
+        const int pos = ppos + tid;
+        int64_t sidx;
+        if (a.paged) {
+          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
+          sidx = (int64_t)pg * a.page_size + pos % a.page_size;
+        } else {
+          sidx = scseg + (int64_t)pos * sc_s32;
+        }
+        nks = load_scale(a.k_scale, sidx, a.scale_is_f32);
+        nvs = load_scale(a.v_scale, sidx, a.scale_is_f32);
+      }
+    }
   };
   // Fetch the next tile of the share, or mark the record as empty.
   auto produce = [&](int vstage, int mslot) {
@@ -608,18 +788,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   };
 
   // ------------------------------------------------------------------ consumer state
-  float m_run[8], l_run[8], o[8];  // l_run: this thread's token share of the denominators; o: head-dim index tid
+  float m_run[8], l_run[8];  // l_run: this thread's token share of the denominators
+  float o[4];                // rows 4 g .. 4 g + 3, head-dim index t
   int piece_t0 = 0;
   const float unit2 = a.sm_scale * kLog2e;
   const uint32_t bar_s = smem_u32(&sm.bar[0]), bar_o = smem_u32(&sm.bar[1]);
   const uint32_t q_desc_addr = smem_u32(&sm.qlev[0]), p_desc_addr = smem_u32(&sm.plev[0][0]);
   const uint32_t k_addr = smem_u32(&sm.k[0]);
-  // this thread's byte of row r of the probability levels: ((tid / 16) ^ r) * 16 + tid % 16.
-  // plev is 1024-byte aligned, so the XOR with r << 4 can be applied to the whole address.
-  uint32_t p_row[8];
-#pragma unroll
-  for (int r = 0; r < 8; ++r)
-    p_row[r] = (smem_u32(&sm.plev[0][0]) + (tid & 15) + ((uint32_t)(tid >> 4) << 4)) ^ (uint32_t)(r << 4);
+  // this thread's byte of row 0 of its half's probability levels: chunk t / 16, byte t % 16.  Each
+  // half is 1024-byte aligned, so row r's XOR with r << 4 can be applied to the whole address.
+  const uint32_t p_base = smem_u32(&sm.plev[g][0]) + (t & 15) + ((uint32_t)(t >> 4) << 4);
 
   // Query levels of the piece that starts with the tile of record `mt` (when it
   // starts one), then S^T of that tile (one MMA group per half that holds a
@@ -628,41 +806,46 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   // logits of the tile before are out of tensor memory.
   auto prepare = [&](const TileMeta& mt, bool first) {
     if (first || mt.t == 0) {
-      // thread (row = tid / 16, chunk = tid % 16) converts 8 values of one query row
-      const int row = tid >> 4, ch = tid & 15;
-      float f[8];
-      if (row < R) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[row * (kD * 2) + ch * 16]);
-        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      if (g == 0) {
+        // thread (row = t / 16, chunk = t % 16) converts 8 values of one query row
+        const int row = t >> 4, ch = t & 15;
+        float f[8];
+        if (row < R) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[row * (kD * 2) + ch * 16]);
+          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 t = __bfloat1622float2(p2[e]);
-          f[2 * e] = t.x;
-          f[2 * e + 1] = t.y;
+          for (int e = 0; e < 4; ++e) {
+            const float2 tt = __bfloat1622float2(p2[e]);
+            f[2 * e] = tt.x;
+            f[2 * e + 1] = tt.y;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = 0.f;
         }
-      } else {
+        float amax = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = 0.f;
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+#pragma unroll
+        for (int sh = 1; sh <= 8; sh <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+        const float inv = amax > 0.f ? 127.f / amax : 0.f;
+        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float tt = f[e] * inv;
+          const float h = rintf(tt);
+          const float l = rintf((tt - h) * 254.f);
+          hi[e >> 2] |= ((uint32_t)(int)h & 0xffu) << (8 * (e & 3));
+          lo[e >> 2] |= ((uint32_t)(int)l & 0xffu) << (8 * (e & 3));
+        }
+        *reinterpret_cast<uint2*>(&sm.qlev[swz(row, 8 * ch)]) = make_uint2(hi[0], hi[1]);
+        *reinterpret_cast<uint2*>(&sm.qlev[swz(8 + row, 8 * ch)]) = make_uint2(lo[0], lo[1]);
+        if (ch == 0) {
+          sm.qsc[row] = amax * (1.f / 127.f) * unit2 * (1.f / 254.f);
+          sm.qsr[row] = amax * (1.f / 127.f) * (1.f / 254.f);
+        }
+        fence_async_smem();
       }
-      float amax = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
-#pragma unroll
-      for (int sh = 1; sh <= 8; sh <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
-      const float inv = amax > 0.f ? 127.f / amax : 0.f;
-      uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float t = f[e] * inv;
-        const float h = rintf(t);
-        const float l = rintf((t - h) * 254.f);
-        hi[e >> 2] |= ((uint32_t)(int)h & 0xffu) << (8 * (e & 3));
-        lo[e >> 2] |= ((uint32_t)(int)l & 0xffu) << (8 * (e & 3));
-      }
-      *reinterpret_cast<uint2*>(&sm.qlev[swz(row, 8 * ch)]) = make_uint2(hi[0], hi[1]);
-      *reinterpret_cast<uint2*>(&sm.qlev[swz(8 + row, 8 * ch)]) = make_uint2(lo[0], lo[1]);
-      if (ch == 0) sm.qsc[row] = amax * (1.f / 127.f) * unit2 * (1.f / 254.f);
-      fence_async_smem();
       tc_fence_before();
       __syncthreads();
     }
@@ -682,17 +865,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
   };
   // O^T of the tile with the given parity into the accumulators (alpha and cmax are that tile's)
-  auto add_output = [&](uint32_t parity, const float (&alpha)[8], float cmax) {
+  auto add_output = [&](uint32_t parity, const float (&al4)[4], float cmax) {
     if (!mbar_wait(bar_o, parity)) dead = true;
     tc_fence_after();
-    uint32_t oo[16];
-    tmem_ld16(tmem_lane + kColO, oo);
+    uint32_t o0[4], o1[4];
+    tmem_ld4(tmem_o, o0);
+    tmem_ld4(tmem_o + 8, o1);
     tmem_ld_wait();
     tc_fence_before();
     const float oscale = cmax * (1.f / 65535.f);
 #pragma unroll
-    for (int r = 0; r < 8; ++r)
-      o[r] = fmaf(o[r], alpha[r], (float)((int)oo[r] + ((int)oo[8 + r] << 8)) * oscale);
+    for (int j = 0; j < 4; ++j) o[j] = fmaf(o[j], al4[j], (float)((int)o0[j] + ((int)o1[j] << 8)) * oscale);
   };
 
   // The tensor core works one step ahead of the threads: S^T of tile i+1 is
@@ -708,23 +891,25 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   JPT_SPAN(3);
   if (mt.t >= 0) prepare(mt, true);
 
-  float alpha_prev[8], cmax_prev = 0.f;
+  float alpha_prev[4], cmax_prev = 0.f;
   bool pending = false;  // O^T of the tile before has not been added yet
   for (int i = 0; mt.t >= 0; ++i) {
-    const float cks0 = nks0, cvs0 = nvs0, cks1 = nks1, cvs1 = nvs1;  // scales of this thread's tokens in this tile
+    const float cks = nks, cvs = nvs;  // scales of this thread's token in this tile
     const int vstage = i & 1;
     const bool last_of_share = mt.pad[2] != 0;
     const uint32_t par = (uint32_t)i & 1u;
-    const int left = mt.pad[0];  // valid rows of this tile
-    const bool two = left > kHalfU;
+    const int left = mt.pad[0];            // valid rows of this tile
+    const bool two = left > kHalfU;        // the second half holds a token
+    const bool mine = g == 0 || two;       // this thread's half does
     if (i == 0 || mt.t == 0) {  // a piece starts (the one before was flushed when it ended)
       piece_t0 = mt.t;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         m_run[r] = kNoMax;
         l_run[r] = 0.f;
-        o[r] = 0.f;
       }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = 0.f;
     }
 
     // ---------------- the output of the tile before and the logits of this one leave
@@ -733,47 +918,52 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     if (!mbar_wait(bar_s, par)) dead = true;
     if (pending && !mbar_wait(bar_o, par ^ 1u)) dead = true;
     tc_fence_after();
-    float x0[8], x1[8];
+    float xr[8];
     {
-      uint32_t s0[16], s1[16];
+      uint32_t s[16];
       if (pending) {
-        uint32_t oo[16];
-        tmem_ld16(tmem_lane + kColO, oo);
-        tmem_ld16(tmem_lane, s0);
-        if (two) tmem_ld16(tmem_lane + kColS1, s1);
+        uint32_t o0[4], o1[4];
+        tmem_ld4(tmem_o, o0);
+        tmem_ld4(tmem_o + 8, o1);
+        if (mine) tmem_ld16(tmem_s, s);
         tmem_ld_wait();
         const float oscale = cmax_prev * (1.f / 65535.f);
 #pragma unroll
-        for (int r = 0; r < 8; ++r)  // the two levels combine exactly in int32
-          o[r] = fmaf(o[r], alpha_prev[r], (float)((int)oo[r] + ((int)oo[8 + r] << 8)) * oscale);
+        for (int j = 0; j < 4; ++j)  // the two levels combine exactly in int32
+          o[j] = fmaf(o[j], alpha_prev[j], (float)((int)o0[j] + ((int)o1[j] << 8)) * oscale);
         pending = false;
       } else {
-        tmem_ld16(tmem_lane, s0);
-        if (two) tmem_ld16(tmem_lane + kColS1, s1);
+        if (mine) tmem_ld16(tmem_s, s);
         tmem_ld_wait();
       }
       more = produce(vstage ^ 1, (i + 1) & 1);
-      const bool valid0 = tid < left, valid1 = kHalfU + tid < left;
-      float mk0 = valid0 ? 0.f : -INFINITY, mk1 = valid1 ? 0.f : -INFINITY;  // past the end: finite dot product + (-inf)
-      if (mt.use_add) {  // additive mask that is not a plain 0 / -inf range (rare)
-        const int64_t mrow = (int64_t)mt.b * a.mk_b + mt.pad[1];
-        if (valid0) mk0 = kLog2e * __bfloat162float(mask[mrow + tid]);
-        if (valid1) mk1 = kLog2e * __bfloat162float(mask[mrow + kHalfU + tid]);
-      }
-      const float4 q0 = *reinterpret_cast<const float4*>(&sm.qsc[0]), q1 = *reinterpret_cast<const float4*>(&sm.qsc[4]);
-      const float qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      const bool valid = tid < left;
+      float mk = valid ? 0.f : -INFINITY;  // a token past the end: finite dot product + (-inf)
+      if (mt.use_add && valid)            // additive mask that is not a plain 0 / -inf range (rare)
+        mk = __bfloat162float(mask[(int64_t)mt.b * a.mk_b + mt.pad[1] + tid]);
+      if (!mine) {
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        x0[r] = fmaf((float)((int)s0[r] * 254 + (int)s0[8 + r]), qs[r] * cks0, mk0);
-        x1[r] = two ? fmaf((float)((int)s1[r] * 254 + (int)s1[8 + r]), qs[r] * cks1, mk1) : -INFINITY;
+        for (int r = 0; r < 8; ++r) xr[r] = -INFINITY;
+      } else if (!a.round_logits) {
+        const float4 q0 = *reinterpret_cast<const float4*>(&sm.qsc[0]), q1 = *reinterpret_cast<const float4*>(&sm.qsc[4]);
+        const float qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const float ml = mk * kLog2e;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) xr[r] = fmaf((float)((int)s[r] * 254 + (int)s[8 + r]), qs[r] * cks, ml);
+      } else {
+        // dense_attention on bf16 tensors: the reference rounds the logit to bf16 after every step
+        const float sqrt_d = __frcp_rn(a.sm_scale);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          xr[r] = kLog2e * rounded_logit((float)((int)s[r] * 254 + (int)s[8 + r]) * sm.qsr[r], sqrt_d, cks, quant, mk);
       }
     }
-    // tile maxima per row (and the largest V scale) across the 256 tokens
+    // tile maxima per row (and the largest V scale) across the 256 tokens: per warp first ...
     {
       float wm[9];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) wm[r] = warp_max(fmaxf(x0[r], x1[r]));
-      wm[8] = warp_max(fmaxf(cvs0, cvs1));
+      for (int r = 0; r < 8; ++r) wm[r] = warp_max(xr[r]);
+      wm[8] = warp_max(cvs);
       if (lane == 0) {
         *reinterpret_cast<float4*>(&sm.xch[warp][0]) = make_float4(wm[0], wm[1], wm[2], wm[3]);
         *reinterpret_cast<float4*>(&sm.xch[warp][4]) = make_float4(wm[4], wm[5], wm[6], wm[7]);
@@ -786,31 +976,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     float alpha[8];
     float cmax;
     {
-      float4 t0[4], t1[4];
+      // ... then lane c of every warp folds column c of the 8 warps, and the lanes hand the
+      // 9 results round
+      const int col = lane < 9 ? lane : 8;
+      float v = sm.xch[0][col];
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        t0[w] = *reinterpret_cast<const float4*>(&sm.xch[w][0]);
-        t1[w] = *reinterpret_cast<const float4*>(&sm.xch[w][4]);
-      }
-      cmax = fmaxf(fmaxf(sm.xch[0][8], sm.xch[1][8]), fmaxf(sm.xch[2][8], sm.xch[3][8]));
+      for (int w = 1; w < 8; ++w) v = fmaxf(v, sm.xch[w][col]);
       float tm[8];
-      tm[0] = fmaxf(fmaxf(t0[0].x, t0[1].x), fmaxf(t0[2].x, t0[3].x));
-      tm[1] = fmaxf(fmaxf(t0[0].y, t0[1].y), fmaxf(t0[2].y, t0[3].y));
-      tm[2] = fmaxf(fmaxf(t0[0].z, t0[1].z), fmaxf(t0[2].z, t0[3].z));
-      tm[3] = fmaxf(fmaxf(t0[0].w, t0[1].w), fmaxf(t0[2].w, t0[3].w));
-      tm[4] = fmaxf(fmaxf(t1[0].x, t1[1].x), fmaxf(t1[2].x, t1[3].x));
-      tm[5] = fmaxf(fmaxf(t1[0].y, t1[1].y), fmaxf(t1[2].y, t1[3].y));
-      tm[6] = fmaxf(fmaxf(t1[0].z, t1[1].z), fmaxf(t1[2].z, t1[3].z));
-      tm[7] = fmaxf(fmaxf(t1[0].w, t1[1].w), fmaxf(t1[2].w, t1[3].w));
-      // p <= 1 and the ratio is held at 1 (the fast division may land one ulp above), so
-      // the product stays below 2^16 without a clamp per row
+#pragma unroll
+      for (int r = 0; r < 8; ++r) tm[r] = __shfl_sync(0xffffffffu, v, r);
+      cmax = __shfl_sync(0xffffffffu, v, 8);
+      // p <= 1 and the product is held at 2^16 - 1 (the fast division may land one ulp above)
       const float rc = cmax > 0.f ? __fdividef(65535.f, cmax) : 0.f;
-      const float ps0 = fminf(cvs0 * rc, 65535.f), ps1 = fminf(cvs1 * rc, 65535.f);
-      if (two) {
-        softmax_rows<0, true>(m_run, l_run, alpha, tm, x0, x1, ps0, ps1, p_row);
-      } else {
-        softmax_rows<0, false>(m_run, l_run, alpha, tm, x0, x1, ps0, ps1, p_row);
-      }
+      const float ps = fminf(cvs * rc, 65535.f);
+      softmax_rows<0>(m_run, l_run, alpha, tm, xr, ps, p_base);
     }
     fence_async_smem();
     __syncthreads();
@@ -833,9 +1012,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       umma_commit(bar_o);
     }
 
+    float al4[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) al4[j] = g == 0 ? alpha[j] : alpha[4 + j];
     if (!(last_of_share || mt.t == mt.T - 1)) {
 #pragma unroll
-      for (int r = 0; r < 8; ++r) alpha_prev[r] = alpha[r];
+      for (int j = 0; j < 4; ++j) alpha_prev[j] = al4[j];
       cmax_prev = cmax;
       pending = true;
     } else {
@@ -843,7 +1025,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       const bool is_final = piece_t0 == 0 && mt.t == mt.T - 1;
       const int slot = piece_t0 > 0 ? 0 : 1;
       const int64_t row_base = ((int64_t)mt.b * a.Hkv + mt.h) * R;
-      // denominators: sum the token shares of the 128 threads (while the last O^T MMA runs)
+      // denominators: sum the token shares of the 256 threads (while the last O^T MMA runs)
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         float l = l_run[r];
@@ -852,23 +1034,35 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         if (lane == r) sm.red[warp][r] = l;
       }
       __syncthreads();
-      add_output(par, alpha, cmax);
+      add_output(par, al4, cmax);
+      float L4[4], M4[4];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int j = 0; j < 4; ++j) {
+        const int r = 4 * g + j;
+        float L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) L += sm.red[w][r];
+        L4[j] = L;
+        const float mr = g == 0 ? m_run[j] : m_run[4 + j];
+        M4[j] = mr > 0.5f * kNoMax ? mr : -INFINITY;  // every logit of the row was masked
+      }
+      if (is_final && nt.enabled) add_new_token(std::integral_constant<int, 4>(), g, mt.b, mt.h, 4 * g, M4, L4, o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = 4 * g + j;
         if (r < R) {
-          const float L = (sm.red[0][r] + sm.red[1][r]) + (sm.red[2][r] + sm.red[3][r]);
-          const float M = m_run[r] > 0.5f * kNoMax ? m_run[r] : -INFINITY;  // every logit of the row was masked
+          const float L = L4[j], M = M4[j];
           if (is_final) {
             const int64_t row = row_base + r;
-            static_cast<__nv_bfloat16*>(a.o)[row * kD + tid] = __float2bfloat16_rn(L > 0.f ? o[r] / L : 0.f);
-            if (tid == 0) {
+            static_cast<__nv_bfloat16*>(a.o)[row * kD + t] = __float2bfloat16_rn(L > 0.f ? o[j] / L : 0.f);
+            if (t == 0) {
               if (a.m) a.m[row] = M * kLn2;
               if (a.l) a.l[row] = L > 0.f ? L : 0.f;
             }
           } else {
             const int64_t pr = ((int64_t)cta * 2 + slot) * kMaxRows + r;
-            __stcg(&x.part_o[pr * kD + tid], o[r]);
-            if (tid == 0) {
+            __stcg(&x.part_o[pr * kD + t], o[j]);
+            if (t == 0) {
               __stcg(&x.part_m[pr], M);
               __stcg(&x.part_l[pr], L);
               __stcg(&x.part_t[pr], M);
@@ -886,11 +1080,35 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
           sm.flag = old == (unsigned)(mt.parts - 1);
         }
         __syncthreads();
-        if (sm.flag) {
+        if (sm.flag && g == 0) {  // the first 128 threads merge (thread t: head-dim index t of all rows)
           __threadfence();
-          // the O^T MMA of this tile is complete, so its V stage (64 KB) is free; the next
+          // the O^T MMA of this tile is complete, so its V stage (32 KB) is free; the next
           // tile's V rows go to the other stage
-          merge_segment(a, x, mt.first_cta, mt.parts, row_base, reinterpret_cast<float*>(&sm.v[vstage][0]));
+          float* scratch = reinterpret_cast<float*>(&sm.v[vstage][0]);
+          if (nt.enabled) {
+            const int hb = mt.b, hh = mt.h;
+            merge_segment<true>(a, x, mt.first_cta, mt.parts, row_base, scratch,
+                                [&](float* sM, float* sL, float (&acc)[kMaxRows]) {
+                                  float M8[8], L8[8], a8[8];
+#pragma unroll
+                                  for (int r = 0; r < 8; ++r) {
+                                    M8[r] = sM[r];
+                                    L8[r] = sL[r];
+                                    a8[r] = acc[r];
+                                  }
+                                  add_new_token(std::integral_constant<int, 8>(), 0, hb, hh, 0, M8, L8, a8);
+#pragma unroll
+                                  for (int r = 0; r < 8; ++r) acc[r] = a8[r];
+                                  group_sync<true>();  // every thread has read sM / sL
+                                  if (t < 8) {
+                                    sM[t] = M8[t];
+                                    sL[t] = L8[t];
+                                  }
+                                  group_sync<true>();
+                                });
+          } else {
+            merge_segment<true>(a, x, mt.first_cta, mt.parts, row_base, scratch);
+          }
         }
       }
     }
@@ -917,6 +1135,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   }
   JPT_SPAN(5);
   clear_empty_rows();
+  exchange_done();
   cp_async_wait<0>();  // (a copy-engine request is never left in flight: every issued tile was waited for)
   tc_fence_before();
   __syncthreads();
@@ -1026,7 +1245,7 @@ bool attention_umma_eligible(const jpt_attn_params& p) {
   return attention_mma_eligible(p) && p.kv_dtype == JPT_INT8 && R <= 8;
 }
 
-int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st) {
+int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st, const NewTokenArgs* nt_in) {
   const ScratchLayout lay = scratch_layout(p, umma_num_ctas());
   JPT_REQUIRE(p.workspace && p.workspace_bytes >= lay.total, JPT_EWORKSPACE,
               "flash_decode: workspace of %zu bytes needed, %zu given", lay.total, p.workspace_bytes);
@@ -1060,8 +1279,21 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   memset(&maps, 0, sizeof(maps));
   int big_rows = kTileU;
   const int tma_mode = tensor_maps_for(p, &maps, &big_rows);
-  launch_after_previous(flash_decode_i8_umma_kernel, dim3(lay.num_ctas), dim3(kThreads), smem_bytes, st, a, x, status, maps,
-                        tma_mode, big_rows);
+  NewTokenArgs nt;
+  memset(&nt, 0, sizeof(nt));
+  if (nt_in) {
+    nt = *nt_in;
+    if (nt.px_state == nullptr) {  // one GPU: the exchange slots live in the workspace
+      nt.px_state = reinterpret_cast<unsigned*>(ws + lay.exchange);
+      nt.px_slots[0] = reinterpret_cast<unsigned long long*>(ws + lay.exchange + kExchangeStateBytes);
+      nt.px_rank = 0;
+      nt.px_world = 1;
+    }
+    if (nt.px_wait_cycles <= 0) nt.px_wait_cycles = kWaitCycles;
+    nt.enabled = 1;
+  }
+  launch_after_previous(flash_decode_i8_umma_kernel, dim3(lay.num_ctas), dim3(kThreadsU), smem_bytes, st, a, x, status, maps,
+                        tma_mode, big_rows, nt);
   return check_launch("flash_decode_i8_umma_kernel");
 }
 

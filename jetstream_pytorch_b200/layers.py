@@ -98,12 +98,19 @@ class Int8KVAttentionKernel(_AttentionKernelBase):
   """layers.py:553-718."""
 
   quantized = True
+  fused_step = True  # the lazy ragged decode step of a GQA model runs as one launch where the shape allows
 
   def __call__(self, xq, xk, xv, mask, cache, start=None, end=None, ragged_batch_index=None,
                ragged_block_index=None):
-    _, num_heads, seqlen, _ = xq.shape
+    bsz, num_heads, seqlen, head_dim = xq.shape
     n_rep = num_heads // xk.shape[-3]
     args = (cache, start, end, ragged_batch_index, ragged_block_index, seqlen, n_rep)
+    if (self.fused_step and self.env.ragged_mha and self.env.lazy_cache_update and n_rep > 1 and seqlen == 1
+        and hasattr(cache, "update_and_attend") and cache.fused_step_supported(xq, xk)):
+      # One launch instead of update + ragged attention over the cache + flash attention over the
+      # new token + merge (the four steps below): the same softmax over the same tokens.
+      _, (out, _, _) = cache.update_and_attend(xq, xk, xv, self.layer_id, start, end)
+      return out.reshape(bsz, num_heads, seqlen, head_dim).float()  # the merge of the four-step form yields float32
     (orig_keys, orig_values, new_key, new_value, k_scaler, v_scaler, new_k_scaler,
      new_v_scaler) = cache.update(xk, xv, self.layer_id)
     existing_output, (existing_max, existing_denom) = self._attend(xq, orig_keys, orig_values, k_scaler,
