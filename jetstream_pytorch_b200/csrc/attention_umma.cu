@@ -44,9 +44,13 @@
 //
 // Every wait (mbarriers, exchange words) is bounded; a CTA that gives up raises
 // the status word of the workspace, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "attention_tiles.cuh"
 
@@ -54,7 +58,6 @@ namespace jpt {
 namespace {
 
 constexpr int kTileU = 128;     // tokens per tile = TMEM lanes = threads per CTA
-constexpr int kStagesU = 2;     // K/V ring depth
 constexpr int kTmemCols = 32;   // S^T: columns 0..15, O^T: columns 16..31
 constexpr int kColO = 16;
 constexpr int kCtasPerSm = 3;
@@ -66,10 +69,11 @@ constexpr long long kWaitCycles = 1000000000ll;  // about half a second: far bey
 constexpr int kMaxPartsU = 250;  // pieces of one segment the in-kernel merge can hold in its 16 KB of scratch
 
 struct __align__(1024) SmemU {
-  uint8_t kv[kStagesU][2][kTileU * kD];  // [stage][K, V][token][128 bytes], swizzled
+  uint8_t k[2][kTileU * kD];             // K ring: [slot][token][128 bytes], swizzled
+  uint8_t v[2][kTileU * kD];             // V ring
   uint8_t qlev[16 * kD];                 // query levels: rows 0..7 high bytes, 8..15 low bytes
   uint8_t plev[16 * kTileU];             // probability levels: row 8 l + r, one byte per token
-  uint8_t qraw[8 * kD * 2];              // bf16 query rows of the piece whose first tile is in flight
+  uint8_t qraw[2][8 * kD * 2];           // bf16 query rows of a piece that starts with a tile in flight (by tile parity)
   float xch[4][12];                      // per warp: row maxima of the tile [8], largest V scale [1]
   float red[4][8];                       // per warp: denominators at the end of a piece
   float qsc[8];                          // s_r * sm_scale * log2(e) / 254
@@ -77,10 +81,11 @@ struct __align__(1024) SmemU {
   float ntx[4];                          // new token: K amax, V amax
   float dot[4][8];                       // new token, per warp: partial logits of the 8 rows
   uint64_t bar[2];                       // MMA completion: S^T, O^T
+  uint64_t bar_k[2], bar_v[2];           // rows landed (copy-engine path), per ring slot
   uint32_t tmem_base;
   int start[3];
   int flag;
-  TileMeta meta[kStagesU];
+  TileMeta meta[4];                      // records of the tiles in flight (by tile number mod 4)
 };
 
 // 16-byte copy with compile-time offsets on both addresses (one pair of base registers per tensor)
@@ -89,11 +94,10 @@ __device__ __forceinline__ void cp_async16_at(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %2], 16;\n" ::"r"(dst), "l"(src), "n"(kOff));
 }
 template <int kI>
-__device__ __forceinline__ void cp_async_tile_rows(uint32_t kdst, uint32_t vdst, const void* kp, const void* vp) {
-  if constexpr (kI < 8) {
-    cp_async16_at<2048 * kI>(kdst, kp);
-    cp_async16_at<2048 * kI>(vdst, vp);
-    cp_async_tile_rows<kI + 1>(kdst, vdst, kp, vp);
+__device__ __forceinline__ void cp_async_tile_rows(uint32_t dst, const void* src) {
+  if constexpr (kI < 8) {  // 8 passes of 16 rows
+    cp_async16_at<2048 * kI>(dst, src);
+    cp_async_tile_rows<kI + 1>(dst, src);
   }
 }
 // The two bytes of y into level rows r, 8 + r (kRowOff = 128 r) of the probability levels.
@@ -127,8 +131,28 @@ __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8
     softmax_rows<kRow + 1>(m_run, l_run, alpha, tm, xv, ps, p_base);
   }
 }
-__device__ __forceinline__ int tiles_u(int n) { return (n + kTileU - 1) / kTileU; }
-__device__ __forceinline__ int slots_u(int n) { return n > 0 ? tiles_u(n) + kPieceCostU : 0; }
+// A segment's valid tokens form one run of consecutive rows, or two when the
+// ring wraps: [first, first + nA) and [0, n - nA).  Tiles never straddle the
+// wrap: run A is cut into tiles of 128 rows (the last one partial), then run B,
+// so a tile is always one range of rows (one box for the copy engine).
+__device__ __forceinline__ int run_a(const SeqRange& r, int S) { return min(r.n, S - r.first); }
+__device__ __forceinline__ int tiles_run(int n) { return (n + kTileU - 1) / kTileU; }
+__device__ __forceinline__ int tiles_u(const SeqRange& r, int S) {
+  const int na = run_a(r, S);
+  return tiles_run(na) + tiles_run(r.n - na);
+}
+__device__ __forceinline__ int slots_u(const SeqRange& r, int S) { return r.n > 0 ? tiles_u(r, S) + kPieceCostU : 0; }
+// Tile t of the segment: physical position of its first row and its number of valid rows.
+__device__ __forceinline__ void tile_rows(const SeqRange& r, int S, int t, int* pos, int* cnt) {
+  const int na = run_a(r, S), ta = tiles_run(na);
+  if (t < ta) {
+    *pos = r.first + t * kTileU;
+    *cnt = min(kTileU, na - t * kTileU);
+  } else {
+    *pos = (t - ta) * kTileU;
+    *cnt = min(kTileU, r.n - na - (t - ta) * kTileU);
+  }
+}
 
 // Byte offset of (row, byte) in a tile of 128-byte rows with 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz(int row, int byte) {
@@ -200,6 +224,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One box of a 4-d tensor map (128 bytes x rows x 1 x 1) into swizzled shared memory of this CTA.
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int row, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(row), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+// Tensor maps of the K and V tensors: dense [B, Hkv, S, 128 bytes] with the caller's strides
+// (box: the 128 rows of a tile), or the page pool [Hkv, pages, page_size, 128 bytes] (box: a
+// page, or 128 rows of a larger one).
+struct TmaMaps {
+  CUtensorMap k, v;
+};
+constexpr int kTmaNone = 0, kTmaDense = 1, kTmaPaged = 2;
+
 // maximum over the 32 lanes in one instruction
 __device__ __forceinline__ float warp_max(float x) {
   float r;
@@ -223,11 +265,36 @@ __device__ __forceinline__ unsigned long long gtimer_ns() {
 #define JPT_SPAN(k) do {} while (0)
 #endif
 
-// kFused = the launch carries the decode step's new token, kRound = dense_attention's rounded logit chain.
-template <bool kFused, bool kRound>
+#ifdef JPT_UMMA_PHASES
+// Debug builds only: cycles thread 0 of every CTA spent per phase of the tile loop (slot 15: tiles).
+__device__ unsigned long long g_umma_phase[1024 * 32];
+#define JPT_PH_DECL unsigned long long ph_acc[32] = {}; long long ph_last = clock64();
+#define JPT_PH(k)                                          \
+  do {                                                     \
+    if (threadIdx.x == 0) {                                \
+      const long long ph_now = clock64();                  \
+      ph_acc[k] += (unsigned long long)(ph_now - ph_last); \
+      ph_last = ph_now;                                    \
+    }                                                      \
+  } while (0)
+#define JPT_PH_FLUSH()                                                            \
+  do {                                                                            \
+    if (threadIdx.x == 0 && blockIdx.x < 1024)                                    \
+      for (int z = 0; z < 32; ++z) g_umma_phase[32 * blockIdx.x + z] = ph_acc[z]; \
+  } while (0)
+#else
+#define JPT_PH_DECL
+#define JPT_PH(k) do {} while (0)
+#define JPT_PH_FLUSH() do {} while (0)
+#endif
+
+// kFused = the launch carries the decode step's new token, kRound = dense_attention's rounded
+// logit chain, kTma = the copy engine moves the K/V rows (tensor maps) instead of the threads.
+template <bool kFused, bool kRound, bool kTma>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     flash_decode_i8_umma_kernel(const __grid_constant__ AttnArgs a, const __grid_constant__ MmaScratch x, int* status,
-                                const __grid_constant__ NewTokenArgs nt) {
+                                const __grid_constant__ NewTokenArgs nt, const __grid_constant__ TmaMaps maps, int tma_mode,
+                                int box_rows) {
   // The swizzled tiles need a 1024-byte aligned base.  The array is declared
   // with that alignment (and used in place, so that every access compiles to a
   // shared-memory instruction); a base that is not aligned after all is reported.
@@ -246,13 +313,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   if (threadIdx.x == 0 && blockIdx.x < 1024)
     for (int z = 0; z < 8; ++z) g_umma_spans[8 * blockIdx.x + z] = 0;
 #endif
-  JPT_SPAN(0);
+  JPT_SPAN(2);  // entry
 
   // ------------------------------------------------------------------ barriers and tensor memory
   // (warp 1; warp 0 is busy with the scan below, the barriers of the schedule publish the result)
   if (tid == 32) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[0])));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar[1])));
+    if constexpr (kTma) {
+      for (int z = 0; z < 2; ++z) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar_k[z])));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&sm.bar_v[z])));
+      }
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.k)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.v)) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -266,6 +341,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   // it ran under the kernel before this one (the append of the new token).
   grid_dependency_wait();
   grid_dependency_trigger();
+  JPT_SPAN(0);  // the kernel before this one is complete
 
   // ------------------------------------------------------------------ new token: amax to every rank
   unsigned nt_epoch = 0;
@@ -327,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   int mine = 0;
   for (int b = b_lo; b < b_hi; ++b) {
     int ua;
-    mine += slots_u(seq_range_x(a, x, b, &ua).n);
+    mine += slots_u(seq_range_x(a, x, b, &ua), a.S);
   }
   scan[tid] = mine;
   __syncthreads();
@@ -354,9 +430,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   }
   __syncthreads();
   const int total = scan[kThreads] * a.Hkv;  // the host checked that this fits in 31 bits
-  const int share = (total + x.num_ctas - 1) / x.num_ctas;
-  const int G0 = cta * share;
-  const int G1 = min(total, G0 + share);
+  // CTA c takes slots [G0, G1): the first `rem` CTAs one slot more than the others
+  const int share_lo = total / x.num_ctas, rem = total - share_lo * x.num_ctas;
+  const int G0 = cta * share_lo + min(cta, rem);
+  const int G1 = G0 + share_lo + (cta < rem ? 1 : 0);
+  auto cta_of_slot = [&](int slot) {
+    const int big = rem * (share_lo + 1);
+    return slot < big ? slot / (share_lo + 1) : rem + (slot - big) / max(share_lo, 1);
+  };
   {
     // the thread whose slice holds slot G0 walks it and publishes (b, h, slot in segment)
     const int lo = scan[tid] * a.Hkv, hi = scan[tid + 1] * a.Hkv;
@@ -364,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       int run = lo;
       for (int b = b_lo; b < b_hi; ++b) {
         int ua;
-        const int sl = slots_u(seq_range_x(a, x, b, &ua).n);
+        const int sl = slots_u(seq_range_x(a, x, b, &ua), a.S);
         const int nxt = run + sl * a.Hkv;
         if (G0 < nxt) {
           const int rem = G0 - run;
@@ -526,15 +607,19 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
     return;
   }
-  JPT_SPAN(2);
   const uint32_t tmem_lane = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
 
   const int8_t* kbase = static_cast<const int8_t*>(a.k);
   const int8_t* vbase = static_cast<const int8_t*>(a.v);
   const __nv_bfloat16* mask = static_cast<const __nv_bfloat16*>(a.mask);
 
+  JPT_PH_DECL
   // ------------------------------------------------------------------ producer
-  // Position of the next tile to fetch (uniform across the CTA) ...
+  // K and V rows travel in rings of their own (two slots of 16 KB each; tile j uses slot j % 2 of
+  // both).  A K slot is free as soon as the S^T MMA of its tile is complete, a V slot when the O^T
+  // MMA is: in iteration i the K rows of tile i + 2 and the V rows of tile i + 1 are requested, so
+  // every row has one and a half to two iterations to land.
+  // Position of the next tile whose K rows are to be fetched (uniform across the CTA) ...
   int pb = sm.start[0], ph = sm.start[1], pt, pslot = G0;  // pslot: global slot index of tile pt
   int pT, pn, pfirst, puse_add;
   // ... and what follows from it for this thread: 16-byte column tid % 8 of
@@ -548,32 +633,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   const int passes_per_page = pass_pages ? a.page_size / 16 : 1;
   const bool rows_packed = !a.paged && a.kv_s == kD;  // rows of a tile kD bytes apart
   const int kv_s32 = (int)a.kv_s, sc_s32 = (int)a.sc_s;
-  const int8_t *kseg, *vseg;  // segment base + this thread's column
-  int64_t scseg;
-  int ppos;                   // physical position of row 0 of tile pt
   int pfirst_cta, pparts;
 
   auto load_seq = [&]() {
     const SeqRange r = seq_range_x(a, x, pb, &puse_add);
     pn = r.n;
     pfirst = r.first;
-    pT = tiles_u(r.n);
+    pT = tiles_u(r, a.S);
   };
   auto seg_setup = [&]() {  // pt, pslot are set
-    const int64_t seg = a.paged ? (int64_t)ph * a.kv_h : (int64_t)pb * a.kv_b + (int64_t)ph * a.kv_h;
-    kseg = kbase + seg + pcol * 16;
-    vseg = vbase + seg + pcol * 16;
-    scseg = a.paged ? 0 : (int64_t)pb * a.sc_b;
-    ppos = pfirst + pt * kTileU;
-    if (ppos >= a.S) ppos -= a.S;
     const int t0slot = pslot - pt;  // slot of tile 0 of this segment
-    pfirst_cta = t0slot / share;
-    pparts = (t0slot + pT - 1) / share - pfirst_cta + 1;
+    pfirst_cta = cta_of_slot(t0slot);
+    pparts = cta_of_slot(t0slot + pT - 1) - pfirst_cta + 1;
   };
   auto advance = [&]() {
     ++pslot;
-    ppos += kTileU;
-    if (ppos >= a.S) ppos -= a.S;
     if (++pt < pT) return;
     pt = 0;
     pslot += kPieceCostU;  // the overhead slots of the next segment
@@ -602,39 +676,23 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     seg_setup();
   }
 
-  float nks = 1.f, nvs = 0.f;  // scales of this thread's token in the tile fetched last
-  bool first_issue = true;
-
-  auto issue_tile = [&](int stage) {
-    const int j0 = pt * kTileU;
-    const bool piece_start = first_issue || pt == 0;
-    first_issue = false;
-    if (tid == 0) {
-      TileMeta mt;
-      mt.b = pb; mt.h = ph; mt.t = pt; mt.T = pT; mt.n = pn; mt.first = pfirst; mt.use_add = puse_add;
-      mt.first_cta = pfirst_cta; mt.parts = pparts;
-      mt.pad[0] = mt.pad[1] = 0;
-      mt.pad[2] = pslot + 1 >= G1;  // no tile follows in this CTA's share
-      sm.meta[stage] = mt;
-    }
-    const uint32_t kdst = smem_u32(&sm.kv[stage][0][0]) + pdst;
-    const uint32_t vdst = smem_u32(&sm.kv[stage][1][0]) + pdst;
-    if (rows_packed && j0 + kTileU <= pn && ppos + kTileU <= a.S) {
-      // whole tile valid, no ring wrap, rows kD bytes apart: one address per tensor
-      const int64_t off = (int64_t)(ppos + prow) * kD;
-      const int8_t* kp = kseg + off;
-      const int8_t* vp = vseg + off;
-      cp_async_tile_rows<0>(kdst, vdst, kp, vp);
+  // Rows [pos, pos + cnt) of segment (b, h) of one tensor (a tile: cnt <= 128, no ring wrap inside)
+  // into the 16 KB at `dst`, by all threads; paged caches: pos is the token index.
+  auto copy_rows = [&](uint32_t dst, const int8_t* base, int b, int h, int pos, int cnt) {
+    const int8_t* seg = base + (a.paged ? (int64_t)h * a.kv_h : (int64_t)b * a.kv_b + (int64_t)h * a.kv_h) + pcol * 16;
+    dst += pdst;
+    if (rows_packed && cnt == kTileU) {
+      // whole tile valid, rows kD bytes apart: one address
+      cp_async_tile_rows<0>(dst, seg + (int64_t)(pos + prow) * kD);
     } else if (pass_pages) {
-      // paged caches start at position 0: pass i (rows 16 i ..) lies inside one page
-      int pi = j0 / a.page_size, within = (j0 % a.page_size) / 16;
+      // pass i (rows 16 i ..) lies inside one page (tiles of paged caches start at multiples of 128)
+      int pi = pos / a.page_size, within = (pos % a.page_size) / 16;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const bool valid = j0 + 16 * i + prow < pn;
-        const int page = (j0 + 16 * i) < pn ? a.page_table[(int64_t)pb * a.max_pages + pi] : 0;
+        const bool valid = 16 * i + prow < cnt;
+        const int page = 16 * i < cnt ? a.page_table[(int64_t)b * a.max_pages + pi] : 0;
         const int64_t off = (int64_t)page * a.kv_page + (int64_t)(within * 16 + prow) * kD;
-        cp_async16(kdst + 2048 * i, kseg + off, valid);
-        cp_async16(vdst + 2048 * i, vseg + off, valid);
+        cp_async16(dst + 2048 * i, seg + off, valid);
         if (++within == passes_per_page) {
           within = 0;
           ++pi;
@@ -644,51 +702,113 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r = prow + 16 * i;
-        const bool valid = j0 + r < pn;
-        int pos = valid ? ppos + r : ppos;
-        if (pos >= a.S) pos -= a.S;
+        const bool valid = r < cnt;
+        const int tok = valid ? pos + r : pos;
         int64_t off;
         if (a.paged) {
-          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
-          off = (int64_t)pg * a.kv_page + (int64_t)(pos % a.page_size) * kD;
+          const int pg = a.page_table[(int64_t)b * a.max_pages + tok / a.page_size];
+          off = (int64_t)pg * a.kv_page + (int64_t)(tok % a.page_size) * kD;
         } else {
-          off = (int64_t)pos * kv_s32;
+          off = (int64_t)tok * kv_s32;
         }
-        cp_async16(kdst + 2048 * i, kseg + off, valid);
-        cp_async16(vdst + 2048 * i, vseg + off, valid);
-      }
-    }
-    if (piece_start) {
-      const __nv_bfloat16* q = qbase + ((int64_t)pb * a.Hkv + ph) * R * kD;
-      for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.qraw[0]) + ch * 16, q + ch * 8, true);
-    }
-    // scales of token `tid` of the tile, consumed by this same thread
-    nks = 1.f;
-    nvs = 0.f;
-    if (j0 + tid < pn) {
-      nvs = 1.f;
-      if (quant) {
-        int pos = ppos + tid;
-        if (pos >= a.S) pos -= a.S;
-        int64_t sidx;
-        if (a.paged) {
-          const int pg = a.page_table[(int64_t)pb * a.max_pages + pos / a.page_size];
-          sidx = (int64_t)pg * a.page_size + pos % a.page_size;
-        } else {
-          sidx = scseg + (int64_t)pos * sc_s32;
-        }
-        nks = load_scale(a.k_scale, sidx, a.scale_is_f32);
-        nvs = load_scale(a.v_scale, sidx, a.scale_is_f32);
+        cp_async16(dst + 2048 * i, seg + off, valid);
       }
     }
   };
-  // Fetch the next tile of the share into `stage`, or mark the stage as empty.
-  auto produce = [&](int stage) {
+  // The same by the copy engine, requested by the calling thread alone: whole boxes (rows past cnt
+  // hold other tokens or the zero fill of the tensor's edge; their logits are masked and their
+  // probabilities zero), 16 KB in all, counted on `bar`.
+  auto request_rows = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int b, int h, int pos, int cnt) {
+    fence_async_smem();  // earlier accesses of the threads to this slot (the merge scratch) come first
+    mbar_arrive_expect_tx(bar, (uint32_t)(kTileU * kD));
+    if (tma_mode == kTmaDense) {
+      tma_load_rows(dst, map, pos, h, b, bar);
+    } else if (box_rows == kTileU) {  // pages of 128 rows or more: the tile lies inside one
+      const int page = a.page_table[(int64_t)b * a.max_pages + pos / a.page_size];
+      tma_load_rows(dst, map, pos % a.page_size, page, h, bar);
+    } else {  // one box per page
+      int pi = pos / a.page_size;
+      for (int r = 0; r < kTileU; r += box_rows, ++pi) {
+        const int page = r < cnt ? a.page_table[(int64_t)b * a.max_pages + pi] : 0;
+        tma_load_rows(dst + r * kD, map, 0, page, h, bar);
+      }
+    }
+  };
+
+  // K rows of the next tile of the share (with its record and, when it starts a piece, its
+  // query rows) into ring position `seq`; a record with t = -1 when the share is exhausted.
+  auto issue_k = [&](int seq) {
     if (pslot < G1) {
-      issue_tile(stage);
+      SeqRange rg;
+      rg.n = pn;
+      rg.first = pfirst;
+      int pos, cnt;
+      tile_rows(rg, a.S, pt, &pos, &cnt);
+      JPT_PH(18);
+      if (tid == 0) {
+        TileMeta mt;
+        mt.b = pb; mt.h = ph; mt.t = pt; mt.T = pT; mt.n = pn; mt.first = pfirst; mt.use_add = puse_add;
+        mt.first_cta = pfirst_cta; mt.parts = pparts;
+        mt.pad[0] = cnt;  // valid rows of the tile
+        mt.pad[1] = pos;  // position of its first row (paged: token index)
+        mt.pad[2] = pslot + 1 >= G1;  // no tile follows in this CTA's share
+        sm.meta[seq & 3] = mt;
+        if constexpr (kTma) request_rows(smem_u32(&sm.k[seq & 1][0]), &maps.k, smem_u32(&sm.bar_k[seq & 1]), pb, ph, pos, cnt);
+      }
+      JPT_PH(19);
+      if constexpr (!kTma) copy_rows(smem_u32(&sm.k[seq & 1][0]), kbase, pb, ph, pos, cnt);
+      if (seq == 0 || pt == 0) {  // a piece starts with this tile
+        const __nv_bfloat16* q = qbase + ((int64_t)pb * a.Hkv + ph) * R * kD;
+        for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.qraw[seq & 1][0]) + ch * 16, q + ch * 8, true);
+      }
+      JPT_PH(20);
       advance();
+      JPT_PH(21);
     } else if (tid == 0) {
-      sm.meta[stage].t = -1;
+      sm.meta[seq & 3].t = -1;
+    }
+    cp_async_commit();
+  };
+  // V rows of the tile at ring position `seq` (its record is in shared memory), and the
+  // scales of this thread's token in it, consumed by this same thread an iteration later:
+  // they stay raw bits until then, so that nothing here waits for the loads.
+  const bool sc_f32 = a.scale_is_f32 != 0;
+  const uint32_t raw_one = sc_f32 ? 0x3f800000u : 0x3f80u;
+  auto scale_of = [&](uint32_t raw) { return __uint_as_float(sc_f32 ? raw : raw << 16); };
+  uint32_t nks = raw_one, nvs = 0u;
+  auto issue_v = [&](int seq) {
+    const int mb = sm.meta[seq & 3].b, mh = sm.meta[seq & 3].h, mtile = sm.meta[seq & 3].t;
+    const int cnt = sm.meta[seq & 3].pad[0], pos = sm.meta[seq & 3].pad[1];
+    if (mtile >= 0) {
+      JPT_PH(16);
+      if constexpr (kTma) {
+        if (tid == 0) request_rows(smem_u32(&sm.v[seq & 1][0]), &maps.v, smem_u32(&sm.bar_v[seq & 1]), mb, mh, pos, cnt);
+        JPT_PH(17);
+      } else {
+        copy_rows(smem_u32(&sm.v[seq & 1][0]), vbase, mb, mh, pos, cnt);
+      }
+      nks = raw_one;
+      nvs = 0u;
+      if (tid < cnt) {
+        nvs = raw_one;
+        if (quant) {
+          const int tok = pos + tid;
+          int64_t sidx;
+          if (a.paged) {
+            const int pg = a.page_table[(int64_t)mb * a.max_pages + tok / a.page_size];
+            sidx = (int64_t)pg * a.page_size + tok % a.page_size;
+          } else {
+            sidx = (int64_t)mb * a.sc_b + (int64_t)tok * sc_s32;
+          }
+          if (sc_f32) {
+            nks = static_cast<const uint32_t*>(a.k_scale)[sidx];
+            nvs = static_cast<const uint32_t*>(a.v_scale)[sidx];
+          } else {
+            nks = static_cast<const uint16_t*>(a.k_scale)[sidx];
+            nvs = static_cast<const uint16_t*>(a.v_scale)[sidx];
+          }
+        }
+      }
     }
     cp_async_commit();
   };
@@ -704,17 +824,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   // plev is 1024-byte aligned, so the XOR with r << 4 can be applied to the whole address.
   const uint32_t p_base = smem_u32(&sm.plev[0]) + (tid & 15) + ((uint32_t)(tid >> 4) << 4);
 
-  // Query levels of the piece that starts with the tile in `st` (when it
+  // Query levels of the piece that starts with tile number `seq` of this CTA (when it
   // starts one), then S^T of that tile on the tensor core.  Called by the whole
-  // CTA once the tile's rows have landed and a barrier has made them (and the
+  // CTA once the tile's K rows have landed and a barrier has made them (and the
   // record) visible; the logits of the tile before are out of tensor memory.
-  auto prepare = [&](int st, const TileMeta& mt, bool first) {
+  auto prepare = [&](int seq, const TileMeta& mt, bool first) {
     if (first || mt.t == 0) {
       // thread (row = tid / 16, chunk = tid % 16) converts 8 values of one query row
       const int row = tid >> 4, ch = tid & 15;
       float f[8];
       if (row < R) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[row * (kD * 2) + ch * 16]);
+        const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[seq & 1][row * (kD * 2) + ch * 16]);
         const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -752,8 +872,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       __syncthreads();
     }
     if (tid == 0) {
+      if constexpr (kTma) {
+        if (!mbar_wait(smem_u32(&sm.bar_k[seq & 1]), (uint32_t)(seq >> 1) & 1u)) dead = true;
+      }
       tc_fence_after();
-      const uint32_t k_addr = smem_u32(&sm.kv[st][0][0]);
+      const uint32_t k_addr = smem_u32(&sm.k[seq & 1][0]);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma_i8(tmem, umma_desc(k_addr + 32 * ks), umma_desc(q_desc_addr + 32 * ks), kIdescS, ks > 0);
@@ -778,8 +901,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   // issued at the end of iteration i, and O^T of tile i is collected in
   // iteration i+1 (at once only when tile i ends a piece), so neither MMA is
   // waited for right after it was issued.
-  produce(0);
-  cp_async_wait<0>();
+  // Copy groups are committed in the order K0, V0, K1, then V(i+1), K(i+2) in iteration i.
+  issue_k(0);
+  __syncthreads();  // the record of tile 0
+  issue_v(0);
+  issue_k(1);
+  cp_async_wait<1>();  // K0 (with the query rows) and V0
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -789,10 +916,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 
   float alpha_prev[8], cmax_prev = 0.f;
   bool pending = false;  // O^T of the tile before has not been added yet
-  int stage = 0;
   for (int i = 0; mt.t >= 0; ++i) {
-    const float cks = nks, cvs = nvs;  // scales of this thread's token in the tile of `stage`
-    const int next_stage = stage ^ 1;
+    JPT_PH(11);
+    const float cks = scale_of(nks), cvs = scale_of(nvs);  // scales of this thread's token in tile i
     const bool last_of_share = mt.pad[2] != 0;
     const uint32_t par = (uint32_t)i & 1u;
     if (i == 0 || mt.t == 0) {  // a piece starts (the one before was flushed when it ended)
@@ -806,10 +932,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
 
     // ---------------- the output of the tile before and the logits of this one leave
-    // tensor memory in one round trip; the stage of the tile before is free after that
+    // tensor memory in one round trip; the K slot of this tile and the V slot of the tile
+    // before are free after that
     if (!mbar_wait(bar_s, par)) dead = true;
     if (pending && !mbar_wait(bar_o, par ^ 1u)) dead = true;
     tc_fence_after();
+    JPT_PH(0);
     float xv[8];
     {
       uint32_t s[16];
@@ -827,15 +955,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         tmem_ld16(tmem_lane, s);
         tmem_ld_wait();
       }
-      produce(next_stage);
-      const bool valid = mt.t * kTileU + tid < mt.n;
-      float mk = valid ? 0.f : -INFINITY;  // a token past the end: finite dot product + (-inf)
-      if (mt.use_add && valid) {  // additive mask that is not a plain 0 / -inf range (rare)
-        SeqRange rg;
-        rg.n = mt.n;
-        rg.first = mt.first;
-        mk = __bfloat162float(mask[(int64_t)mt.b * a.mk_b + physical_pos(a, rg, mt.t * kTileU + tid)]);
-      }
+      JPT_PH(1);
+      issue_v(i + 1);
+      issue_k(i + 2);
+      JPT_PH(2);
+      const bool valid = tid < mt.pad[0];
+      float mk = valid ? 0.f : -INFINITY;  // a row past the tile's tokens: finite dot product + (-inf)
+      if (mt.use_add && valid)             // additive mask that is not a plain 0 / -inf range (rare)
+        mk = __bfloat162float(mask[(int64_t)mt.b * a.mk_b + mt.pad[1] + tid]);
       if constexpr (!kRound) {
         const float4 q0 = *reinterpret_cast<const float4*>(&sm.qsc[0]), q1 = *reinterpret_cast<const float4*>(&sm.qsc[4]);
         const float qc[8] = {q0.x * cks, q0.y * cks, q0.z * cks, q0.w * cks, q1.x * cks, q1.y * cks, q1.z * cks, q1.w * cks};
@@ -863,7 +990,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
     }
     tc_fence_before();
+    JPT_PH(3);
     __syncthreads();
+    JPT_PH(4);
 
     float alpha[8];
     float cmax;
@@ -889,29 +1018,65 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       const float ps = fminf(cvs * rc, 65535.f);
       softmax_rows<0>(m_run, l_run, alpha, tm, xv, ps, p_base);
     }
+    JPT_PH(5);
+    cp_async_wait<3>();  // V rows of this tile (younger groups: K(i+1), V(i+1), K(i+2))
     fence_async_smem();
+    JPT_PH(12);
     __syncthreads();
+    JPT_PH(6);
 
     // ---------------- O^T = V^T Pl^T on the tensor core
     if (tid == 0) {
+      if constexpr (kTma) {
+        if (!mbar_wait(smem_u32(&sm.bar_v[i & 1]), (uint32_t)(i >> 1) & 1u)) dead = true;
+      }
       tc_fence_after();
-      const uint32_t v_addr = smem_u32(&sm.kv[stage][1][0]);
+      const uint32_t v_addr = smem_u32(&sm.v[i & 1][0]);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         umma_i8(tmem + kColO, umma_desc(v_addr + 4096 * ks), umma_desc(p_desc_addr + 32 * ks), kIdescO, ks > 0);
       umma_commit(bar_o);
     }
 
-    if (!(last_of_share || mt.t == mt.T - 1)) {
+    JPT_PH(7);
+    // The tile that ends a piece leaves through the epilogue below, after the next tile's S^T has been
+    // issued (the tensor core and the copies keep going while the rows are written or merged).
+    const bool piece_ends = last_of_share || mt.t == mt.T - 1;
+    const int cb = mt.b, chd = mt.h, ct = mt.t, cT = mt.T, cfirst_cta = mt.first_cta, cparts = mt.parts;
+    if (!piece_ends) {
 #pragma unroll
       for (int r = 0; r < 8; ++r) alpha_prev[r] = alpha[r];
       cmax_prev = cmax;
       pending = true;
-    } else {
+    }
+
+    // ---------------- the next tile: its K rows were requested an iteration ago
+    JPT_PH(28);
+    cp_async_wait<2>();  // (younger groups: V(i+1), K(i+2))
+    JPT_PH(13);
+    fence_async_smem();
+    tc_fence_before();
+    if (__syncthreads_or(dead)) {
+      if (tid == 0) {
+        atomicExch(status, 1);
+        if constexpr (kTma) {  // requests of the copy engine that may still be in flight get their (bounded) time
+          if (sm.meta[(i + 1) & 3].t >= 0) {
+            mbar_wait(smem_u32(&sm.bar_k[(i + 1) & 1]), (uint32_t)((i + 1) >> 1) & 1u);
+            mbar_wait(smem_u32(&sm.bar_v[(i + 1) & 1]), (uint32_t)((i + 1) >> 1) & 1u);
+            if (sm.meta[(i + 2) & 3].t >= 0) mbar_wait(smem_u32(&sm.bar_k[i & 1]), (uint32_t)((i + 2) >> 1) & 1u);
+          }
+        }
+      }
+      break;
+    }
+    JPT_PH(9);
+    mt = sm.meta[(i + 1) & 3];
+    if (mt.t >= 0) prepare(i + 1, mt, false);
+    if (piece_ends) {
       // ---------------- end of a piece: write the rows, or a partial for the merge
-      const bool is_final = piece_t0 == 0 && mt.t == mt.T - 1;
+      const bool is_final = piece_t0 == 0 && ct == cT - 1;
       const int slot = piece_t0 > 0 ? 0 : 1;
-      const int64_t row_base = ((int64_t)mt.b * a.Hkv + mt.h) * R;
+      const int64_t row_base = ((int64_t)cb * a.Hkv + chd) * R;
       // denominators: sum the token shares of the 128 threads (while the last O^T MMA runs)
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
@@ -920,8 +1085,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         for (int sh = 1; sh <= 16; sh <<= 1) l += __shfl_xor_sync(0xffffffffu, l, sh);
         if (lane == r) sm.red[warp][r] = l;
       }
+      JPT_PH(22);
       __syncthreads();
+      JPT_PH(23);
       add_output(par, alpha, cmax);
+      JPT_PH(24);
       float L8[8], M8[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
@@ -929,7 +1097,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         M8[r] = m_run[r] > 0.5f * kNoMax ? m_run[r] : -INFINITY;  // every logit of the row was masked
       }
       if constexpr (kFused) {
-        if (is_final) add_new_token(mt.b, mt.h, M8, L8, o);
+        if (is_final) add_new_token(cb, chd, M8, L8, o);
       }
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
@@ -956,20 +1124,23 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       if (!is_final) {
         // Whoever delivers the last piece of the segment combines all of them.
         // The counter wraps back to zero on that arrival, ready for the next launch.
+        JPT_PH(25);
         __threadfence();
+        JPT_PH(26);
         __syncthreads();
         if (tid == 0) {
-          const unsigned old = atomicInc(&x.counters[mt.b * a.Hkv + mt.h], (unsigned)(mt.parts - 1));
-          sm.flag = old == (unsigned)(mt.parts - 1);
+          const unsigned old = atomicInc(&x.counters[cb * a.Hkv + chd], (unsigned)(cparts - 1));
+          sm.flag = old == (unsigned)(cparts - 1);
         }
         __syncthreads();
+        JPT_PH(27);
         if (sm.flag) {
           __threadfence();
-          // both MMAs of this stage are complete, so its K rows (16 KB) are free
-          float* scratch = reinterpret_cast<float*>(&sm.kv[stage][0][0]);
+          // the O^T MMA of this tile is complete, so its V slot (16 KB) is free until the next iteration
+          float* scratch = reinterpret_cast<float*>(&sm.v[i & 1][0]);
           if constexpr (kFused) {
-            const int hb = mt.b, hh = mt.h;
-            merge_segment<false>(a, x, mt.first_cta, mt.parts, row_base, scratch,
+            const int hb = cb, hh = chd;
+            merge_segment<false>(a, x, cfirst_cta, cparts, row_base, scratch,
                                  [&](float* sM, float* sL, float (&acc)[kMaxRows]) {
                                    float Mh[8], Lh[8], ah[8];
 #pragma unroll
@@ -988,32 +1159,25 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                                    __syncthreads();
                                  });
           } else {
-            merge_segment<false>(a, x, mt.first_cta, mt.parts, row_base, scratch);
+            merge_segment<false>(a, x, cfirst_cta, cparts, row_base, scratch);
           }
         }
       }
+    
     }
-
-    // ---------------- the next tile: its rows have had the iteration to land
-    cp_async_wait<0>();
-    fence_async_smem();
-    tc_fence_before();
-    if (__syncthreads_or(dead)) {
-      if (tid == 0) atomicExch(status, 1);
-      break;
-    }
-    mt = sm.meta[next_stage];
-    if (mt.t >= 0) prepare(next_stage, mt, false);
-    stage = next_stage;
+    JPT_PH(10);
+#ifdef JPT_UMMA_PHASES
+    ph_acc[15] += 1;
+#endif
     if (i == 0) JPT_SPAN(4);
 #ifdef JPT_UMMA_SPANS
     if (threadIdx.x == 0 && blockIdx.x < 1024) {
       g_umma_spans[8 * blockIdx.x + 6] += 1;                                  // tiles
-      if (i == 0 || sm.meta[stage ^ 1].t >= 0) g_umma_spans[8 * blockIdx.x + 7] += (mt.t == 0);  // pieces started after the first
     }
 #endif
   }
   JPT_SPAN(5);
+  JPT_PH_FLUSH();
   clear_empty_rows();
   exchange_done();
   cp_async_wait<0>();
@@ -1022,9 +1186,102 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemCols) : "memory");
   }
+  JPT_SPAN(7);  // end
 }
 
 int umma_num_ctas() { return sm_count() * kCtasPerSm; }
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// [dims[3]][dims[2]][dims[1]][128] bytes with byte strides str[0..2] between rows / dims[2] / dims[3].
+bool encode_rows_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&str)[3], int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint32_t box[4] = {(cuuint32_t)kD, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, str, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+  const void *k, *v;
+  int64_t d1, d2, d3, s0, s1, s2;
+  int mode, box_rows, device;
+  bool operator==(const MapKey& o) const {
+    return k == o.k && v == o.v && d1 == o.d1 && d2 == o.d2 && d3 == o.d3 && s0 == o.s0 && s1 == o.s1 && s2 == o.s2 &&
+           mode == o.mode && box_rows == o.box_rows && device == o.device;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  TmaMaps maps;
+};
+
+// Tensor maps for this call (cached per tensor pair and geometry); kTmaNone when
+// the layout cannot be described (the kernel then copies the rows with its threads).
+// JPT_NO_TMA=1 in the environment forces that path.
+int tensor_maps_for(const jpt_attn_params& p, TmaMaps* out, int* box_rows) {
+  static const bool off = [] {
+    const char* e = getenv("JPT_NO_TMA");
+    return e && e[0] == '1';
+  }();
+  if (off) return kTmaNone;
+  MapKey key{};
+  key.k = p.k;
+  key.v = p.v;
+  key.device = current_device();
+  if (p.paged) {
+    if (p.page_size % 16 != 0 || p.kv_page != (int64_t)p.page_size * kD || p.kv_h <= 0 || p.kv_h % p.kv_page != 0) return kTmaNone;
+    if ((kTileU % p.page_size) != 0 && (p.page_size % kTileU) != 0) return kTmaNone;
+    key.mode = kTmaPaged;
+    key.box_rows = p.page_size < kTileU ? p.page_size : kTileU;
+    key.d1 = p.page_size; key.d2 = p.kv_h / p.kv_page; key.d3 = p.Hkv;
+    key.s0 = kD; key.s1 = p.kv_page; key.s2 = p.kv_h;
+  } else {
+    key.mode = kTmaDense;
+    key.box_rows = kTileU;
+    key.d1 = p.S; key.d2 = p.Hkv; key.d3 = p.B;
+    key.s0 = p.kv_s; key.s1 = p.kv_h; key.s2 = p.kv_b;
+    if (p.Hkv == 1 && key.s1 <= 0) key.s1 = key.s0 * p.S;  // a single head: its stride is never used
+    if (p.B == 1 && key.s2 <= 0) key.s2 = key.s1 * p.Hkv;
+  }
+  if (key.s0 % 16 || key.s1 % 16 || key.s2 % 16 || key.s0 < kD || key.s1 <= 0 || key.s2 <= 0) return kTmaNone;
+  if (!aligned(p.k, 16) || !aligned(p.v, 16)) return kTmaNone;
+  *box_rows = key.box_rows;
+  static std::mutex mu;
+  static std::vector<MapEntry> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const MapEntry& e : cache) {
+    if (e.key == key) {
+      *out = e.maps;
+      return key.mode;
+    }
+  }
+  const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)key.d1, (cuuint64_t)key.d2, (cuuint64_t)key.d3};
+  const cuuint64_t str[3] = {(cuuint64_t)key.s0, (cuuint64_t)key.s1, (cuuint64_t)key.s2};
+  MapEntry e;
+  e.key = key;
+  if (!encode_rows_map(&e.maps.k, p.k, dims, str, key.box_rows) || !encode_rows_map(&e.maps.v, p.v, dims, str, key.box_rows))
+    return kTmaNone;
+  if (cache.size() >= 4096) cache.clear();
+  cache.push_back(e);
+  *out = e.maps;
+  return key.mode;
+}
 
 }  // namespace
 
@@ -1032,7 +1289,7 @@ bool attention_umma_eligible(const jpt_attn_params& p) {
   const int R = (p.Hq / p.Hkv) * p.Tq;
   // the merge of a segment's pieces keeps (pieces + 4) * 16 floats in its scratch; a segment spans at most
   // its tiles + 1 CTAs
-  const int max_tiles = (p.S + kTileU - 1) / kTileU;
+  const int max_tiles = (p.S + kTileU - 1) / kTileU + 1;  // (+1: a ring that wraps is cut run by run)
   return attention_mma_eligible(p) && p.kv_dtype == JPT_INT8 && R <= 8 && max_tiles + 1 <= kMaxPartsU;
 }
 
@@ -1053,6 +1310,7 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   int* status = reinterpret_cast<int*>(ws + kWorkspaceStatusOffset);
 
   constexpr int smem_bytes = (int)sizeof(SmemU);
+  static_assert(kCtasPerSm * (smem_bytes + 1024) <= 228 * 1024, "shared memory of the resident CTAs exceeds the SM");
   static std::atomic<bool> configured[kMaxDevices];
   if (int rc = configure_once_per_device(configured, "flash_decode_i8_umma_kernel", [] {
         cudaError_t e = cudaSuccess;
@@ -1061,10 +1319,14 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
           if (e == cudaSuccess)
             e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         };
-        set(flash_decode_i8_umma_kernel<false, false>);
-        set(flash_decode_i8_umma_kernel<false, true>);
-        set(flash_decode_i8_umma_kernel<true, false>);
-        set(flash_decode_i8_umma_kernel<true, true>);
+        set(flash_decode_i8_umma_kernel<false, false, false>);
+        set(flash_decode_i8_umma_kernel<false, false, true>);
+        set(flash_decode_i8_umma_kernel<false, true, false>);
+        set(flash_decode_i8_umma_kernel<false, true, true>);
+        set(flash_decode_i8_umma_kernel<true, false, false>);
+        set(flash_decode_i8_umma_kernel<true, false, true>);
+        set(flash_decode_i8_umma_kernel<true, true, false>);
+        set(flash_decode_i8_umma_kernel<true, true, true>);
         return e;
       }))
     return rc;
@@ -1084,16 +1346,32 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
     if (nt.px_wait_cycles <= 0) nt.px_wait_cycles = kWaitCycles;
     nt.enabled = 1;
   }
-  const bool fused = nt.enabled != 0, round = a.round_logits != 0;
+  TmaMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  int box_rows = kTileU;
+  const int tma_mode = tensor_maps_for(p, &maps, &box_rows);
+  const bool fused = nt.enabled != 0, round = a.round_logits != 0, tma = tma_mode != kTmaNone;
   const dim3 grid(lay.num_ctas), block(kThreads);
-  if (fused && round) launch_after_previous(flash_decode_i8_umma_kernel<true, true>, grid, block, smem_bytes, st, a, x, status, nt);
-  else if (fused) launch_after_previous(flash_decode_i8_umma_kernel<true, false>, grid, block, smem_bytes, st, a, x, status, nt);
-  else if (round) launch_after_previous(flash_decode_i8_umma_kernel<false, true>, grid, block, smem_bytes, st, a, x, status, nt);
-  else launch_after_previous(flash_decode_i8_umma_kernel<false, false>, grid, block, smem_bytes, st, a, x, status, nt);
+#define JPT_UMMA_LAUNCH(F, Rd, T) \
+  launch_after_previous(flash_decode_i8_umma_kernel<F, Rd, T>, grid, block, smem_bytes, st, a, x, status, nt, maps, tma_mode, box_rows)
+  if (fused) {
+    if (round) { if (tma) JPT_UMMA_LAUNCH(true, true, true); else JPT_UMMA_LAUNCH(true, true, false); }
+    else       { if (tma) JPT_UMMA_LAUNCH(true, false, true); else JPT_UMMA_LAUNCH(true, false, false); }
+  } else {
+    if (round) { if (tma) JPT_UMMA_LAUNCH(false, true, true); else JPT_UMMA_LAUNCH(false, true, false); }
+    else       { if (tma) JPT_UMMA_LAUNCH(false, false, true); else JPT_UMMA_LAUNCH(false, false, false); }
+  }
+#undef JPT_UMMA_LAUNCH
   return check_launch("flash_decode_i8_umma_kernel");
 }
 
 }  // namespace jpt
+
+#ifdef JPT_UMMA_PHASES
+extern "C" int jpt_debug_umma_phases(unsigned long long* out_host, int n_ctas) {
+  return (int)cudaMemcpyFromSymbol(out_host, jpt::g_umma_phase, sizeof(unsigned long long) * 32 * n_ctas);
+}
+#endif
 
 #ifdef JPT_UMMA_SPANS
 extern "C" int jpt_debug_umma_spans(unsigned long long* out_host, int n_ctas) {
