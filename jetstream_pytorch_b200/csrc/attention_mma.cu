@@ -810,7 +810,7 @@ __global__ void __launch_bounds__(kThreads, kRows16 ? 2 : (kBf16 ? 3 : 4))
         __syncthreads();
         if (s_flag) {
           __threadfence();
-          merge_segment(a, x, mt.first_cta, mt.parts, row_base, obuf);
+          merge_segment(a, x, mt.first_cta, mt.parts, row_base);
         }
       }
       // The next iteration's barrier orders these reads before the stage is refilled.

@@ -74,113 +74,95 @@ __device__ __forceinline__ SeqRange seq_range_x(const AttnArgs& a, const MmaScra
   return seq_range(a, b);
 }
 
-// Barrier of the 128 threads that run merge_segment: the whole CTA, or (in a
-// CTA with more warps) threads 0..127 through named barrier 2.
-template <bool kWorkerGroup>
-__device__ __forceinline__ void group_sync() {
-  if constexpr (kWorkerGroup) {
-    asm volatile("bar.sync 2, 128;" ::: "memory");
-  } else {
-    __syncthreads();
-  }
-}
-
 // Combine the `parts` partials of one segment (CTAs first .. first+parts-1) and
-// write its R final rows.  `scratch` is at least (parts + 4) * 16 floats of
-// shared memory.  Called by 128 threads (threadIdx.x 0..127).
+// write its R final rows.  Called by 128 threads (threadIdx.x 0..127): thread t
+// owns head-dim index t of every row
+// and the rows' statistics travel by warp shuffles, so there is no staging in
+// shared memory and no barrier; two pieces are combined per step with all of
+// their loads in flight at once (one L2 round trip for the usual two pieces).
 struct NoMergeHook {
-  __device__ __forceinline__ void operator()(float*, float*, float (&)[kMaxRows]) const {}
+  template <typename A>
+  __device__ __forceinline__ void operator()(A&, A&, A&) const {}
 };
 
 // `hook(M, L, acc)` runs after the pieces are combined and before the rows are
-// written: M[r] the maximum (log2 domain) and L[r] the denominator of row r (in
-// shared memory, read by every thread), acc[r] this thread's head-dim component
-// of the unnormalised output.  It may change all three (the tcgen05 kernel adds
-// the decode step's new token there) and is called by all 128 threads.
-template <bool kWorkerGroup = false, typename Hook = NoMergeHook>
-static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int first, int parts, int64_t row_base,
-                                     float* scratch, Hook hook = Hook()) {
-  const int tid = threadIdx.x, R = a.R;
-  float* s_w = scratch;                     // [parts][16] weights
-  float* s_M = scratch + parts * kMaxRows;  // [16] reference maximum
-  float* s_L = s_M + kMaxRows;              // [16] denominator relative to s_M
-  for (int i = tid; i < parts * R; i += kThreads) {
-    const int pi = i / R, r = i - pi * R;
-    s_w[pi * kMaxRows + r] = __ldcg(&x.part_m[((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows + r]);
-  }
-  group_sync<kWorkerGroup>();
-  if (tid < R) {
-    float M = -INFINITY;
-    for (int pi = 0; pi < parts; ++pi) M = fmaxf(M, s_w[pi * kMaxRows + tid]);
-    s_M[tid] = M;
-  }
-  group_sync<kWorkerGroup>();
-  for (int i = tid; i < parts * R; i += kThreads) {
-    const int pi = i / R, r = i - pi * R;
-    const float mw = s_w[pi * kMaxRows + r];
-    s_w[pi * kMaxRows + r] = mw == -INFINITY ? 0.f : fast_exp2(mw - s_M[r]);
-  }
-  group_sync<kWorkerGroup>();
-  if (tid < R) {
-    float L = 0.f, mt = -INFINITY;
-    for (int pi = 0; pi < parts; ++pi) {
-      const int64_t pr = ((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows + tid;
-      L += s_w[pi * kMaxRows + tid] * __ldcg(&x.part_l[pr]);
-      mt = fmaxf(mt, __ldcg(&x.part_t[pr]));
+// written: M[r] the maximum (log2 domain) and L[r] the denominator of row r
+// (equal in every thread), acc[r] this thread's head-dim component of the
+// unnormalised output.  It may change all three, the same way in every thread
+// (the tcgen05 kernel adds the decode step's new token there), and is called by
+// all 128 threads.
+template <int kR, typename Hook>
+static __device__ __forceinline__ void merge_rows(const AttnArgs& a, const MmaScratch& x, int first, int parts, int64_t row_base,
+                                                  Hook& hook) {
+  const int tid = threadIdx.x, lane = tid & 31, R = a.R;
+  // Lane r of every warp keeps row r's statistics (reference maximum, denominator relative to
+  // it, true maximum) and hands the weights to the other lanes by shuffles.
+  const bool mine = lane < R;
+  float Mr = -INFINITY, Lr = 0.f, Tr = -INFINITY;
+  float acc[kR];
+#pragma unroll
+  for (int r = 0; r < kR; ++r) acc[r] = 0.f;
+  for (int pi = 0; pi < parts; pi += 2) {
+    const bool two = pi + 1 < parts;
+    const int64_t i0 = ((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows;
+    const int64_t i1 = ((int64_t)(first + pi + 1) * 2) * kMaxRows;
+    const float m0 = mine ? __ldcg(x.part_m + i0 + lane) : -INFINITY;
+    const float l0 = mine ? __ldcg(x.part_l + i0 + lane) : 0.f;
+    const float t0 = mine ? __ldcg(x.part_t + i0 + lane) : -INFINITY;
+    const float m1 = (mine && two) ? __ldcg(x.part_m + i1 + lane) : -INFINITY;
+    const float l1 = (mine && two) ? __ldcg(x.part_l + i1 + lane) : 0.f;
+    const float t1 = (mine && two) ? __ldcg(x.part_t + i1 + lane) : -INFINITY;
+    float v0[kR], v1[kR];
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+      v0[r] = r < R ? __ldcg(x.part_o + (i0 + r) * kD + tid) : 0.f;
+      v1[r] = (two && r < R) ? __ldcg(x.part_o + (i1 + r) * kD + tid) : 0.f;
     }
-    // keep the denominator relative to the true maximum, which is what gets reported
-    s_L[tid] = L > 0.f ? L * fast_exp2(s_M[tid] - mt) : 0.f;
-    s_w[parts * kMaxRows + 2 * kMaxRows + tid] = L > 0.f ? fast_exp2(s_M[tid] - mt) : 0.f;  // rescale of acc
-    s_M[tid] = mt;
-  }
-  group_sync<kWorkerGroup>();
-  float acc[kMaxRows];
+    const float mn = fmaxf(Mr, fmaxf(m0, m1));
+    const float s = Mr == -INFINITY ? 0.f : fast_exp2(Mr - mn);
+    const float w0 = m0 == -INFINITY ? 0.f : fast_exp2(m0 - mn);
+    const float w1 = m1 == -INFINITY ? 0.f : fast_exp2(m1 - mn);
+    Lr = Lr * s + w0 * l0 + w1 * l1;
+    Mr = mn;
+    Tr = fmaxf(Tr, fmaxf(t0, t1));
 #pragma unroll
-  for (int r = 0; r < kMaxRows; ++r) acc[r] = 0.f;
-  if (R <= 8) {
-    // two pieces per step: 16 independent loads in flight instead of one L2 round trip per piece
-    for (int pi = 0; pi < parts; pi += 2) {
-      const bool two = pi + 1 < parts;
-      const float* s0 = x.part_o + (((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows) * kD + tid;
-      const float* s1 = x.part_o + (((int64_t)(first + pi + 1) * 2) * kMaxRows) * kD + tid;
-      float v0[8], v1[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        v0[r] = r < R ? __ldcg(s0 + r * kD) : 0.f;
-        v1[r] = (two && r < R) ? __ldcg(s1 + r * kD) : 0.f;
-      }
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        acc[r] += s_w[pi * kMaxRows + r] * v0[r];
-        if (two) acc[r] += s_w[(pi + 1) * kMaxRows + r] * v1[r];
-      }
-    }
-  } else {
-    for (int pi = 0; pi < parts; ++pi) {
-      const float* src = x.part_o + (((int64_t)(first + pi) * 2 + (pi == 0 ? 1 : 0)) * kMaxRows) * kD + tid;
-#pragma unroll
-      for (int r = 0; r < kMaxRows; ++r) {
-        if (r < R) acc[r] += s_w[pi * kMaxRows + r] * __ldcg(src + r * kD);
-      }
+    for (int r = 0; r < kR; ++r) {
+      const float S = __shfl_sync(0xffffffffu, s, r), W0 = __shfl_sync(0xffffffffu, w0, r), W1 = __shfl_sync(0xffffffffu, w1, r);
+      acc[r] = acc[r] * S + W0 * v0[r] + W1 * v1[r];
     }
   }
-  float* s_c = s_L + kMaxRows;  // [16] factor that brings acc to the true maximum
+  // the denominator and the output relative to the true maximum, which is what gets reported
+  const float c = Lr > 0.f ? fast_exp2(Mr - Tr) : 0.f;
+  Lr *= c;
+  Mr = Tr;
+  float M[kR], L[kR];
 #pragma unroll
-  for (int r = 0; r < kMaxRows; ++r) {
-    if (r < R) acc[r] *= s_c[r];
+  for (int r = 0; r < kR; ++r) {
+    acc[r] *= __shfl_sync(0xffffffffu, c, r);
+    M[r] = __shfl_sync(0xffffffffu, Mr, r);
+    L[r] = __shfl_sync(0xffffffffu, Lr, r);
   }
-  hook(s_M, s_L, acc);
-  if (tid < R) {
-    if (a.m) a.m[row_base + tid] = s_M[tid] * kLn2;
-    if (a.l) a.l[row_base + tid] = s_L[tid];
-  }
+  hook(M, L, acc);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
 #pragma unroll
-  for (int r = 0; r < kMaxRows; ++r) {
+  for (int r = 0; r < kR; ++r) {
     if (r < R) {
-      const float L = s_L[r];
-      o[(row_base + r) * kD + tid] = __float2bfloat16_rn(L > 0.f ? acc[r] / L : 0.f);
+      if (tid == r) {
+        if (a.m) a.m[row_base + r] = M[r] * kLn2;
+        if (a.l) a.l[row_base + r] = L[r];
+      }
+      o[(row_base + r) * kD + tid] = __float2bfloat16_rn(L[r] > 0.f ? acc[r] / L[r] : 0.f);
     }
+  }
+}
+
+template <typename Hook = NoMergeHook>
+static __device__ void merge_segment(const AttnArgs& a, const MmaScratch& x, int first, int parts, int64_t row_base,
+                                     Hook hook = Hook()) {
+  if (a.R <= 8) {
+    merge_rows<8>(a, x, first, parts, row_base, hook);
+  } else {
+    merge_rows<kMaxRows>(a, x, first, parts, row_base, hook);
   }
 }
 

@@ -872,9 +872,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       __syncthreads();
     }
     if (tid == 0) {
+      JPT_PH(30);
       if constexpr (kTma) {
         if (!mbar_wait(smem_u32(&sm.bar_k[seq & 1]), (uint32_t)(seq >> 1) & 1u)) dead = true;
       }
+      JPT_PH(31);
       tc_fence_after();
       const uint32_t k_addr = smem_u32(&sm.k[seq & 1][0]);
 #pragma unroll
@@ -1030,6 +1032,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       if constexpr (kTma) {
         if (!mbar_wait(smem_u32(&sm.bar_v[i & 1]), (uint32_t)(i >> 1) & 1u)) dead = true;
       }
+      JPT_PH(29);
       tc_fence_after();
       const uint32_t v_addr = smem_u32(&sm.v[i & 1][0]);
 #pragma unroll
@@ -1124,11 +1127,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       if (!is_final) {
         // Whoever delivers the last piece of the segment combines all of them.
         // The counter wraps back to zero on that arrival, ready for the next launch.
+        // (the barrier orders the CTA's stores before thread 0's fence, which publishes them with the arrival)
         JPT_PH(25);
-        __threadfence();
-        JPT_PH(26);
         __syncthreads();
+        JPT_PH(26);
         if (tid == 0) {
+          __threadfence();
           const unsigned old = atomicInc(&x.counters[cb * a.Hkv + chd], (unsigned)(cparts - 1));
           sm.flag = old == (unsigned)(cparts - 1);
         }
@@ -1136,30 +1140,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         JPT_PH(27);
         if (sm.flag) {
           __threadfence();
-          // the O^T MMA of this tile is complete, so its V slot (16 KB) is free until the next iteration
-          float* scratch = reinterpret_cast<float*>(&sm.v[i & 1][0]);
           if constexpr (kFused) {
             const int hb = cb, hh = chd;
-            merge_segment<false>(a, x, cfirst_cta, cparts, row_base, scratch,
-                                 [&](float* sM, float* sL, float (&acc)[kMaxRows]) {
-                                   float Mh[8], Lh[8], ah[8];
-#pragma unroll
-                                   for (int r = 0; r < 8; ++r) {
-                                     Mh[r] = sM[r];
-                                     Lh[r] = sL[r];
-                                     ah[r] = acc[r];
-                                   }
-                                   add_new_token(hb, hh, Mh, Lh, ah);  // (its first barrier: every thread has read sM / sL)
-#pragma unroll
-                                   for (int r = 0; r < 8; ++r) acc[r] = ah[r];
-                                   if (tid < 8) {
-                                     sM[tid] = Mh[tid];
-                                     sL[tid] = Lh[tid];
-                                   }
-                                   __syncthreads();
-                                 });
+            merge_segment(a, x, cfirst_cta, cparts, row_base, [&](auto& Mh, auto& Lh, auto& ah) { add_new_token(hb, hh, Mh, Lh, ah); });
           } else {
-            merge_segment<false>(a, x, cfirst_cta, cparts, row_base, scratch);
+            merge_segment(a, x, cfirst_cta, cparts, row_base);
           }
         }
       }
