@@ -4,10 +4,9 @@ decode attention, Llama-2-70B-shaped (batch 96, 64 query / 8 KV heads, head_dim
 uniform in [1, 2048]), over NL layers that each own their cache buffers.
 
 One "step" = one decode step of the KV path through all NL layers (per layer:
-quantise+append of the new token and ragged attention over the sequence's
-valid range in one launch, split pieces merged in-kernel; `--unfused` issues
-the append and the attention as two launches).  tokens/s = batch /
-step time.
+the quantise+append launch of the new token, then the ragged attention launch
+over the sequence's valid range, split pieces merged in-kernel; `--fused` does
+both in one launch, jpt_decode_update_attend).  tokens/s = batch / step time.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -561,7 +560,7 @@ def run_cuda(args):
     from jetstream_pytorch_b200.cache_manager import PeerAmaxExchange
     px = PeerAmaxExchange.with_torch_distributed(B)
 
-  fused = not args.unfused and (world == 1 or px is not None)
+  fused = args.fused and (world == 1 or px is not None)
   existing_d = lens_d - 1  # tokens in the cache before the step's new one
 
   def layer_step(i, q, xk, xv):
@@ -682,8 +681,15 @@ def run_cuda(args):
     for i in range(nl):
       caches[i].update(hk_all[i], hv_all[i], i, peers=px)
 
+  def fused_only():  # the step's other form: append and attention of a layer in one launch
+    for i in range(nl):
+      caches[i].update_and_attend(hq_all[i], hk_all[i], hv_all[i], i, start_d, existing_d, peers=px,
+                                  out=(o_s[i], m_s[i], l_s[i]))
+
   reps = max(1, args.steps // 2)
   legs = {"attn": attn_only, "ring": attn_ring_only, "append": append_only}
+  if not fused and (world == 1 or px is not None):
+    legs["fused"] = fused_only
   if world > 1 and px is None:
     del legs["append"]  # the two-phase form is three launches and a collective: not a kernel on its own
   if graph is not None:
@@ -827,6 +833,10 @@ def run_cuda(args):
                                             workload="same caches, start,end~U[0,2048) with wrap (ring semantics)")}
   if "append" in ms_leg:
     kernels["kv_quant_append"] = kernel_entry(ms_leg["append"] * 1e3, append_bytes(B, hkv), peak)
+  if "fused" in ms_leg:
+    kernels["decode_update_attend"] = kernel_entry(
+        ms_leg["fused"] * 1e3, a_bytes + append_bytes(B, hkv), peak,
+        workload="the step's layer as ONE launch (jpt_decode_update_attend: quantise + append + attention; `--fused` makes it the step)")
   line = {
       "metric": METRIC, "value": B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
       "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -894,8 +904,9 @@ def main():
   ap.add_argument("--layers", type=int, default=80)
   ap.add_argument("--no-graph", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")
-  ap.add_argument("--unfused", action="store_true",
-                  help="per layer: the append launch, then the attention launch (default: one fused launch)")
+  ap.add_argument("--fused", action="store_true",
+                  help="per layer one launch that appends the new token and attends (default: the append launch, then the attention launch)")
+  ap.add_argument("--unfused", action="store_true", help="the default; kept for old command lines")
   ap.add_argument("--no-extras", action="store_true", help="skip the other workloads' kernels (N = 1 runs them by default)")
   ap.add_argument("--amax-exchange", choices=["peers", "nccl"], default="peers",
                   help="N > 1: how the per-token amax is max-reduced over the ranks")

@@ -306,6 +306,7 @@ extern "C" int jpt_decode_update_attend(const jpt_attn_params* pp, const jpt_new
               "decode_update_attend: the existing tokens are a length or a ring range");
   JPT_REQUIRE(p.k_scale && p.v_scale, JPT_EINVAL, "decode_update_attend: an int8 cache needs its scales");
   JPT_REQUIRE(nt->xk && nt->xv, JPT_EINVAL, "decode_update_attend: null new token");
+  JPT_REQUIRE(aligned(nt->xk, 16) && aligned(nt->xv, 16), JPT_EALIGN, "decode_update_attend: the new token must be 16-byte aligned");
   JPT_REQUIRE(nt->in_dtype == JPT_BF16 || nt->in_dtype == JPT_F32, JPT_EINVAL,
               "decode_update_attend: the new token must be bf16 or f32");
   JPT_REQUIRE(p.scale_dtype == nt->in_dtype || !nt->write_cache, JPT_EINVAL,

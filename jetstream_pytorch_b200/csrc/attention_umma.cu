@@ -64,6 +64,9 @@ constexpr int kCtasPerSm = 3;
 #ifndef JPT_PIECE_COST_U
 #define JPT_PIECE_COST_U 1
 #endif
+#ifndef JPT_PIECE_COST_FUSED
+#define JPT_PIECE_COST_FUSED 3
+#endif
 constexpr int kPieceCostU = JPT_PIECE_COST_U;  // overhead slots charged per segment, in 128-token tiles
 constexpr long long kWaitCycles = 1000000000ll;  // about half a second: far beyond any wait of a healthy run
 constexpr int kMaxPartsU = 250;  // pieces of one segment the in-kernel merge can hold in its 16 KB of scratch
@@ -73,7 +76,9 @@ struct __align__(1024) SmemU {
   uint8_t v[2][kTileU * kD];             // V ring
   uint8_t qlev[16 * kD];                 // query levels: rows 0..7 high bytes, 8..15 low bytes
   uint8_t plev[16 * kTileU];             // probability levels: row 8 l + r, one byte per token
-  uint8_t qraw[2][8 * kD * 2];           // bf16 query rows of a piece that starts with a tile in flight (by tile parity)
+  uint8_t qraw[8 * kD * 2];              // bf16 query rows of the piece that starts with the next tile
+  uint8_t ntq[8 * kD * 2];               // new token: the segment's query rows again ...
+  uint8_t ntkv[2][kD * 4];               // ... and the token's K and V rows of this head (bf16 or fp32)
   float xch[4][12];                      // per warp: row maxima of the tile [8], largest V scale [1]
   float red[4][8];                       // per warp: denominators at the end of a piece
   float qsc[8];                          // s_r * sm_scale * log2(e) / 254
@@ -141,7 +146,7 @@ __device__ __forceinline__ int tiles_u(const SeqRange& r, int S) {
   const int na = run_a(r, S);
   return tiles_run(na) + tiles_run(r.n - na);
 }
-__device__ __forceinline__ int slots_u(const SeqRange& r, int S) { return r.n > 0 ? tiles_u(r, S) + kPieceCostU : 0; }
+__device__ __forceinline__ int slots_u(const SeqRange& r, int S, int cost) { return r.n > 0 ? tiles_u(r, S) + cost : 0; }
 // Tile t of the segment: physical position of its first row and its number of valid rows.
 __device__ __forceinline__ void tile_rows(const SeqRange& r, int S, int t, int* pos, int* cnt) {
   const int na = run_a(r, S), ta = tiles_run(na);
@@ -306,6 +311,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   }
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // slots charged per segment on top of its tiles (the new token costs about the time of two more tiles)
+  constexpr int kPieceCost = kFused ? JPT_PIECE_COST_FUSED : kPieceCostU;
   const int R = a.R;
   const bool quant = a.k_scale != nullptr;
   const int cta = blockIdx.x;
@@ -345,19 +352,38 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 
   // ------------------------------------------------------------------ new token: amax to every rank
   unsigned nt_epoch = 0;
-  if constexpr (kFused) {
-    nt_epoch = *reinterpret_cast<volatile unsigned*>(&nt.px_state[0]) + 1u;
+  if constexpr (kFused) nt_epoch = *reinterpret_cast<volatile unsigned*>(&nt.px_state[0]) + 1u;
+  // Called once by every CTA, after its first rows have been requested (the reduction runs under their latency).
+  auto post_amax = [&]() {
     const int HD = a.Hkv * kD;
     for (int b = cta; b < a.B; b += gridDim.x) {
       float am[2];
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
+        // 16 bytes per load, the loads of a pass in flight together (rows are kD elements: 16-byte multiples)
+        const int chunks = HD * (nt.in_f32 ? 4 : 2) / 16;
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(nt.x[which]) +
+                                                          (int64_t)b * HD * (nt.in_f32 ? 4 : 2));
         float v = 0.f;
-        for (int e = tid; e < HD; e += kThreads) {
-          const int64_t idx = (int64_t)b * HD + e;
-          const float xv = nt.in_f32 ? static_cast<const float*>(nt.x[which])[idx]
-                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(nt.x[which])[idx]);
-          v = fmaxf(v, fabsf(xv));
+        for (int c0 = 0; c0 < chunks; c0 += 4 * kThreads) {
+          uint4 u[4];
+#pragma unroll
+          for (int z = 0; z < 4; ++z) {
+            const int c = c0 + z * kThreads + tid;
+            u[z] = c < chunks ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int z = 0; z < 4; ++z) {
+            const uint32_t w[4] = {u[z].x, u[z].y, u[z].z, u[z].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (nt.in_f32) {
+                v = fmaxf(v, fabsf(__uint_as_float(w[e])));
+              } else {  // two bf16 values: their magnitudes as floats
+                v = fmaxf(v, fmaxf(fabsf(__uint_as_float(w[e] << 16)), fabsf(__uint_as_float(w[e] & 0xffff0000u))));
+              }
+            }
+          }
         }
         am[which] = warp_max(v);
       }
@@ -377,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
     }
     __syncthreads();
-  }
+  };
   // Counts this CTA as done with the exchange of this launch; the last one advances the launch number.
   auto exchange_done = [&]() {
     if constexpr (kFused) {
@@ -403,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   int mine = 0;
   for (int b = b_lo; b < b_hi; ++b) {
     int ua;
-    mine += slots_u(seq_range_x(a, x, b, &ua), a.S);
+    mine += slots_u(seq_range_x(a, x, b, &ua), a.S, kPieceCost);
   }
   scan[tid] = mine;
   __syncthreads();
@@ -445,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       int run = lo;
       for (int b = b_lo; b < b_hi; ++b) {
         int ua;
-        const int sl = slots_u(seq_range_x(a, x, b, &ua), a.S);
+        const int sl = slots_u(seq_range_x(a, x, b, &ua), a.S, kPieceCost);
         const int nxt = run + sl * a.Hkv;
         if (G0 < nxt) {
           const int rem = G0 - run;
@@ -469,16 +495,39 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   // -> cache row, scale, stash -> one more softmax term on top of (M, L, acc): M[r] maximum in the
   // log2 domain (-inf: no token yet), L[r] denominator, acc[r] this thread's component of the
   // unnormalised output.  Every thread of the CTA calls it.
+  // Starts the copies add_new_token(b, h, ...) will need into shared memory (query rows, the token's K
+  // and V rows of head h) and has threads 0, 1 look at the exchange words once; called by every thread,
+  // an iteration (or more) before add_new_token, so that nothing there waits for global memory.
+  JPT_PH_DECL
+  const int nt_row_bytes = nt.in_f32 ? kD * 4 : kD * 2;
+  unsigned long long nt_word = 0;  // threads 0, 1 (one rank): the K / V amax word as seen at staging time
+  int nt_pos = 0;                  // where the token is written
+  auto stage_new_token = [&](int b, int h) {
+    const __nv_bfloat16* q = qbase + ((int64_t)b * a.Hkv + h) * R * kD;
+    for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.ntq[0]) + ch * 16, q + ch * 8, true);
+    const int64_t row = ((int64_t)b * a.Hkv + h) * nt_row_bytes;
+    const int chunks = nt_row_bytes / 16;
+    if (tid < 2 * chunks) {
+      const int which = tid / chunks, ch = tid - which * chunks;
+      cp_async16(smem_u32(&sm.ntkv[which][0]) + ch * 16, static_cast<const uint8_t*>(nt.x[which]) + row + ch * 16, true);
+    }
+    nt_pos = nt.pos ? nt.pos[nt.pos_count == 1 ? 0 : b] : nt.pos_host;
+    if (tid < 2 && nt.px_world == 1) {
+      const unsigned long long* p = nt.px_slots[0] + (size_t)(nt_epoch & 1u) * (2 * a.B) + tid * a.B + b;
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(nt_word) : "l"(p) : "memory");
+    }
+  };
   auto add_new_token = [&](int b, int h, float* M, float* L, float* acc) {
-    __syncthreads();  // the scratch is free
-    if (tid < 2) {    // K amax, V amax: largest partial over the ranks
+    cp_async_wait<1>();  // the staged rows (the group requested after them may still be in flight)
+    __syncthreads();     // staged rows visible; the scratch is free
+    if (tid < 2) {       // K amax, V amax: largest partial over the ranks
       const size_t row = (size_t)(nt_epoch & 1u) * nt.px_world;
       float m = 0.f;
       const long long t0 = clock64();
       for (int r = 0; r < nt.px_world; ++r) {
         const unsigned long long* p = nt.px_slots[nt.px_rank] + (row + r) * (2 * a.B) + tid * a.B + b;
-        unsigned long long w;
-        for (;;) {
+        unsigned long long w = nt.px_world == 1 ? nt_word : 0ull;
+        while ((unsigned)(w >> 32) != nt_epoch) {
           asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
           if ((unsigned)(w >> 32) == nt_epoch) break;
           if (clock64() - t0 > nt.px_wait_cycles) {  // a rank never came: report, go on with what is there
@@ -498,18 +547,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const int64_t xi = ((int64_t)b * a.Hkv + h) * kD + tid;
     float xk, xv;
     if (nt.in_f32) {
-      xk = static_cast<const float*>(nt.x[0])[xi];
-      xv = static_cast<const float*>(nt.x[1])[xi];
+      xk = reinterpret_cast<const float*>(&sm.ntkv[0][0])[tid];
+      xv = reinterpret_cast<const float*>(&sm.ntkv[1][0])[tid];
     } else {
-      xk = __bfloat162float(static_cast<const __nv_bfloat16*>(nt.x[0])[xi]);
-      xv = __bfloat162float(static_cast<const __nv_bfloat16*>(nt.x[1])[xi]);
+      xk = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&sm.ntkv[0][0])[tid]);
+      xv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&sm.ntkv[1][0])[tid]);
     }
     const int8_t ck = nt.in_f32 ? decode_code<float>(xk, sc_k) : decode_code<__nv_bfloat16>(xk, sc_k);
     const int8_t cv = nt.in_f32 ? decode_code<float>(xv, sc_v) : decode_code<__nv_bfloat16>(xv, sc_v);
     {
       if (nt.quant[0]) nt.quant[0][xi] = ck;
       if (nt.quant[1]) nt.quant[1][xi] = cv;
-      int pos = nt.pos ? nt.pos[nt.pos_count == 1 ? 0 : b] : nt.pos_host;
+      int pos = nt_pos;
       if (pos < 0) pos += a.S;
       const bool write = nt.write_cache && pos >= 0 && pos < a.S;
       if (write) {
@@ -532,14 +581,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
     }
     // logits of the query rows against the new key: sum over the 128 head-dim indices
-    const __nv_bfloat16* q = qbase + ((int64_t)b * a.Hkv + h) * R * kD;
+    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(&sm.ntq[0]);
     const float kf = (float)ck;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float d = j < R ? __bfloat162float(q[j * kD + tid]) * kf : 0.f;
+#pragma unroll 1  // (cold code: kept small)
+    for (int j = 0; j < R; ++j) {
+      float d = __bfloat162float(q[j * kD + tid]) * kf;
 #pragma unroll
       for (int sh = 1; sh <= 16; sh <<= 1) d += __shfl_xor_sync(0xffffffffu, d, sh);
-      if (lane == j) sm.dot[warp][j] = d;
+      if (lane == 0) sm.dot[warp][j] = d;
     }
     __syncthreads();
     const float unit = sc_k * a.sm_scale * kLog2e;
@@ -574,6 +623,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
               L[j] = 0.f;
               acc[j] = 0.f;
             }
+            stage_new_token(b, h);
+            cp_async_commit();
+            cp_async_commit();  // (add_new_token leaves the youngest group alone)
             add_new_token(b, h, M, L, acc);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -598,6 +650,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
   };
   if (G0 >= G1) {  // no tile for this CTA
+    if constexpr (kFused) post_amax();
     clear_empty_rows();
     exchange_done();
     tc_fence_before();
@@ -613,7 +666,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   const int8_t* vbase = static_cast<const int8_t*>(a.v);
   const __nv_bfloat16* mask = static_cast<const __nv_bfloat16*>(a.mask);
 
-  JPT_PH_DECL
   // ------------------------------------------------------------------ producer
   // K and V rows travel in rings of their own (two slots of 16 KB each; tile j uses slot j % 2 of
   // both).  A K slot is free as soon as the S^T MMA of its tile is complete, a V slot when the O^T
@@ -650,7 +702,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     ++pslot;
     if (++pt < pT) return;
     pt = 0;
-    pslot += kPieceCostU;  // the overhead slots of the next segment
+    pslot += kPieceCost;  // the overhead slots of the next segment
     if (++ph == a.Hkv) {
       ph = 0;
       do {
@@ -667,11 +719,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   {
     load_seq();
     const int v0 = sm.start[2];  // slot inside the segment: overhead slots come first
-    if (v0 < kPieceCostU) {
-      pslot += kPieceCostU - v0;
+    if (v0 < kPieceCost) {
+      pslot += kPieceCost - v0;
       pt = 0;
     } else {
-      pt = v0 - kPieceCostU;
+      pt = v0 - kPieceCost;
     }
     seg_setup();
   }
@@ -735,8 +787,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
   };
 
-  // K rows of the next tile of the share (with its record and, when it starts a piece, its
-  // query rows) into ring position `seq`; a record with t = -1 when the share is exhausted.
+  // K rows of the next tile of the share (with its record) into ring position `seq`; a record
+  // with t = -1 when the share is exhausted.
   auto issue_k = [&](int seq) {
     if (pslot < G1) {
       SeqRange rg;
@@ -757,10 +809,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
       JPT_PH(19);
       if constexpr (!kTma) copy_rows(smem_u32(&sm.k[seq & 1][0]), kbase, pb, ph, pos, cnt);
-      if (seq == 0 || pt == 0) {  // a piece starts with this tile
-        const __nv_bfloat16* q = qbase + ((int64_t)pb * a.Hkv + ph) * R * kD;
-        for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.qraw[seq & 1][0]) + ch * 16, q + ch * 8, true);
-      }
       JPT_PH(20);
       advance();
       JPT_PH(21);
@@ -769,8 +817,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
     cp_async_commit();
   };
-  // V rows of the tile at ring position `seq` (its record is in shared memory), and the
-  // scales of this thread's token in it, consumed by this same thread an iteration later:
+  // V rows of the tile at ring position `seq` (its record is in shared memory), its query rows when
+  // it starts a piece (converted at the end of this iteration), and the scales of this thread's
+  // token in it, consumed by this same thread an iteration later:
   // they stay raw bits until then, so that nothing here waits for the loads.
   const bool sc_f32 = a.scale_is_f32 != 0;
   const uint32_t raw_one = sc_f32 ? 0x3f800000u : 0x3f80u;
@@ -786,6 +835,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         JPT_PH(17);
       } else {
         copy_rows(smem_u32(&sm.v[seq & 1][0]), vbase, mb, mh, pos, cnt);
+      }
+      if (seq == 0 || mtile == 0) {  // a piece starts with this tile
+        const __nv_bfloat16* q = qbase + ((int64_t)mb * a.Hkv + mh) * R * kD;
+        for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.qraw[0]) + ch * 16, q + ch * 8, true);
       }
       nks = raw_one;
       nvs = 0u;
@@ -834,7 +887,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       const int row = tid >> 4, ch = tid & 15;
       float f[8];
       if (row < R) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[seq & 1][row * (kD * 2) + ch * 16]);
+        const uint4 raw = *reinterpret_cast<const uint4*>(&sm.qraw[row * (kD * 2) + ch * 16]);
         const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -908,7 +961,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   __syncthreads();  // the record of tile 0
   issue_v(0);
   issue_k(1);
-  cp_async_wait<1>();  // K0 (with the query rows) and V0
+  if constexpr (kFused) post_amax();
+  cp_async_wait<1>();  // K0 and V0 (with the query rows)
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -958,6 +1012,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         tmem_ld_wait();
       }
       JPT_PH(1);
+      if constexpr (kFused) {  // the tile ends a piece: what the new token needs travels with the next copies
+        if (last_of_share || mt.t == mt.T - 1) stage_new_token(mt.b, mt.h);
+      }
       issue_v(i + 1);
       issue_k(i + 2);
       JPT_PH(2);
@@ -1055,7 +1112,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 
     // ---------------- the next tile: its K rows were requested an iteration ago
     JPT_PH(28);
-    cp_async_wait<2>();  // (younger groups: V(i+1), K(i+2))
+    if (sm.meta[(i + 1) & 3].t == 0) {
+      cp_async_wait<1>();  // it starts a piece: its query rows travel with V(i+1) (younger group: K(i+2))
+    } else {
+      cp_async_wait<2>();  // (younger groups: V(i+1), K(i+2))
+    }
     JPT_PH(13);
     fence_async_smem();
     tc_fence_before();
