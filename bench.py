@@ -721,9 +721,11 @@ def run_cuda(args):
   gathered = {}
   for name, t in mine.items():
     t = t.contiguous()
-    if world > 1:
-      parts = [torch.empty_like(t) for _ in range(world)]
-      dist.all_gather(parts, t)
+    if world > 1:  # as bytes: NCCL has no 16-bit integer type
+      raw = t.view(torch.uint8).reshape(-1)
+      got = [torch.empty_like(raw) for _ in range(world)]
+      dist.all_gather(got, raw)
+      parts = [g.view(t.dtype).reshape(t.shape) for g in got]
     else:
       parts = [t]
     gathered[name] = [p.cpu() for p in parts]
