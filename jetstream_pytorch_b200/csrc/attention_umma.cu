@@ -33,13 +33,17 @@
 // lane t of O^T), which also removes the cross-warp merge of the accumulators.
 //
 // Fused decode update (jpt_decode_update_attend): the launch also takes the
-// step's new K/V token.  CTA b mod grid computes the token's amax over this
-// GPU's heads first thing and stores it into the exchange slots of every rank
-// (NVLink peer stores when the KV heads are sharded); the tiles of the existing
-// tokens stream as usual; the CTA that writes a segment's final rows reads the
-// ranks' words (long there by then), quantises the token's row for its head
-// with the decode quantiser, writes cache row, scale and stash, and folds the
-// token into the result as one more softmax term.  One launch per layer, the
+// step's new K/V token, which becomes the last token of its segment: the
+// schedule counts one token more per sequence, and the CTA that processes the
+// segment's last tile writes the token's int8 codes into the row behind the
+// existing tokens of that tile IN SHARED MEMORY (K tile before the S^T MMA, V
+// tile before the O^T MMA), so the token is attended to like any other, with
+// no separate softmax term.  CTA b mod grid computes the token's amax over
+// this GPU's heads while its first rows are in flight and stores it into the
+// exchange slots of every rank (NVLink peer stores when the KV heads are
+// sharded); the CTA with the last tile reads the ranks' words (long there by
+// then), quantises the token's row of its head with the decode quantiser and
+// also writes cache row, scale and stash.  One launch per layer, the
 // exchange's round trip hidden under the existing tokens.
 //
 // Every wait (mbarriers, exchange words) is bounded; a CTA that gives up raises
@@ -62,10 +66,10 @@ constexpr int kTmemCols = 32;   // S^T: columns 0..15, O^T: columns 16..31
 constexpr int kColO = 16;
 constexpr int kCtasPerSm = 3;
 #ifndef JPT_PIECE_COST_U
-#define JPT_PIECE_COST_U 1
+#define JPT_PIECE_COST_U 2
 #endif
 #ifndef JPT_PIECE_COST_FUSED
-#define JPT_PIECE_COST_FUSED 3
+#define JPT_PIECE_COST_FUSED 2
 #endif
 constexpr int kPieceCostU = JPT_PIECE_COST_U;  // overhead slots charged per segment, in 128-token tiles
 constexpr long long kWaitCycles = 1000000000ll;  // about half a second: far beyond any wait of a healthy run
@@ -77,14 +81,16 @@ struct __align__(1024) SmemU {
   uint8_t qlev[16 * kD];                 // query levels: rows 0..7 high bytes, 8..15 low bytes
   uint8_t plev[16 * kTileU];             // probability levels: row 8 l + r, one byte per token
   uint8_t qraw[8 * kD * 2];              // bf16 query rows of the piece that starts with the next tile
-  uint8_t ntq[8 * kD * 2];               // new token: the segment's query rows again ...
-  uint8_t ntkv[2][kD * 4];               // ... and the token's K and V rows of this head (bf16 or fp32)
+  uint8_t ntkv[2][2][kD * 4];            // new token, by tile parity: its K and V rows of this head (bf16 or fp32)
+  uint8_t ntv[2][kD];                    // ... and its V codes between the K tile's turn and the V tile's
+  float ntsc[2][2];                      // ... and its K and V scales
+  unsigned long long ntw[2][2][8];       // ... the ranks' amax words (K, V) as they were when the tile was requested
+  int ntpos[2][4];                       // ... and where the token is written
   float xch[4][12];                      // per warp: row maxima of the tile [8], largest V scale [1]
   float red[4][8];                       // per warp: denominators at the end of a piece
   float qsc[8];                          // s_r * sm_scale * log2(e) / 254
   float qsr[8];                          // s_r / 254 (the chain of rounded logits starts from the plain dot product)
   float ntx[4];                          // new token: K amax, V amax
-  float dot[4][8];                       // new token, per warp: partial logits of the 8 rows
   uint64_t bar[2];                       // MMA completion: S^T, O^T
   uint64_t bar_k[2], bar_v[2];           // rows landed (copy-engine path), per ring slot
   uint32_t tmem_base;
@@ -311,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   }
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // slots charged per segment on top of its tiles (the new token costs about the time of two more tiles)
+  // slots charged per segment on top of its tiles (with the new token: one more for its quantisation)
   constexpr int kPieceCost = kFused ? JPT_PIECE_COST_FUSED : kPieceCostU;
   const int R = a.R;
   const bool quant = a.k_scale != nullptr;
@@ -419,6 +425,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
   };
 
+  // Valid range of sequence b as the schedule sees it: with the fused update the step's new token
+  // counts as the segment's last token (a full cache has no row for it: reported, the token is dropped).
+  auto seg_range = [&](int b, int* use_add) {
+    SeqRange r = seq_range_x(a, x, b, use_add);
+    if constexpr (kFused) {
+      if (r.n < a.S) {
+        r.n += 1;
+      } else {
+        atomicExch(status, 3);
+      }
+    }
+    return r;
+  };
+
   // ------------------------------------------------------------------ schedule
   // Slots per sequence (tiles + overhead) -> exclusive prefix over sequences;
   // each thread owns a slice of ceil(B/128) sequences.  The scan scratch
@@ -429,7 +449,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   int mine = 0;
   for (int b = b_lo; b < b_hi; ++b) {
     int ua;
-    mine += slots_u(seq_range_x(a, x, b, &ua), a.S, kPieceCost);
+    mine += slots_u(seg_range(b, &ua), a.S, kPieceCost);
   }
   scan[tid] = mine;
   __syncthreads();
@@ -471,7 +491,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       int run = lo;
       for (int b = b_lo; b < b_hi; ++b) {
         int ua;
-        const int sl = slots_u(seq_range_x(a, x, b, &ua), a.S, kPieceCost);
+        const int sl = slots_u(seg_range(b, &ua), a.S, kPieceCost);
         const int nxt = run + sl * a.Hkv;
         if (G0 < nxt) {
           const int rem = G0 - run;
@@ -490,43 +510,45 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   JPT_SPAN(1);
 
   const __nv_bfloat16* qbase = static_cast<const __nv_bfloat16*>(a.q);
-  // The decode step's new token of slot b, KV head h, folded into the 8 rows of the segment by the
-  // whole CTA (thread tid: head-dim index tid): all-ranks amax -> scale -> codes of this head's row
-  // -> cache row, scale, stash -> one more softmax term on top of (M, L, acc): M[r] maximum in the
-  // log2 domain (-inf: no token yet), L[r] denominator, acc[r] this thread's component of the
-  // unnormalised output.  Every thread of the CTA calls it.
-  // Starts the copies add_new_token(b, h, ...) will need into shared memory (query rows, the token's K
-  // and V rows of head h) and has threads 0, 1 look at the exchange words once; called by every thread,
-  // an iteration (or more) before add_new_token, so that nothing there waits for global memory.
   JPT_PH_DECL
+  // The new token of segment (b, h), whose last tile has number `seq` in this CTA: the copies of its K and V
+  // rows start when the tile's K rows are requested (two iterations before they are needed) ...
   const int nt_row_bytes = nt.in_f32 ? kD * 4 : kD * 2;
-  unsigned long long nt_word = 0;  // threads 0, 1 (one rank): the K / V amax word as seen at staging time
-  int nt_pos = 0;                  // where the token is written
-  auto stage_new_token = [&](int b, int h) {
-    const __nv_bfloat16* q = qbase + ((int64_t)b * a.Hkv + h) * R * kD;
-    for (int ch = tid; ch < R * 16; ch += kThreads) cp_async16(smem_u32(&sm.ntq[0]) + ch * 16, q + ch * 8, true);
+  auto stage_new_token = [&](int seq, int b, int h) {
     const int64_t row = ((int64_t)b * a.Hkv + h) * nt_row_bytes;
     const int chunks = nt_row_bytes / 16;
     if (tid < 2 * chunks) {
       const int which = tid / chunks, ch = tid - which * chunks;
-      cp_async16(smem_u32(&sm.ntkv[which][0]) + ch * 16, static_cast<const uint8_t*>(nt.x[which]) + row + ch * 16, true);
+      cp_async16(smem_u32(&sm.ntkv[seq & 1][which][0]) + ch * 16, static_cast<const uint8_t*>(nt.x[which]) + row + ch * 16, true);
     }
-    nt_pos = nt.pos ? nt.pos[nt.pos_count == 1 ? 0 : b] : nt.pos_host;
-    if (tid < 2 && nt.px_world == 1) {
-      const unsigned long long* p = nt.px_slots[0] + (size_t)(nt_epoch & 1u) * (2 * a.B) + tid * a.B + b;
-      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(nt_word) : "l"(p) : "memory");
+    // the exchange words of this sequence (normally posted long ago; looked at again if not) and the position
+    if (tid >= 64 && tid < 64 + 2 * nt.px_world) {
+      const int which = (tid - 64) / nt.px_world, r = (tid - 64) - which * nt.px_world;
+      const unsigned long long* p =
+          nt.px_slots[nt.px_rank] + ((size_t)(nt_epoch & 1u) * nt.px_world + r) * (2 * a.B) + which * a.B + b;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_u32(&sm.ntw[seq & 1][which][r])), "l"(p));
+    }
+    if (tid == 96) {
+      if (nt.pos) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(&sm.ntpos[seq & 1][0])),
+                     "l"(nt.pos + (nt.pos_count == 1 ? 0 : b)));
+      } else {
+        sm.ntpos[seq & 1][0] = nt.pos_host;
+      }
     }
   };
-  auto add_new_token = [&](int b, int h, float* M, float* L, float* acc) {
-    cp_async_wait<1>();  // the staged rows (the group requested after them may still be in flight)
-    __syncthreads();     // staged rows visible; the scratch is free
-    if (tid < 2) {       // K amax, V amax: largest partial over the ranks
-      const size_t row = (size_t)(nt_epoch & 1u) * nt.px_world;
+  // ... and once the tile's K rows are in shared memory, the whole CTA (thread tid: head-dim index tid)
+  // turns the token into codes: all-ranks amax -> scales -> codes of this head's row -> the K code into
+  // row `row` of the K tile, the V code aside for the V tile's turn, cache row, scales and stash to
+  // global memory.  The caller's barrier publishes the shared-memory writes.
+  auto quantise_new_token = [&](int seq, int b, int h, int row) {
+    if (tid < 2) {  // K amax, V amax: largest partial over the ranks
+      const size_t xrow = (size_t)(nt_epoch & 1u) * nt.px_world;
       float m = 0.f;
       const long long t0 = clock64();
       for (int r = 0; r < nt.px_world; ++r) {
-        const unsigned long long* p = nt.px_slots[nt.px_rank] + (row + r) * (2 * a.B) + tid * a.B + b;
-        unsigned long long w = nt.px_world == 1 ? nt_word : 0ull;
+        const unsigned long long* p = nt.px_slots[nt.px_rank] + (xrow + r) * (2 * a.B) + tid * a.B + b;
+        unsigned long long w = sm.ntw[seq & 1][tid][r];
         while ((unsigned)(w >> 32) != nt_epoch) {
           asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
           if ((unsigned)(w >> 32) == nt_epoch) break;
@@ -547,104 +569,53 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const int64_t xi = ((int64_t)b * a.Hkv + h) * kD + tid;
     float xk, xv;
     if (nt.in_f32) {
-      xk = reinterpret_cast<const float*>(&sm.ntkv[0][0])[tid];
-      xv = reinterpret_cast<const float*>(&sm.ntkv[1][0])[tid];
+      xk = reinterpret_cast<const float*>(&sm.ntkv[seq & 1][0][0])[tid];
+      xv = reinterpret_cast<const float*>(&sm.ntkv[seq & 1][1][0])[tid];
     } else {
-      xk = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&sm.ntkv[0][0])[tid]);
-      xv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&sm.ntkv[1][0])[tid]);
+      xk = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&sm.ntkv[seq & 1][0][0])[tid]);
+      xv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(&sm.ntkv[seq & 1][1][0])[tid]);
     }
     const int8_t ck = nt.in_f32 ? decode_code<float>(xk, sc_k) : decode_code<__nv_bfloat16>(xk, sc_k);
     const int8_t cv = nt.in_f32 ? decode_code<float>(xv, sc_v) : decode_code<__nv_bfloat16>(xv, sc_v);
-    {
-      if (nt.quant[0]) nt.quant[0][xi] = ck;
-      if (nt.quant[1]) nt.quant[1][xi] = cv;
-      int pos = nt_pos;
-      if (pos < 0) pos += a.S;
-      const bool write = nt.write_cache && pos >= 0 && pos < a.S;
-      if (write) {
-        const int64_t off = (int64_t)b * a.kv_b + (int64_t)h * a.kv_h + (int64_t)pos * a.kv_s + tid;
-        static_cast<int8_t*>(const_cast<void*>(a.k))[off] = ck;
-        static_cast<int8_t*>(const_cast<void*>(a.v))[off] = cv;
-      }
-      if (tid < 2) {  // every head's CTA writes the same scale: harmless, and no CTA has to wait for another
-        const float sc = tid == 0 ? sc_k : sc_v;
-        void* out = nt.scale_out[tid];
-        void* cache = const_cast<void*>(tid == 0 ? a.k_scale : a.v_scale);
-        const int64_t sidx = (int64_t)b * a.sc_b + (int64_t)pos * a.sc_s;
-        if (nt.in_f32) {
-          if (out) static_cast<float*>(out)[b] = sc;
-          if (write) static_cast<float*>(cache)[sidx] = sc;
-        } else {
-          if (out) static_cast<__nv_bfloat16*>(out)[b] = __float2bfloat16_rn(sc);
-          if (write) static_cast<__nv_bfloat16*>(cache)[sidx] = __float2bfloat16_rn(sc);
-        }
-      }
+    sm.k[seq & 1][swz(row, tid)] = (uint8_t)ck;
+    sm.ntv[seq & 1][tid] = (uint8_t)cv;
+    if (tid < 2) sm.ntsc[seq & 1][tid] = tid == 0 ? sc_k : sc_v;
+    if (nt.quant[0]) nt.quant[0][xi] = ck;
+    if (nt.quant[1]) nt.quant[1][xi] = cv;
+    int pos = sm.ntpos[seq & 1][0];
+    if (pos < 0) pos += a.S;
+    const bool write = nt.write_cache && pos >= 0 && pos < a.S;
+    if (write) {
+      const int64_t off = (int64_t)b * a.kv_b + (int64_t)h * a.kv_h + (int64_t)pos * a.kv_s + tid;
+      static_cast<int8_t*>(const_cast<void*>(a.k))[off] = ck;
+      static_cast<int8_t*>(const_cast<void*>(a.v))[off] = cv;
     }
-    // logits of the query rows against the new key: sum over the 128 head-dim indices
-    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(&sm.ntq[0]);
-    const float kf = (float)ck;
-#pragma unroll 1  // (cold code: kept small)
-    for (int j = 0; j < R; ++j) {
-      float d = __bfloat162float(q[j * kD + tid]) * kf;
-#pragma unroll
-      for (int sh = 1; sh <= 16; sh <<= 1) d += __shfl_xor_sync(0xffffffffu, d, sh);
-      if (lane == 0) sm.dot[warp][j] = d;
-    }
-    __syncthreads();
-    const float unit = sc_k * a.sm_scale * kLog2e;
-    const float vf = (float)cv * sc_v;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < R) {
-        const float xn = ((sm.dot[0][j] + sm.dot[1][j]) + (sm.dot[2][j] + sm.dot[3][j])) * unit;
-        const float mn = fmaxf(M[j], xn);
-        const float al = M[j] == -INFINITY ? 0.f : ex2(M[j] - mn);
-        const float pn = ex2(xn - mn);
-        acc[j] = fmaf(acc[j], al, pn * vf);
-        L[j] = fmaf(L[j], al, pn);
-        M[j] = mn;
+    if (tid < 2) {  // every head's CTA writes the same scale: harmless, and no CTA has to wait for another
+      const float sc = tid == 0 ? sc_k : sc_v;
+      void* out = nt.scale_out[tid];
+      void* cache = const_cast<void*>(tid == 0 ? a.k_scale : a.v_scale);
+      const int64_t sidx = (int64_t)b * a.sc_b + (int64_t)pos * a.sc_s;
+      if (nt.in_f32) {
+        if (out) static_cast<float*>(out)[b] = sc;
+        if (write) static_cast<float*>(cache)[sidx] = sc;
+      } else {
+        if (out) static_cast<__nv_bfloat16*>(out)[b] = __float2bfloat16_rn(sc);
+        if (write) static_cast<__nv_bfloat16*>(cache)[sidx] = __float2bfloat16_rn(sc);
       }
     }
   };
-  // Rows of empty sequences are nobody's tile: sequence b is handled by CTA b mod grid (at the end of
-  // the CTA's life, off the path to its first tile): zero rows, or the new token alone.
+  // Rows of empty sequences are nobody's tile: sequence b is cleared by CTA b mod grid (at the end of
+  // the CTA's life, off the path to its first tile).  (With the fused update no sequence is empty.)
   auto clear_empty_rows = [&]() {
     for (int b = cta; b < a.B; b += gridDim.x) {
       int ua;
-      if (seq_range_x(a, x, b, &ua).n == 0) {
+      if (seg_range(b, &ua).n == 0) {
         const int64_t r0 = (int64_t)b * a.Hkv * R;
         __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.o);
-        if constexpr (kFused) {
-          for (int h = 0; h < a.Hkv; ++h) {
-            float M[8], L[8], acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              M[j] = -INFINITY;
-              L[j] = 0.f;
-              acc[j] = 0.f;
-            }
-            stage_new_token(b, h);
-            cp_async_commit();
-            cp_async_commit();  // (add_new_token leaves the youngest group alone)
-            add_new_token(b, h, M, L, acc);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (j < R) {
-                const int64_t row = r0 + (int64_t)h * R + j;
-                o[row * kD + tid] = __float2bfloat16_rn(acc[j] / L[j]);
-                if (tid == 0) {
-                  if (a.m) a.m[row] = M[j] * kLn2;
-                  if (a.l) a.l[row] = L[j];
-                }
-              }
-            }
-          }
-        } else {
-          for (int i = tid; i < a.Hkv * R * kD; i += kThreads) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
-          for (int i = tid; i < a.Hkv * R; i += kThreads) {
-            if (a.m) a.m[r0 + i] = -INFINITY;
-            if (a.l) a.l[r0 + i] = 0.f;
-          }
+        for (int i = tid; i < a.Hkv * R * kD; i += kThreads) o[r0 * kD + i] = __float2bfloat16_rn(0.f);
+        for (int i = tid; i < a.Hkv * R; i += kThreads) {
+          if (a.m) a.m[r0 + i] = -INFINITY;
+          if (a.l) a.l[r0 + i] = 0.f;
         }
       }
     }
@@ -688,7 +659,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   int pfirst_cta, pparts;
 
   auto load_seq = [&]() {
-    const SeqRange r = seq_range_x(a, x, pb, &puse_add);
+    const SeqRange r = seg_range(pb, &puse_add);
     pn = r.n;
     pfirst = r.first;
     pT = tiles_u(r, a.S);
@@ -809,6 +780,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
       JPT_PH(19);
       if constexpr (!kTma) copy_rows(smem_u32(&sm.k[seq & 1][0]), kbase, pb, ph, pos, cnt);
+      if constexpr (kFused) {
+        if (pt == pT - 1) stage_new_token(seq, pb, ph);  // the segment's last tile takes the new token
+      }
       JPT_PH(20);
       advance();
       JPT_PH(21);
@@ -924,6 +898,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       tc_fence_before();
       __syncthreads();
     }
+    if constexpr (kFused) {
+      if (mt.t == mt.T - 1) {  // the new token becomes the row behind the tile's existing tokens
+        if constexpr (kTma) {
+          if (!mbar_wait(smem_u32(&sm.bar_k[seq & 1]), (uint32_t)(seq >> 1) & 1u)) dead = true;  // the rows must be there first
+        }
+        quantise_new_token(seq, mt.b, mt.h, mt.pad[0] - 1);
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+      }
+    }
     if (tid == 0) {
       JPT_PH(30);
       if constexpr (kTma) {
@@ -974,7 +959,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   bool pending = false;  // O^T of the tile before has not been added yet
   for (int i = 0; mt.t >= 0; ++i) {
     JPT_PH(11);
-    const float cks = scale_of(nks), cvs = scale_of(nvs);  // scales of this thread's token in tile i
+    float cks = scale_of(nks), cvs = scale_of(nvs);  // scales of this thread's token in tile i
+    if constexpr (kFused) {
+      if (mt.t == mt.T - 1 && tid == mt.pad[0] - 1) {  // the new token: its scales were just computed
+        cks = sm.ntsc[i & 1][0];
+        cvs = sm.ntsc[i & 1][1];
+      }
+    }
     const bool last_of_share = mt.pad[2] != 0;
     const uint32_t par = (uint32_t)i & 1u;
     if (i == 0 || mt.t == 0) {  // a piece starts (the one before was flushed when it ended)
@@ -1012,9 +1003,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         tmem_ld_wait();
       }
       JPT_PH(1);
-      if constexpr (kFused) {  // the tile ends a piece: what the new token needs travels with the next copies
-        if (last_of_share || mt.t == mt.T - 1) stage_new_token(mt.b, mt.h);
-      }
       issue_v(i + 1);
       issue_k(i + 2);
       JPT_PH(2);
@@ -1078,6 +1066,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       softmax_rows<0>(m_run, l_run, alpha, tm, xv, ps, p_base);
     }
     JPT_PH(5);
+    if constexpr (kFused) {
+      if (mt.t == mt.T - 1) {  // the new token's V codes into the row behind the tile's existing tokens
+        if constexpr (kTma) {
+          if (!mbar_wait(smem_u32(&sm.bar_v[i & 1]), (uint32_t)(i >> 1) & 1u)) dead = true;
+        } else {
+          cp_async_wait<3>();
+          __syncthreads();  // every thread's copies into this tile have landed
+        }
+        sm.v[i & 1][swz(mt.pad[0] - 1, tid)] = sm.ntv[i & 1][tid];
+      }
+    }
     cp_async_wait<3>();  // V rows of this tile (younger groups: K(i+1), V(i+1), K(i+2))
     fence_async_smem();
     JPT_PH(12);
@@ -1160,9 +1159,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         L8[r] = (sm.red[0][r] + sm.red[1][r]) + (sm.red[2][r] + sm.red[3][r]);
         M8[r] = m_run[r] > 0.5f * kNoMax ? m_run[r] : -INFINITY;  // every logit of the row was masked
       }
-      if constexpr (kFused) {
-        if (is_final) add_new_token(cb, chd, M8, L8, o);
-      }
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         if (r < R) {
@@ -1201,12 +1197,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         JPT_PH(27);
         if (sm.flag) {
           __threadfence();
-          if constexpr (kFused) {
-            const int hb = cb, hh = chd;
-            merge_segment(a, x, cfirst_cta, cparts, row_base, [&](auto& Mh, auto& Lh, auto& ah) { add_new_token(hb, hh, Mh, Lh, ah); });
-          } else {
-            merge_segment(a, x, cfirst_cta, cparts, row_base);
-          }
+          merge_segment(a, x, cfirst_cta, cparts, row_base);
         }
       }
     
