@@ -335,8 +335,10 @@ size_t jpt_flash_decode_workspace_bytes(const jpt_attn_params* p);
 int jpt_flash_decode_workspace_init(void* workspace, size_t bytes, void* stream);
 /*
  * Health word of the attention kernels that used this workspace: 0, or a
- * positive code if a bounded wait inside a kernel ever gave up (the kernel then
- * returns early and its outputs are invalid).  Copies one int to the host and
+ * positive code: 1 if a bounded wait inside a kernel ever gave up (the kernel
+ * then returns early and its outputs are invalid), 2 for a misaligned shared
+ * memory base, 3 if jpt_decode_update_attend met a sequence whose cache had no
+ * row left for the new token.  Copies one int to the host and
  * SYNCHRONISES the stream: a diagnostic for tests, not for the step path.
  * workspace == NULL reads the word of the scratch built into the library (the
  * one jpt_flash_decode_static uses) on the current device.  The word is sticky:
@@ -390,6 +392,12 @@ int jpt_flash_decode_static(const jpt_attn_params* p, void* stream);
  *            under the attention over the existing tokens.  A launch of this
  *            function and a launch of jpt_kv_quant_append_dense_peers on the same
  *            exchange buffers both count as one step of the exchange.
+ *            xk, xv must be 16-byte aligned.
+ * The token is attended to as the LAST token of its sequence (the kernel
+ * writes its codes into the last tile's rows in shared memory), so the
+ * range must leave room for it: end - start < S (ring) / end < S (length).
+ * A sequence that does not is attended to without the token and the
+ * workspace's status word reads 3 (jpt_flash_decode_status).
  * Returns JPT_EINVAL for shapes the fused kernel does not take (use the two
  * separate calls then).  Codes, scales and cache contents are bit-identical to
  * the separate update; attention rows agree within rounding.

@@ -366,7 +366,9 @@ class Int8KVCacheGenerate:
     written and `finalize` moves it into the cache later, as in the reference.
     `peers` (a `PeerAmaxExchange`) shards the KV heads over GPUs; the amax
     exchange then runs inside the same launch, hidden under the attention over
-    the existing tokens.
+    the existing tokens.  The token is attended to as the sequence's last one,
+    so the range must leave room for it (end - start < cache length); a sequence
+    that does not is attended to without it and `kernel_status()` reads 3.
 
     Returns (the 8-tuple `update` returns, (o [B,Hkv,rep,D], m, l [B,Hkv,rep])).
     Codes, scales and cache contents equal those of `update` bit for bit; the
