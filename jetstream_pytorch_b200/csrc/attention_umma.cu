@@ -427,14 +427,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 
   // Valid range of sequence b as the schedule sees it: with the fused update the step's new token
   // counts as the segment's last token (a full cache has no row for it: reported, the token is dropped).
-  auto seg_range = [&](int b, int* use_add) {
+  auto seg_range = [&](int b, int* use_add, bool* extended = nullptr) {
     SeqRange r = seq_range_x(a, x, b, use_add);
     if constexpr (kFused) {
-      if (r.n < a.S) {
+      const bool room = r.n < a.S;
+      if (room) {
         r.n += 1;
       } else {
         atomicExch(status, 3);
       }
+      if (extended) *extended = room;
     }
     return r;
   };
@@ -645,6 +647,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   // Position of the next tile whose K rows are to be fetched (uniform across the CTA) ...
   int pb = sm.start[0], ph = sm.start[1], pt, pslot = G0;  // pslot: global slot index of tile pt
   int pT, pn, pfirst, puse_add;
+  bool pext = false;  // the sequence's last token is the step's new one
   // ... and what follows from it for this thread: 16-byte column tid % 8 of
   // rows tid / 8 + 16 i of a tile.  The swizzled shared-memory offset of row
   // + 16 i is that of row plus 2048 i.
@@ -659,7 +662,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   int pfirst_cta, pparts;
 
   auto load_seq = [&]() {
-    const SeqRange r = seg_range(pb, &puse_add);
+    const SeqRange r = seg_range(pb, &puse_add, &pext);
     pn = r.n;
     pfirst = r.first;
     pT = tiles_u(r, a.S);
@@ -774,14 +777,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         mt.first_cta = pfirst_cta; mt.parts = pparts;
         mt.pad[0] = cnt;  // valid rows of the tile
         mt.pad[1] = pos;  // position of its first row (paged: token index)
-        mt.pad[2] = pslot + 1 >= G1;  // no tile follows in this CTA's share
+        mt.pad[2] = (pslot + 1 >= G1 ? 1 : 0)              // no tile follows in this CTA's share
+                    | (pext && pt == pT - 1 ? 2 : 0);      // the tile's last row is the step's new token
         sm.meta[seq & 3] = mt;
         if constexpr (kTma) request_rows(smem_u32(&sm.k[seq & 1][0]), &maps.k, smem_u32(&sm.bar_k[seq & 1]), pb, ph, pos, cnt);
       }
       JPT_PH(19);
       if constexpr (!kTma) copy_rows(smem_u32(&sm.k[seq & 1][0]), kbase, pb, ph, pos, cnt);
       if constexpr (kFused) {
-        if (pt == pT - 1) stage_new_token(seq, pb, ph);  // the segment's last tile takes the new token
+        if (pext && pt == pT - 1) stage_new_token(seq, pb, ph);  // the segment's last tile takes the new token
       }
       JPT_PH(20);
       advance();
@@ -899,7 +903,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       __syncthreads();
     }
     if constexpr (kFused) {
-      if (mt.t == mt.T - 1) {  // the new token becomes the row behind the tile's existing tokens
+      if (mt.pad[2] & 2) {  // the new token becomes the row behind the tile's existing tokens
         if constexpr (kTma) {
           if (!mbar_wait(smem_u32(&sm.bar_k[seq & 1]), (uint32_t)(seq >> 1) & 1u)) dead = true;  // the rows must be there first
         }
@@ -961,12 +965,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     JPT_PH(11);
     float cks = scale_of(nks), cvs = scale_of(nvs);  // scales of this thread's token in tile i
     if constexpr (kFused) {
-      if (mt.t == mt.T - 1 && tid == mt.pad[0] - 1) {  // the new token: its scales were just computed
+      if ((mt.pad[2] & 2) && tid == mt.pad[0] - 1) {  // the new token: its scales were just computed
         cks = sm.ntsc[i & 1][0];
         cvs = sm.ntsc[i & 1][1];
       }
     }
-    const bool last_of_share = mt.pad[2] != 0;
+    const bool last_of_share = (mt.pad[2] & 1) != 0;
     const uint32_t par = (uint32_t)i & 1u;
     if (i == 0 || mt.t == 0) {  // a piece starts (the one before was flushed when it ended)
       piece_t0 = mt.t;
@@ -1067,7 +1071,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
     JPT_PH(5);
     if constexpr (kFused) {
-      if (mt.t == mt.T - 1) {  // the new token's V codes into the row behind the tile's existing tokens
+      if (mt.pad[2] & 2) {  // the new token's V codes into the row behind the tile's existing tokens
         if constexpr (kTma) {
           if (!mbar_wait(smem_u32(&sm.bar_v[i & 1]), (uint32_t)(i >> 1) & 1u)) dead = true;
         } else {

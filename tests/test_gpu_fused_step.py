@@ -135,3 +135,32 @@ def test_fused_step_lone_rank_wait_runs_out():
     assert torch.equal(r[0].cpu(), e[0]) and torch.equal(r[6].cpu(), e[6])
   finally:
     px.close()
+
+
+def test_fused_step_full_cache_is_reported():
+  """A sequence whose cache has no row left for the new token: the launch attends to the existing
+  tokens of that sequence, writes nothing for it, and the workspace's status word reads 3; the other
+  sequences are unaffected, and the word is cleared by the read."""
+  from jetstream_pytorch_b200 import attention_kernel as ak
+  from jetstream_pytorch_b200.cache_manager import Int8KVCacheGenerate
+
+  b, hq, hkv, s, d = 4, 16, 2, 256, 128
+  ck, cv, ks, vs, q, xk, xv, start, end, input_pos = _case(404, b, hq, hkv, s, d, False)
+  end[3] = s          # full: the token has nowhere to go
+  input_pos[3] = s    # (out of range: not written)
+  env = make_env(batch_size=b, cache_sequence_length=s, ring_buffer=False)
+  dev = lambda x: x.to(DEV)
+  assert ak.kernel_status() == 0
+  c = Int8KVCacheGenerate(dev(ck).clone(), dev(cv).clone(), dev(ks).clone(), dev(vs).clone(), dev(input_pos), env=env)
+  r, (o, m, l) = c.update_and_attend(dev(q), dev(xk), dev(xv), 0, dev(start), dev(end))
+  torch.cuda.synchronize()
+  assert ak.kernel_status() == 3
+  assert ak.kernel_status() == 0
+  assert torch.equal(r[0][3].cpu(), ck[3]), "the full sequence's cache must be untouched"
+  ok = torch.tensor([True, True, True, False])
+  e = oc.int8_update(ck, cv, ks, vs, xk, xv, torch.where(ok, input_pos, torch.zeros_like(input_pos)), ring_buffer=False, lazy=False)
+  eo, (em, el) = oa.ragged_mha(q, e[0], e[1], 0, start, end + 1, e[4], e[5], bk=128)
+  assert attention_close(o[ok], eo[ok]), describe(o[ok], eo[ok])
+  # the full sequence: its existing tokens alone
+  fo, _ = oa.ragged_mha(q, ck, cv, 0, start, end, ks, vs, bk=128)
+  assert attention_close(o[3:], fo[3:]), describe(o[3:], fo[3:])
