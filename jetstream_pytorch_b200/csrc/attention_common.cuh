@@ -96,9 +96,15 @@ __device__ __forceinline__ float load_scale(const void* base, int64_t idx, int i
 
 // Every workspace starts with this many bytes of per-segment arrival counters
 // that must stay zero between launches; no kernel puts anything else there.
-constexpr size_t kWorkspaceCounterBytes = 256 * 1024;  // header: counters, then one status word in its last 256 bytes
+// header: 192 KiB of counters, then the one-GPU exchange area of the fused decode step, then one status
+// word in the last 256 bytes.  Everything whose meaning outlives a launch lives here, at offsets that do
+// not depend on the shape, because one workspace serves calls of any shape (whose partials would
+// otherwise land on another shape's state).
+constexpr size_t kWorkspaceCounterBytes = 256 * 1024;
 constexpr size_t kWorkspaceStatusOffset = kWorkspaceCounterBytes - 256;
-constexpr size_t kWorkspaceMaxSegments = kWorkspaceStatusOffset / sizeof(unsigned);  // (sequence, head) pairs
+constexpr size_t kWorkspaceExchangeOffset = 192 * 1024;
+constexpr size_t kWorkspaceExchangeBytes = kWorkspaceStatusOffset - kWorkspaceExchangeOffset;
+constexpr size_t kWorkspaceMaxSegments = kWorkspaceExchangeOffset / sizeof(unsigned);  // (sequence, head) pairs
 
 // The new token of a decode step, handed to the attention launch itself
 // (jpt_decode_update_attend): quantised with the decode quantiser, written to

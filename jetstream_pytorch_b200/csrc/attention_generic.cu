@@ -311,6 +311,8 @@ extern "C" int jpt_decode_update_attend(const jpt_attn_params* pp, const jpt_new
               "decode_update_attend: the new token must be bf16 or f32");
   JPT_REQUIRE(p.scale_dtype == nt->in_dtype || !nt->write_cache, JPT_EINVAL,
               "decode_update_attend: the scale caches must have the new token's dtype");
+  JPT_REQUIRE(nt->px != nullptr || exchange_bytes(p.B, 1) <= kWorkspaceExchangeBytes, JPT_EINVAL,
+              "decode_update_attend: batch %d is more than the workspace's exchange area holds", p.B);
   JPT_REQUIRE(nt->pos == nullptr || nt->pos_count == 1 || nt->pos_count == p.B, JPT_EINVAL,
               "decode_update_attend: pos_count must be 1 or B");
   NewTokenArgs n{};

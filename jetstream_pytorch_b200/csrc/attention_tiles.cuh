@@ -224,8 +224,7 @@ inline ScratchLayout scratch_layout(const jpt_attn_params& p, int num_ctas) {
   off = kWorkspaceCounterBytes;
   s.seqinfo = off;
   off = align_up(off + sizeof(int32_t) * 4 * p.B, 256);
-  s.exchange = off;  // one-GPU exchange slots of the fused update (zero after workspace init, kept consistent by the kernel)
-  off = align_up(off + exchange_bytes(p.B, 1), 256);
+  s.exchange = kWorkspaceExchangeOffset;  // one-GPU exchange slots of the fused update, inside the header
   s.part_m = off;
   off = align_up(off + sizeof(float) * s.num_ctas * 2 * kMaxRows, 256);
   s.part_l = off;

@@ -127,10 +127,10 @@ __device__ __forceinline__ float ex2(float x) {
 // probability, denominator share, and the probability's two level bytes.
 // m_run starts at kNoMax (finite), so exp2(old - new) and exp2(-inf - new) need
 // no special case.
-template <int kRow>
+template <int kRow, int kR>
 __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8], float (&alpha)[8], const float (&tm)[8],
                                              const float (&xv)[8], float ps, uint32_t p_base) {
-  if constexpr (kRow < 8) {
+  if constexpr (kRow < kR) {
     const float mn = fmaxf(m_run[kRow], tm[kRow]);
     const float al = ex2(m_run[kRow] - mn);
     const float p = ex2(xv[kRow] - mn);
@@ -139,7 +139,7 @@ __device__ __forceinline__ void softmax_rows(float (&m_run)[8], float (&l_run)[8
     l_run[kRow] = fmaf(l_run[kRow], al, p);
     // the byte of row r: 16-byte chunk (t / 16) ^ r of that row (the XOR folds into the address)
     store_levels<128 * kRow>(p_base ^ (uint32_t)(kRow << 4), __float2uint_rn(p * ps));
-    softmax_rows<kRow + 1>(m_run, l_run, alpha, tm, xv, ps, p_base);
+    softmax_rows<kRow + 1, kR>(m_run, l_run, alpha, tm, xv, ps, p_base);
   }
 }
 // A segment's valid tokens form one run of consecutive rows, or two when the
@@ -300,8 +300,10 @@ __device__ unsigned long long g_umma_phase[1024 * 32];
 #endif
 
 // kFused = the launch carries the decode step's new token, kRound = dense_attention's rounded
-// logit chain, kTma = the copy engine moves the K/V rows (tensor maps) instead of the threads.
-template <bool kFused, bool kRound, bool kTma>
+// logit chain, kTma = the copy engine moves the K/V rows (tensor maps) instead of the threads, kR = query
+// rows the softmax phase works on (8, or 2 for multi-head attention with its single row per KV head; the
+// level rows of the others hold zeros, their results are never looked at).
+template <bool kFused, bool kRound, bool kTma, int kR>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     flash_decode_i8_umma_kernel(const __grid_constant__ AttnArgs a, const __grid_constant__ MmaScratch x, int* status,
                                 const __grid_constant__ NewTokenArgs nt, const __grid_constant__ TmaMaps maps, int tma_mode,
@@ -937,7 +939,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     tc_fence_before();
     const float oscale = cmax * (1.f / 65535.f);
 #pragma unroll
-    for (int r = 0; r < 8; ++r)  // the two levels combine exactly in int32
+    for (int r = 0; r < kR; ++r)  // the two levels combine exactly in int32
       o[r] = fmaf(o[r], alpha[r], (float)((int)o01[r] + ((int)o01[8 + r] << 8)) * oscale);
   };
 
@@ -975,7 +977,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     if (i == 0 || mt.t == 0) {  // a piece starts (the one before was flushed when it ended)
       piece_t0 = mt.t;
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int r = 0; r < kR; ++r) {
         m_run[r] = kNoMax;
         l_run[r] = 0.f;
         o[r] = 0.f;
@@ -999,7 +1001,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         tmem_ld_wait();
         const float oscale = cmax_prev * (1.f / 65535.f);
 #pragma unroll
-        for (int r = 0; r < 8; ++r)  // the two levels combine exactly in int32 (|O_0 + 256 O_1| < 2^31)
+        for (int r = 0; r < kR; ++r)  // the two levels combine exactly in int32 (|O_0 + 256 O_1| < 2^31)
           o[r] = fmaf(o[r], alpha_prev[r], (float)((int)o01[r] + ((int)o01[8 + r] << 8)) * oscale);
         pending = false;
       } else {
@@ -1019,20 +1021,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         const float qc[8] = {q0.x * cks, q0.y * cks, q0.z * cks, q0.w * cks, q1.x * cks, q1.y * cks, q1.z * cks, q1.w * cks};
         const float ml = mk * kLog2e;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) xv[r] = fmaf((float)((int)s[r] * 254 + (int)s[8 + r]), qc[r], ml);
+        for (int r = 0; r < kR; ++r) xv[r] = fmaf((float)((int)s[r] * 254 + (int)s[8 + r]), qc[r], ml);
       } else {
         // dense_attention on bf16 tensors: the reference rounds the logit to bf16 after every step
         const float sqrt_d = __frcp_rn(a.sm_scale);
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
+        for (int r = 0; r < kR; ++r)
           xv[r] = kLog2e * rounded_logit((float)((int)s[r] * 254 + (int)s[8 + r]) * sm.qsr[r], sqrt_d, cks, quant, mk);
       }
     }
     // tile maxima per row (and the largest V scale) across the 128 tokens
     {
-      float wm[9];
+      float wm[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < 8; ++r) wm[r] = warp_max(xv[r]);
+      for (int r = 0; r < kR; ++r) wm[r] = warp_max(xv[r]);
       wm[8] = warp_max(cvs);
       if (lane == 0) {
         *reinterpret_cast<float4*>(&sm.xch[warp][0]) = make_float4(wm[0], wm[1], wm[2], wm[3]);
@@ -1067,7 +1069,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       // p <= 1 and the product is held at 2^16 - 1 (the fast division may land one ulp above)
       const float rc = cmax > 0.f ? __fdividef(65535.f, cmax) : 0.f;
       const float ps = fminf(cvs * rc, 65535.f);
-      softmax_rows<0>(m_run, l_run, alpha, tm, xv, ps, p_base);
+      softmax_rows<0, kR>(m_run, l_run, alpha, tm, xv, ps, p_base);
     }
     JPT_PH(5);
     if constexpr (kFused) {
@@ -1108,7 +1110,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const int cb = mt.b, chd = mt.h, ct = mt.t, cT = mt.T, cfirst_cta = mt.first_cta, cparts = mt.parts;
     if (!piece_ends) {
 #pragma unroll
-      for (int r = 0; r < 8; ++r) alpha_prev[r] = alpha[r];
+      for (int r = 0; r < kR; ++r) alpha_prev[r] = alpha[r];
       cmax_prev = cmax;
       pending = true;
     }
@@ -1146,7 +1148,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       const int64_t row_base = ((int64_t)cb * a.Hkv + chd) * R;
       // denominators: sum the token shares of the 128 threads (while the last O^T MMA runs)
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int r = 0; r < kR; ++r) {
         float l = l_run[r];
 #pragma unroll
         for (int sh = 1; sh <= 16; sh <<= 1) l += __shfl_xor_sync(0xffffffffu, l, sh);
@@ -1157,14 +1159,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       JPT_PH(23);
       add_output(par, alpha, cmax);
       JPT_PH(24);
-      float L8[8], M8[8];
+      float L8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, M8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int r = 0; r < kR; ++r) {
         L8[r] = (sm.red[0][r] + sm.red[1][r]) + (sm.red[2][r] + sm.red[3][r]);
         M8[r] = m_run[r] > 0.5f * kNoMax ? m_run[r] : -INFINITY;  // every logit of the row was masked
       }
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int r = 0; r < kR; ++r) {
         if (r < R) {
           const float L = L8[r], M = M8[r];
           if (is_final) {
@@ -1360,14 +1362,22 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
           if (e == cudaSuccess)
             e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         };
-        set(flash_decode_i8_umma_kernel<false, false, false>);
-        set(flash_decode_i8_umma_kernel<false, false, true>);
-        set(flash_decode_i8_umma_kernel<false, true, false>);
-        set(flash_decode_i8_umma_kernel<false, true, true>);
-        set(flash_decode_i8_umma_kernel<true, false, false>);
-        set(flash_decode_i8_umma_kernel<true, false, true>);
-        set(flash_decode_i8_umma_kernel<true, true, false>);
-        set(flash_decode_i8_umma_kernel<true, true, true>);
+        set(flash_decode_i8_umma_kernel<false, false, false, 8>);
+        set(flash_decode_i8_umma_kernel<false, false, true, 8>);
+        set(flash_decode_i8_umma_kernel<false, true, false, 8>);
+        set(flash_decode_i8_umma_kernel<false, true, true, 8>);
+        set(flash_decode_i8_umma_kernel<true, false, false, 8>);
+        set(flash_decode_i8_umma_kernel<true, false, true, 8>);
+        set(flash_decode_i8_umma_kernel<true, true, false, 8>);
+        set(flash_decode_i8_umma_kernel<true, true, true, 8>);
+        set(flash_decode_i8_umma_kernel<false, false, false, 2>);
+        set(flash_decode_i8_umma_kernel<false, false, true, 2>);
+        set(flash_decode_i8_umma_kernel<false, true, false, 2>);
+        set(flash_decode_i8_umma_kernel<false, true, true, 2>);
+        set(flash_decode_i8_umma_kernel<true, false, false, 2>);
+        set(flash_decode_i8_umma_kernel<true, false, true, 2>);
+        set(flash_decode_i8_umma_kernel<true, true, false, 2>);
+        set(flash_decode_i8_umma_kernel<true, true, true, 2>);
         return e;
       }))
     return rc;
@@ -1393,8 +1403,16 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   const int tma_mode = tensor_maps_for(p, &maps, &box_rows);
   const bool fused = nt.enabled != 0, round = a.round_logits != 0, tma = tma_mode != kTmaNone;
   const dim3 grid(lay.num_ctas), block(kThreads);
-#define JPT_UMMA_LAUNCH(F, Rd, T) \
-  launch_after_previous(flash_decode_i8_umma_kernel<F, Rd, T>, grid, block, smem_bytes, st, a, x, status, nt, maps, tma_mode, box_rows)
+#define JPT_UMMA_LAUNCH2(F, Rd, T)                                                                                       \
+  do {                                                                                                                   \
+    if (a.R <= 2)                                                                                                        \
+      launch_after_previous(flash_decode_i8_umma_kernel<F, Rd, T, 2>, grid, block, smem_bytes, st, a, x, status, nt, maps, \
+                            tma_mode, box_rows);                                                                         \
+    else                                                                                                                 \
+      launch_after_previous(flash_decode_i8_umma_kernel<F, Rd, T, 8>, grid, block, smem_bytes, st, a, x, status, nt, maps, \
+                            tma_mode, box_rows);                                                                         \
+  } while (0)
+#define JPT_UMMA_LAUNCH(F, Rd, T) JPT_UMMA_LAUNCH2(F, Rd, T)
   if (fused) {
     if (round) { if (tma) JPT_UMMA_LAUNCH(true, true, true); else JPT_UMMA_LAUNCH(true, true, false); }
     else       { if (tma) JPT_UMMA_LAUNCH(true, false, true); else JPT_UMMA_LAUNCH(true, false, false); }
@@ -1402,6 +1420,7 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
     if (round) { if (tma) JPT_UMMA_LAUNCH(false, true, true); else JPT_UMMA_LAUNCH(false, true, false); }
     else       { if (tma) JPT_UMMA_LAUNCH(false, false, true); else JPT_UMMA_LAUNCH(false, false, false); }
   }
+#undef JPT_UMMA_LAUNCH2
 #undef JPT_UMMA_LAUNCH
   return check_launch("flash_decode_i8_umma_kernel");
 }

@@ -164,3 +164,35 @@ def test_fused_step_full_cache_is_reported():
   # the full sequence: its existing tokens alone
   fo, _ = oa.ragged_mha(q, ck, cv, 0, start, end, ks, vs, bk=128)
   assert attention_close(o[3:], fo[3:]), describe(o[3:], fo[3:])
+
+
+def test_fused_step_state_survives_other_shapes_on_the_workspace():
+  """The fused launch keeps a launch counter and exchange words in the workspace between calls; launches
+  of other shapes in between (whose partial results use the same workspace) must not disturb them."""
+  from jetstream_pytorch_b200 import attention_kernel as ak
+  from jetstream_pytorch_b200.cache_manager import Int8KVCacheGenerate
+
+  b, hq, hkv, s, d = 6, 32, 4, 512, 128
+  ck, cv, ks, vs, q, xk, xv, start, end, input_pos = _case(405, b, hq, hkv, s, d, False)
+  env = make_env(batch_size=b, cache_sequence_length=s, ring_buffer=False)
+  dev = lambda x: x.to(DEV)
+  fused = Int8KVCacheGenerate(dev(ck).clone(), dev(cv).clone(), dev(ks).clone(), dev(vs).clone(), dev(input_pos), env=env)
+  plain = Int8KVCacheGenerate(dev(ck).clone(), dev(cv).clone(), dev(ks).clone(), dev(vs).clone(), dev(input_pos), env=env)
+  g = torch.Generator().manual_seed(406)
+  for call in range(3):
+    r, _ = fused.update_and_attend(dev(q), dev(xk), dev(xv), 0, dev(start), dev(end))
+    rp = plain.update(dev(xk), dev(xv), 0)
+    for i, (got, want) in enumerate(zip(r, rp)):
+      assert torch.equal(got, want), f"call {call}: element {i} of the update tuple differs"
+    # other shapes on the same workspace: a long bf16 cache with few sequences (many partial pieces) ...
+    ob, oh, os_, od = 2, 8, 4096, 128
+    k2 = torch.randn(ob, oh, os_, od, generator=g).to(torch.bfloat16).to(DEV)
+    q2 = torch.randn(ob, oh, 1, od, generator=g).to(torch.bfloat16).to(DEV)
+    ak.ragged_mha(q2, k2, k2, 0, torch.zeros(ob, dtype=torch.int32, device=DEV),
+                  torch.full((ob,), os_, dtype=torch.int32, device=DEV), None, None, None, None)
+    # ... and the split-K kernel (head_dim 64)
+    k3 = torch.randn(3, 2, 1024, 64, generator=g).to(torch.bfloat16).to(DEV)
+    q3 = torch.randn(3, 2, 1, 64, generator=g).to(torch.bfloat16).to(DEV)
+    ak.ragged_mha(q3, k3, k3, 0, torch.zeros(3, dtype=torch.int32, device=DEV),
+                  torch.full((3,), 1024, dtype=torch.int32, device=DEV), None, None, None, None)
+  assert ak.kernel_status() == 0
