@@ -685,6 +685,14 @@ def run_cuda(args):
     for i in range(nl):
       caches[i].update(hk_all[i], hv_all[i], i, peers=px)
 
+  # the same caches under multi-head attention: one query head per KV head (Llama-2-7B/13B-like grouping)
+  q_mha = hq_all[:, :, ::HQ // HKV].contiguous()
+  o_mha = torch.empty_like(q_mha)
+
+  def attn_mha_only():
+    for i in range(nl):
+      ak.ragged_mha(q_mha[i], ck[i], cv[i], i, start_d, lens_d, None, None, ks[i], vs[i], out=(o_mha[i], None, None))
+
   def two_launch_layer(i):
     r = caches[i].update(hk_all[i], hv_all[i], i, peers=px)
     ak.ragged_mha(hq_all[i], r[0], r[1], i, start_d, lens_d, None, None, r[4], r[5], out=(o_s[i], m_s[i], l_s[i]))
@@ -696,6 +704,8 @@ def run_cuda(args):
 
   reps = max(1, args.steps // 2)
   legs = {"attn": attn_only, "ring": attn_ring_only, "append": append_only}
+  if world == 1:
+    legs["mha"] = attn_mha_only
   if not fused and (world == 1 or px is not None):
     legs["fused"] = fused_only
   if fused:
@@ -843,6 +853,10 @@ def run_cuda(args):
   traffic, traffic_src = profiled_traffic() if world == 1 else (None, "captured on one GPU holding all 8 KV heads only")
   kernels = {"attention_ring": kernel_entry(ms_leg["ring"] * 1e3, attention_bytes(ring_n.sum(), B, hq, hkv), peak,
                                             workload="same caches, start,end~U[0,2048) with wrap (ring semantics)")}
+  if "mha" in ms_leg:
+    kernels["attention_mha"] = kernel_entry(
+        ms_leg["mha"] * 1e3, attention_bytes(lens.sum(), B, hkv, hkv, ml=False), peak,
+        workload="same caches, one query head per KV head (multi-head attention): the kernel's two-row variant")
   if "append" in ms_leg:
     kernels["kv_quant_append"] = kernel_entry(ms_leg["append"] * 1e3, append_bytes(B, hkv), peak)
   if "two_launch" in ms_leg:
