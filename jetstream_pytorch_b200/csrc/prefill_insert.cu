@@ -164,6 +164,60 @@ __global__ void __launch_bounds__(256) insert_quant_warp_kernel(InsertArgs a) {
     return;
   }
   const T* src = static_cast<const T*>(a.prefix[which]) + l * a.ps_l + (int64_t)t * a.ps_t;
+  if constexpr (sizeof(T) == 2) {
+    // bf16 tokens: the reference's chain is a chain of bf16 operations, which the packed bf16
+    // instructions perform exactly (|x| and max are exact; the product of two bf16 values rounded
+    // once to bf16 is what `bf16(w * r)` is), two elements per instruction.
+    uint4 raw[NVW][2];
+#pragma unroll
+    for (int n = 0; n < NVW; ++n) {
+      const int e = (n * 32 + lane) * 16;
+      const int h = e / a.D, d = e - h * a.D;
+      const uint4* p = reinterpret_cast<const uint4*>(src + h * a.ps_h + d);
+      raw[n][0] = p[0];
+      raw[n][1] = p[1];
+    }
+    __nv_bfloat162 m2 = __float2bfloat162_rn(0.f);
+#pragma unroll
+    for (int n = 0; n < NVW; ++n)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[n][j]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m2 = __hmax2(m2, __habs2(h2[i]));
+      }
+    const float2 mf = __bfloat1622float2(m2);
+    float amax = fmaxf(mf.x, mf.y);
+#pragma unroll
+    for (int sh = 16; sh >= 1; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+    const float scale = insert_scale<T>(amax);
+    const float recip = insert_recip<T>(scale);
+    if (!dst.ok) return;
+    const __nv_bfloat162 r2 = __float2bfloat162_rn(recip);  // (exact: recip is a bf16 value)
+#pragma unroll
+    for (int n = 0; n < NVW; ++n) {
+      const int e = (n * 32 + lane) * 16;
+      const int h = e / a.D, d = e - h * a.D;
+      uint32_t packed[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[n][j]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {  // four elements -> four bytes
+          const float2 lo = __bfloat1622float2(__hmul2(h2[2 * i], r2)), hi = __bfloat1622float2(__hmul2(h2[2 * i + 1], r2));
+          // round half to even, then saturate to int8 while packing (element 0 in the lowest byte)
+          const int q0 = __float2int_rn(lo.x), q1 = __float2int_rn(lo.y), q2 = __float2int_rn(hi.x), q3 = __float2int_rn(hi.y);
+          uint32_t top, all;
+          asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(top) : "r"(q3), "r"(q2), "r"(0));
+          asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(all) : "r"(q1), "r"(q0), "r"(top));
+          packed[2 * j + i] = all;
+        }
+      }
+      *reinterpret_cast<uint4*>(cache + dst.row0 + h * dst.hstep + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    if (lane == 0 && scaler) scaler[dst.sidx] = from_f32<T>(scale);
+    return;
+  }
   float v[NVW][16];
   float amax = 0.f;
 #pragma unroll
