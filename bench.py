@@ -784,7 +784,7 @@ def run_cuda(args):
   q_s, k_s, v_s = torch.empty_like(hq_all), torch.empty_like(hk_all), torch.empty_like(hv_all)
   copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
   compute = torch.cuda.current_stream()
-  chunk = max(1, nl // 8)
+  chunk = max(1, nl // max(1, args.e2e_chunks))
   chunks = [(c0, min(nl, c0 + chunk)) for c0 in range(0, nl, chunk)]
 
   def chunk_fn(c0, c1):
@@ -933,6 +933,8 @@ def main():
   ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
   ap.add_argument("--layers", type=int, default=80)
   ap.add_argument("--no-graph", action="store_true")
+  ap.add_argument("--e2e-chunks", type=int, default=16,
+                  help="end-to-end leg: the layers are pipelined (copy in, compute, copy out) in this many chunks")
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--fused", action="store_true",
                   help="per layer one launch that appends the new token and attends (the default when N > 1)")
