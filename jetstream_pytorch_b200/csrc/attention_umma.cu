@@ -301,8 +301,9 @@ __device__ unsigned long long g_umma_phase[1024 * 32];
 
 // kFused = the launch carries the decode step's new token, kRound = dense_attention's rounded
 // logit chain, kTma = the copy engine moves the K/V rows (tensor maps) instead of the threads, kR = query
-// rows the softmax phase works on (8, or 2 for multi-head attention with its single row per KV head; the
-// level rows of the others hold zeros, their results are never looked at).
+// rows the softmax phase works on (8; 4 for groups of up to four query heads; 2 for multi-head attention
+// with its single row per KV head; the level rows of the others hold zeros, their results are never
+// looked at).
 template <bool kFused, bool kRound, bool kTma, int kR>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     flash_decode_i8_umma_kernel(const __grid_constant__ AttnArgs a, const __grid_constant__ MmaScratch x, int* status,
@@ -1383,6 +1384,14 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
         set(flash_decode_i8_umma_kernel<true, false, true, 8>);
         set(flash_decode_i8_umma_kernel<true, true, false, 8>);
         set(flash_decode_i8_umma_kernel<true, true, true, 8>);
+        set(flash_decode_i8_umma_kernel<false, false, false, 4>);
+        set(flash_decode_i8_umma_kernel<false, false, true, 4>);
+        set(flash_decode_i8_umma_kernel<false, true, false, 4>);
+        set(flash_decode_i8_umma_kernel<false, true, true, 4>);
+        set(flash_decode_i8_umma_kernel<true, false, false, 4>);
+        set(flash_decode_i8_umma_kernel<true, false, true, 4>);
+        set(flash_decode_i8_umma_kernel<true, true, false, 4>);
+        set(flash_decode_i8_umma_kernel<true, true, true, 4>);
         set(flash_decode_i8_umma_kernel<false, false, false, 2>);
         set(flash_decode_i8_umma_kernel<false, false, true, 2>);
         set(flash_decode_i8_umma_kernel<false, true, false, 2>);
@@ -1420,6 +1429,9 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
   do {                                                                                                                   \
     if (a.R <= 2)                                                                                                        \
       launch_after_previous(flash_decode_i8_umma_kernel<F, Rd, T, 2>, grid, block, smem_bytes, st, a, x, status, nt, maps, \
+                            tma_mode, box_rows);                                                                         \
+    else if (a.R <= 4)                                                                                                   \
+      launch_after_previous(flash_decode_i8_umma_kernel<F, Rd, T, 4>, grid, block, smem_bytes, st, a, x, status, nt, maps, \
                             tma_mode, box_rows);                                                                         \
     else                                                                                                                 \
       launch_after_previous(flash_decode_i8_umma_kernel<F, Rd, T, 8>, grid, block, smem_bytes, st, a, x, status, nt, maps, \
