@@ -292,6 +292,76 @@ def kernel_entry(us, nbytes, peak, **extra):
 # ---------------------------------------------------------------------------
 
 
+def peer_insert(reps, nl=32):
+  """Prefill -> decode hand-over inside one box (one process, two GPUs): a 2048-token bf16 prefix of `nl`
+  layers (8 KV heads, D=128) that lies on cuda:1 goes into the int8 page pools of cuda:0 with the insert
+  quantiser.  Timed: the insert of a prefix already on cuda:0; the insert kernel of cuda:0 reading the
+  prefix from cuda:1 over NVLink (one pass); and a peer copy to cuda:0 followed by the local insert."""
+  from jetstream_pytorch_b200 import insert as ins
+  from jetstream_pytorch_b200.page_attention_manager import PageAttentionManager
+
+  if torch.cuda.device_count() < 2:
+    return {"unavailable": "needs two GPUs in one process"}
+  d0, d1 = torch.device("cuda", 0), torch.device("cuda", 1)
+  h, l, d, b, p, ps, maxp = 8, 2048, 128, 8, 512, 64, 40
+  g = torch.Generator().manual_seed(1)
+  spk = torch.randn(nl, 1, h, l, d, generator=g).to(torch.bfloat16)
+  spv = torch.randn(nl, 1, h, l, d, generator=g).to(torch.bfloat16)
+  loc, rem = (spk.to(d0), spv.to(d0)), (spk.to(d1), spv.to(d1))
+  kp = torch.zeros(nl, h, p, ps, d, dtype=torch.int8, device=d0)
+  vp = torch.zeros_like(kp)
+  ksp = torch.zeros(nl, 1, p, ps, 1, dtype=torch.bfloat16, device=d0)
+  vsp = torch.zeros_like(ksp)
+  pam = PageAttentionManager(b, p, ps, maxp)
+  _, upd = pam.reserve_pages_insert(0, l)
+  upd = torch.as_tensor(np.asarray(upd).astype(np.int32)).to(d0)
+  pools = [(kp[i], vp[i]) for i in range(nl)]
+  scales = [(ksp[i], vsp[i]) for i in range(nl)]
+  stage = (torch.empty_like(loc[0]), torch.empty_like(loc[1]))
+
+  def run(src):
+    pam.insert_prefill_cache([(src[0][i], src[1][i]) for i in range(nl)], pools, upd, None, None, decode_scales=scales)
+
+  def copy_then_insert():
+    stage[0].copy_(rem[0], non_blocking=True)
+    stage[1].copy_(rem[1], non_blocking=True)
+    run(stage)
+
+  ins.prefix_on_peer(rem[0], d0)  # access enabled and streams ordered once: the captures below hold the kernel alone
+  order_streams, ins.prefix_on_peer = ins.prefix_on_peer, lambda *a, **k: None
+  out = {"workload": f"2048-token bf16 prefix x {nl} layers (8 KV heads, D=128) into int8 pages of cuda:0",
+         "prefix_bytes": 2 * nl * l * h * d * 2}
+  try:
+    with torch.cuda.device(d0):
+      for key, f, graph in (("same_gpu", lambda: run(loc), True), ("peer_read_by_insert_kernel", lambda: run(rem), True),
+                            ("peer_copy_then_insert", copy_then_insert, False)):
+        for _ in range(3):
+          f()
+        torch.cuda.synchronize(d0)
+        torch.cuda.synchronize(d1)
+        fn = f
+        if graph:  # (a copy between devices cannot be captured: that leg is timed eagerly)
+          gr = torch.cuda.CUDAGraph()
+          with torch.cuda.graph(gr):
+            f()
+          fn = gr.replay
+        fn()
+        torch.cuda.synchronize(d0)
+        torch.cuda.synchronize(d1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(max(3, reps)):
+          fn()
+        e1.record()
+        torch.cuda.synchronize(d0)
+        torch.cuda.synchronize(d1)
+        us = e0.elapsed_time(e1) * 1e3 / max(3, reps)
+        out[key] = {"us": us, "prefix_gbs": out["prefix_bytes"] / us / 1e3}
+  finally:
+    ins.prefix_on_peer = order_streams
+  return out
+
+
 def extra_dense_int8_mha(dev, peak, reps):
   """Dense int8 KV decode step, Llama-2-7B-shaped MHA: batch 8, 32 heads,
   D=128, S=2048; quantise+append (ring: one shared position; per-slot
@@ -518,6 +588,9 @@ def run_cuda(args):
   peak, peak_kind = peaks()
   if args.only == "insert":
     print(json.dumps({"only": "insert", **extra_insert_burst(dev, peak, args.steps, nl=min(32, nl))}), flush=True)
+    return
+  if args.only == "peer-insert":
+    print(json.dumps({"only": "peer-insert", **peer_insert(args.steps, nl=min(32, nl))}), flush=True)
     return
 
   # ---- device-resident state: every layer owns its cache (>> L2 in total).  Layer 0 comes from
@@ -943,7 +1016,7 @@ def main():
   ap.add_argument("--no-extras", action="store_true", help="skip the other workloads' kernels (N = 1 runs them by default)")
   ap.add_argument("--amax-exchange", choices=["peers", "nccl"], default="peers",
                   help="N > 1: how the per-token amax is max-reduced over the ranks")
-  ap.add_argument("--only", choices=["attention", "append", "insert"], default=None,
+  ap.add_argument("--only", choices=["attention", "append", "insert", "peer-insert"], default=None,
                   help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
   ap.add_argument("--kv", choices=["int8", "bf16"], default="int8", help="with --only attention: cache dtype")
   ap.add_argument("--attn-kernel", choices=["auto", "mma"], default="auto",

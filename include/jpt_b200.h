@@ -226,6 +226,19 @@ int jpt_prefill_insert_dense(const void* prefix_k, const void* prefix_v,
                              int64_t ss_b, int64_t ss_s, void* stream);
 
 /*
+ * Disaggregated serving: the prefix produced on a prefill GPU may be handed to
+ * jpt_prefill_insert_dense / jpt_prefill_insert_paged of the decode GPU while it
+ * still lies in the prefill GPU's memory (prefix_k / prefix_v are then peer
+ * pointers; everything else belongs to the device the call is launched on).
+ * The insert kernels read it over NVLink and write rows, codes and scales in
+ * the cache's own format, so the transfer and the insert are one pass.
+ * Replaces the prefill -> decode hand-over through host memory of
+ * jetstream_pt/ray_worker.py:501-551 and jetstream_pt/ray_engine.py:119-127.
+ * This call makes the peer's memory readable from `device` (idempotent).
+ */
+int jpt_enable_peer_access(int device, int peer);
+
+/*
  * Scatter a prefix into pages: page i of the prefix goes to page
  * update_indexes[i]; the tail of the last page is written with zeros.
  * Replaces PageAttentionManager.insert_prefill_cache,

@@ -90,6 +90,7 @@ _SIGNATURES = {
                                          c_void_p] + [c_int] * 8 + [c_i64] * 10 + [c_void_p]),
     "jpt_prefill_insert_paged": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                          c_void_p, c_void_p] + [c_int] * 7 + [c_i64] * 5 + [c_void_p]),
+    "jpt_enable_peer_access": (c_int, [c_int, c_int]),
     "jpt_quantize_tokens": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "jpt_flash_decode": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
     "jpt_flash_decode_static": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),

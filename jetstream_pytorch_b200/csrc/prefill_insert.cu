@@ -402,3 +402,27 @@ extern "C" int jpt_quantize_tokens(const void* w, int in_dtype, int token_major,
   a.ss_s = 1;
   return launch_insert(a, in_dtype, JPT_INT8, static_cast<cudaStream_t>(stream));
 }
+
+// Lets kernels launched on `device` read the memory of `peer` (NVLink peer loads): what a decode GPU needs
+// to insert a prefix that still lies in the prefill GPU's memory.  Idempotent; the current device is kept.
+extern "C" int jpt_enable_peer_access(int device, int peer) {
+  JPT_REQUIRE(device >= 0 && peer >= 0, JPT_EINVAL, "enable_peer_access: negative device");
+  if (device == peer) return 0;
+  int can = 0;
+  cudaError_t e = cudaDeviceCanAccessPeer(&can, device, peer);
+  if (e != cudaSuccess) return fail((int)e, "enable_peer_access: %s", cudaGetErrorString(e));
+  JPT_REQUIRE(can, JPT_EINVAL, "enable_peer_access: device %d cannot access the memory of device %d", device, peer);
+  int cur = 0;
+  cudaGetDevice(&cur);
+  e = cudaSetDevice(device);
+  if (e == cudaSuccess) {
+    e = cudaDeviceEnablePeerAccess(peer, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+      cudaGetLastError();  // (not an error: clear it)
+      e = cudaSuccess;
+    }
+  }
+  cudaSetDevice(cur);
+  if (e != cudaSuccess) return fail((int)e, "enable_peer_access: %s", cudaGetErrorString(e));
+  return 0;
+}

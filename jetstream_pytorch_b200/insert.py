@@ -10,6 +10,29 @@ import torch
 from jetstream_pytorch_b200 import _lib
 
 
+_peer_enabled = set()
+
+
+def prefix_on_peer(prefix, cache_device):
+  """Disaggregated serving (the reference hands the prefix from the prefill engine to the decode
+  engine through host memory, ray_worker.py:501-551): a prefix that lies on ANOTHER GPU of the box
+  is inserted as it is.  The insert kernels of the cache's GPU read it over NVLink and write rows,
+  codes and scales in the cache's format, so transfer and insert are one pass.  This makes the
+  prefix's memory readable from `cache_device` (once per pair of devices) and orders the cache
+  device's stream after the work queued so far on the prefix's device."""
+  src, dst = prefix.device, torch.device(cache_device)
+  if src == dst:
+    return
+  if src.type != "cuda" or dst.type != "cuda":
+    raise ValueError(f"prefix on {src}, cache on {dst}: both must be GPUs of one box")
+  if (dst.index, src.index) not in _peer_enabled:
+    _lib.check(_lib.lib().jpt_enable_peer_access(dst.index, src.index))
+    _peer_enabled.add((dst.index, src.index))
+  done = torch.cuda.Event()
+  done.record(torch.cuda.current_stream(src))
+  torch.cuda.current_stream(dst).wait_event(done)
+
+
 def _prefix_strides(pk, pv):
   if pk.stride(-1) != 1 or pv.stride() != pk.stride():
     pk, pv = pk.contiguous(), pv.contiguous()
@@ -29,6 +52,8 @@ def insert_dense(prefix_k, prefix_v, cache_k, cache_v, slot, pos, *, wrap=False,
     if k_scaler is not None:
       k_scaler, v_scaler = k_scaler[layer], v_scaler[layer]
   pk, pv = _prefix_strides(prefix_k, prefix_v)
+  if pk.device != cache_k.device:  # a prefix still on the prefill GPU: read over NVLink by this GPU's kernel
+    prefix_on_peer(pk, cache_k.device)
   _, h, l, d = pk.shape
   b, hc, s, dc = cache_k.shape
   if (hc, dc) != (h, d):
@@ -41,10 +66,11 @@ def insert_dense(prefix_k, prefix_v, cache_k, cache_v, slot, pos, *, wrap=False,
   ss = (0, 0)
   if k_scaler is not None:
     ss = (k_scaler.stride(0), k_scaler.stride(2))
-  _lib.check(_lib.lib().jpt_prefill_insert_dense(
-      _lib.ptr(pk), _lib.ptr(pv), _lib.dt(pk), _lib.ptr(cache_k), _lib.ptr(cache_v), _lib.dt(cache_k),
-      _lib.ptr(k_scaler), _lib.ptr(v_scaler), slot, int(pos), int(wrap), 1, h, l, s, d, 0, pk.stride(1),
-      pk.stride(2), 0, cache_k.stride(0), cache_k.stride(1), cache_k.stride(2), 0, ss[0], ss[1], _lib.stream()))
+  with torch.cuda.device(cache_k.device):  # the launch belongs to the cache's GPU
+    _lib.check(_lib.lib().jpt_prefill_insert_dense(
+        _lib.ptr(pk), _lib.ptr(pv), _lib.dt(pk), _lib.ptr(cache_k), _lib.ptr(cache_v), _lib.dt(cache_k),
+        _lib.ptr(k_scaler), _lib.ptr(v_scaler), slot, int(pos), int(wrap), 1, h, l, s, d, 0, pk.stride(1),
+        pk.stride(2), 0, cache_k.stride(0), cache_k.stride(1), cache_k.stride(2), 0, ss[0], ss[1], _lib.stream()))
 
 
 def insert_mask_row(cache_len, pos, current_pos, wrap, device, dtype=torch.float32):

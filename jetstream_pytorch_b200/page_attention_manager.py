@@ -184,6 +184,15 @@ class PageAttentionManager:
     dev = decode_caches[0][0].device
     upd = _lib.as_i32(update_indexes, dev).contiguous()
     n_pages = upd.numel()
+    if prefill_caches[0][0].device != dev:
+      # a prefix still on the prefill GPU (disaggregated serving): this GPU's kernel reads it over NVLink
+      from jetstream_pytorch_b200.insert import prefix_on_peer
+      prefix_on_peer(prefill_caches[0][0], dev)  # (one device pair, one ordering point for all layers)
+      with torch.cuda.device(dev):
+        return self._insert_prefill_cache_here(prefill_caches, decode_caches, upd, n_pages, decode_scales)
+    return self._insert_prefill_cache_here(prefill_caches, decode_caches, upd, n_pages, decode_scales)
+
+  def _insert_prefill_cache_here(self, prefill_caches, decode_caches, upd, n_pages, decode_scales):
     stacked = _layer_strides(prefill_caches, decode_caches, decode_scales)
     if stacked is not None:
       # the layers lie at a constant stride (views of stacked tensors): one launch for all of them

@@ -141,3 +141,51 @@ def test_one_process_drives_two_gpus():
     o, _ = ak.ragged_mha(q.to(dev), kf.to(dev), vf.to(dev), 0, start.to(dev), end.to(dev), None, None, None, None)
     assert attention_close(o, eo_bf), describe(o, eo_bf)
   assert ak.kernel_status() == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_prefix_inserted_from_the_other_gpu():
+  """Disaggregated prefill -> decode: the prefix lies on cuda:1, the caches on cuda:0; the insert
+  kernels of cuda:0 read it over NVLink.  Dense (int8, quantising, wrap and no wrap) and paged
+  (stacked int8 pools in one launch) results must equal those of a prefix on the same GPU."""
+  from jetstream_pytorch_b200.insert import insert_dense
+  from jetstream_pytorch_b200.page_attention_manager import PageAttentionManager
+
+  d0, d1 = torch.device("cuda", 0), torch.device("cuda", 1)
+  g = torch.Generator().manual_seed(901)
+  h, l, d, s, b = 8, 300, 128, 512, 4
+  pk = torch.randn(1, h, l, d, generator=g).to(torch.bfloat16)
+  pv = torch.randn(1, h, l, d, generator=g).to(torch.bfloat16)
+  for wrap, pos in ((False, 17), (True, 400)):
+    out = []
+    for src in (d0, d1):
+      ck = torch.zeros(b, h, s, d, dtype=torch.int8, device=d0)
+      cv = torch.zeros(b, h, s, d, dtype=torch.int8, device=d0)
+      ks = torch.ones(b, 1, s, 1, dtype=torch.bfloat16, device=d0)
+      vs = torch.ones(b, 1, s, 1, dtype=torch.bfloat16, device=d0)
+      insert_dense(pk.to(src), pv.to(src), ck, cv, 2, pos, wrap=wrap, k_scaler=ks, v_scaler=vs)
+      torch.cuda.synchronize(d0)
+      out.append((ck.cpu(), cv.cpu(), ks.cpu(), vs.cpu()))
+    for a, c in zip(out[0], out[1]):
+      assert torch.equal(a, c), f"wrap={wrap}: a prefix on the other GPU gave a different cache"
+    assert out[0][0][2].any()
+
+  nl, p, ps, maxp = 3, 32, 64, 8
+  spk = torch.randn(nl, 1, h, l, d, generator=g).to(torch.bfloat16)
+  spv = torch.randn(nl, 1, h, l, d, generator=g).to(torch.bfloat16)
+  out = []
+  for src in (d0, d1):
+    pam = PageAttentionManager(b, p, ps, maxp)
+    _, upd = pam.reserve_pages_insert(1, l)
+    kp = torch.zeros(nl, h, p, ps, d, dtype=torch.int8, device=d0)
+    vp = torch.zeros(nl, h, p, ps, d, dtype=torch.int8, device=d0)
+    ksp = torch.zeros(nl, 1, p, ps, 1, dtype=torch.bfloat16, device=d0)
+    vsp = torch.zeros(nl, 1, p, ps, 1, dtype=torch.bfloat16, device=d0)
+    a_k, a_v = spk.to(src), spv.to(src)
+    pam.insert_prefill_cache([(a_k[i], a_v[i]) for i in range(nl)], [(kp[i], vp[i]) for i in range(nl)], upd, None, None,
+                             decode_scales=[(ksp[i], vsp[i]) for i in range(nl)])
+    torch.cuda.synchronize(d0)
+    out.append((kp.cpu(), vp.cpu(), ksp.cpu(), vsp.cpu()))
+  for a, c in zip(out[0], out[1]):
+    assert torch.equal(a, c), "paged: a prefix on the other GPU gave different pools"
+  assert out[0][0].any()
