@@ -23,14 +23,19 @@
 // are the two splits above and the fp32 online-softmax arithmetic.
 //
 // A tile is 128 consecutive valid tokens of one (sequence, KV head) segment;
-// tiles are scheduled exactly as in the mma.sync kernel (equal contiguous
-// shares of one global tile list, pieces, last-arriver merge).  K and V rows
-// of a tile land in shared memory as 128-byte rows, 16-byte chunks XORed with
-// (row & 7): that is the canonical 128-byte-swizzle layout of the tensor core
-// for both operand roles (K-major for K, MN-major for V), so nothing is
-// rearranged.  In the softmax phase thread t owns token t of the tile (TMEM
-// lane t of S^T); in the output phase thread t owns head-dim index t (TMEM
-// lane t of O^T), which also removes the cross-warp merge of the accumulators.
+// tiles are scheduled as in the mma.sync kernel (contiguous shares of one
+// global tile list, pieces, last-arriver merge).  K and V rows of a tile land
+// in shared memory as 128-byte rows, 16-byte chunks XORed with (row & 7): that
+// is the canonical 128-byte-swizzle layout of the tensor core for both operand
+// roles (K-major for K, MN-major for V), so nothing is rearranged.  K and V
+// have rings of two slots each; where a tensor map describes the cache the
+// rows are moved by the copy engine (cp.async.bulk.tensor, one request per
+// tile and tensor, one and a half to two tiles ahead, completion counted on an
+// mbarrier per slot that only the MMA-issuing threads wait for), else by
+// 16-byte cp.async of all threads.  In the softmax phase thread t owns token t
+// of the tile (TMEM lane t of S^T); in the output phase thread t owns head-dim
+// index t (TMEM lane t of O^T), which also removes the cross-warp merge of the
+// accumulators.  The softmax phase is compiled for 8, 4 or 2 query rows.
 //
 // Fused decode update (jpt_decode_update_attend): the launch also takes the
 // step's new K/V token, which becomes the last token of its segment: the
@@ -73,7 +78,6 @@ constexpr int kCtasPerSm = 3;
 #endif
 constexpr int kPieceCostU = JPT_PIECE_COST_U;  // overhead slots charged per segment, in 128-token tiles
 constexpr long long kWaitCycles = 1000000000ll;  // about half a second: far beyond any wait of a healthy run
-constexpr int kMaxPartsU = 250;  // pieces of one segment the in-kernel merge can hold in its 16 KB of scratch
 
 struct __align__(1024) SmemU {
   uint8_t k[2][kTileU * kD];             // K ring: [slot][token][128 bytes], swizzled
@@ -276,28 +280,6 @@ __device__ __forceinline__ unsigned long long gtimer_ns() {
 #define JPT_SPAN(k) do {} while (0)
 #endif
 
-#ifdef JPT_UMMA_PHASES
-// Debug builds only: cycles thread 0 of every CTA spent per phase of the tile loop (slot 15: tiles).
-__device__ unsigned long long g_umma_phase[1024 * 32];
-#define JPT_PH_DECL unsigned long long ph_acc[32] = {}; long long ph_last = clock64();
-#define JPT_PH(k)                                          \
-  do {                                                     \
-    if (threadIdx.x == 0) {                                \
-      const long long ph_now = clock64();                  \
-      ph_acc[k] += (unsigned long long)(ph_now - ph_last); \
-      ph_last = ph_now;                                    \
-    }                                                      \
-  } while (0)
-#define JPT_PH_FLUSH()                                                            \
-  do {                                                                            \
-    if (threadIdx.x == 0 && blockIdx.x < 1024)                                    \
-      for (int z = 0; z < 32; ++z) g_umma_phase[32 * blockIdx.x + z] = ph_acc[z]; \
-  } while (0)
-#else
-#define JPT_PH_DECL
-#define JPT_PH(k) do {} while (0)
-#define JPT_PH_FLUSH() do {} while (0)
-#endif
 
 // kFused = the launch carries the decode step's new token, kRound = dense_attention's rounded
 // logit chain, kTma = the copy engine moves the K/V rows (tensor maps) instead of the threads, kR = query
@@ -515,7 +497,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   JPT_SPAN(1);
 
   const __nv_bfloat16* qbase = static_cast<const __nv_bfloat16*>(a.q);
-  JPT_PH_DECL
   // The new token of segment (b, h), whose last tile has number `seq` in this CTA: the copies of its K and V
   // rows start when the tile's K rows are requested (two iterations before they are needed) ...
   const int nt_row_bytes = nt.in_f32 ? kD * 4 : kD * 2;
@@ -786,7 +767,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       rg.first = pfirst;
       int pos, cnt;
       tile_rows(rg, a.S, pt, &pos, &cnt);
-      JPT_PH(18);
       if (tid == kWalkerThread) {
         TileMeta mt;
         mt.b = pb; mt.h = ph; mt.t = pt; mt.T = pT; mt.n = pn; mt.first = pfirst; mt.use_add = puse_add;
@@ -798,14 +778,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         sm.meta[seq & 3] = mt;
         if constexpr (kTma) request_rows(smem_u32(&sm.k[seq & 1][0]), &maps.k, smem_u32(&sm.bar_k[seq & 1]), pb, ph, pos, cnt);
       }
-      JPT_PH(19);
       if constexpr (!kTma) copy_rows(smem_u32(&sm.k[seq & 1][0]), kbase, pb, ph, pos, cnt);
       if constexpr (kFused) {
         if (pext && pt == pT - 1) stage_new_token(seq, pb, ph);  // the segment's last tile takes the new token
       }
-      JPT_PH(20);
       advance();
-      JPT_PH(21);
     } else if (tid == kWalkerThread) {
       sm.meta[seq & 3].t = -1;
     }
@@ -823,10 +800,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const int mb = sm.meta[seq & 3].b, mh = sm.meta[seq & 3].h, mtile = sm.meta[seq & 3].t;
     const int cnt = sm.meta[seq & 3].pad[0], pos = sm.meta[seq & 3].pad[1];
     if (mtile >= 0) {
-      JPT_PH(16);
       if constexpr (kTma) {
         if (tid == kVRequestThread) request_rows(smem_u32(&sm.v[seq & 1][0]), &maps.v, smem_u32(&sm.bar_v[seq & 1]), mb, mh, pos, cnt);
-        JPT_PH(17);
       } else {
         copy_rows(smem_u32(&sm.v[seq & 1][0]), vbase, mb, mh, pos, cnt);
       }
@@ -930,11 +905,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
     }
     if (tid == 0) {
-      JPT_PH(30);
       if constexpr (kTma) {
         if (!mbar_wait(smem_u32(&sm.bar_k[seq & 1]), (uint32_t)(seq >> 1) & 1u)) dead = true;
       }
-      JPT_PH(31);
       tc_fence_after();
       const uint32_t k_addr = smem_u32(&sm.k[seq & 1][0]);
 #pragma unroll
@@ -978,7 +951,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
   float alpha_prev[8], cmax_prev = 0.f;
   bool pending = false;  // O^T of the tile before has not been added yet
   for (int i = 0; mt.t >= 0; ++i) {
-    JPT_PH(11);
     float cks = scale_of(nks), cvs = scale_of(nvs);  // scales of this thread's token in tile i
     if constexpr (kFused) {
       if ((mt.pad[2] & 2) && tid == mt.pad[0] - 1) {  // the new token: its scales were just computed
@@ -1004,7 +976,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     if (!mbar_wait(bar_s, par)) dead = true;
     if (pending && !mbar_wait(bar_o, par ^ 1u)) dead = true;
     tc_fence_after();
-    JPT_PH(0);
     float xv[8];
     {
       uint32_t s[16];
@@ -1022,10 +993,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         tmem_ld16(tmem_lane, s);
         tmem_ld_wait();
       }
-      JPT_PH(1);
       issue_v(i + 1);
       issue_k(i + 2);
-      JPT_PH(2);
       const bool valid = tid < mt.pad[0];
       float mk = valid ? 0.f : -INFINITY;  // a row past the tile's tokens: finite dot product + (-inf)
       if (mt.use_add && valid)             // additive mask that is not a plain 0 / -inf range (rare)
@@ -1057,9 +1026,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
     }
     tc_fence_before();
-    JPT_PH(3);
     __syncthreads();
-    JPT_PH(4);
 
     float alpha[8];
     float cmax;
@@ -1085,7 +1052,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       const float ps = fminf(cvs * rc, 65535.f);
       softmax_rows<0, kR>(m_run, l_run, alpha, tm, xv, ps, p_base);
     }
-    JPT_PH(5);
     if constexpr (kFused) {
       if (mt.pad[2] & 2) {  // the new token's V codes into the row behind the tile's existing tokens
         if constexpr (kTma) {
@@ -1099,16 +1065,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
     cp_async_wait<3>();  // V rows of this tile (younger groups: K(i+1), V(i+1), K(i+2))
     fence_async_smem();
-    JPT_PH(12);
     __syncthreads();
-    JPT_PH(6);
 
     // ---------------- O^T = V^T Pl^T on the tensor core
     if (tid == kPvThread) {
       if constexpr (kTma) {
         if (!mbar_wait(smem_u32(&sm.bar_v[i & 1]), (uint32_t)(i >> 1) & 1u)) dead = true;
       }
-      JPT_PH(29);
       tc_fence_after();
       const uint32_t v_addr = smem_u32(&sm.v[i & 1][0]);
 #pragma unroll
@@ -1117,7 +1080,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       umma_commit(bar_o);
     }
 
-    JPT_PH(7);
     // The tile that ends a piece leaves through the epilogue below, after the next tile's S^T has been
     // issued (the tensor core and the copies keep going while the rows are written or merged).
     const bool piece_ends = last_of_share || mt.t == mt.T - 1;
@@ -1130,13 +1092,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
 
     // ---------------- the next tile: its K rows were requested an iteration ago
-    JPT_PH(28);
     if (sm.meta[(i + 1) & 3].t == 0) {
       cp_async_wait<1>();  // it starts a piece: its query rows travel with V(i+1) (younger group: K(i+2))
     } else {
       cp_async_wait<2>();  // (younger groups: V(i+1), K(i+2))
     }
-    JPT_PH(13);
     fence_async_smem();
     tc_fence_before();
     if (__syncthreads_or(dead)) {
@@ -1152,7 +1112,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
       break;
     }
-    JPT_PH(9);
     mt = sm.meta[(i + 1) & 3];
     if (mt.t >= 0) prepare(i + 1, mt, false);
     if (piece_ends) {
@@ -1168,11 +1127,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         for (int sh = 1; sh <= 16; sh <<= 1) l += __shfl_xor_sync(0xffffffffu, l, sh);
         if (lane == r) sm.red[warp][r] = l;
       }
-      JPT_PH(22);
       __syncthreads();
-      JPT_PH(23);
       add_output(par, alpha, cmax);
-      JPT_PH(24);
       float L8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, M8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < kR; ++r) {
@@ -1205,16 +1161,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         // Whoever delivers the last piece of the segment combines all of them.
         // The counter wraps back to zero on that arrival, ready for the next launch.
         // (the barrier orders the CTA's stores before thread 0's fence, which publishes them with the arrival)
-        JPT_PH(25);
         __syncthreads();
-        JPT_PH(26);
         if (tid == 0) {
           __threadfence();
           const unsigned old = atomicInc(&x.counters[cb * a.Hkv + chd], (unsigned)(cparts - 1));
           sm.flag = old == (unsigned)(cparts - 1);
         }
         __syncthreads();
-        JPT_PH(27);
         if (sm.flag) {
           __threadfence();
           merge_segment(a, x, cfirst_cta, cparts, row_base);
@@ -1222,10 +1175,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
       }
     
     }
-    JPT_PH(10);
-#ifdef JPT_UMMA_PHASES
-    ph_acc[15] += 1;
-#endif
     if (i == 0) JPT_SPAN(4);
 #ifdef JPT_UMMA_SPANS
     if (threadIdx.x == 0 && blockIdx.x < 1024) {
@@ -1234,7 +1183,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 #endif
   }
   JPT_SPAN(5);
-  JPT_PH_FLUSH();
   clear_empty_rows();
   exchange_done();
   cp_async_wait<0>();
@@ -1344,10 +1292,7 @@ int tensor_maps_for(const jpt_attn_params& p, TmaMaps* out, int* box_rows) {
 
 bool attention_umma_eligible(const jpt_attn_params& p) {
   const int R = (p.Hq / p.Hkv) * p.Tq;
-  // the merge of a segment's pieces keeps (pieces + 4) * 16 floats in its scratch; a segment spans at most
-  // its tiles + 1 CTAs
-  const int max_tiles = (p.S + kTileU - 1) / kTileU + 1;  // (+1: a ring that wraps is cut run by run)
-  return attention_mma_eligible(p) && p.kv_dtype == JPT_INT8 && R <= 8 && max_tiles + 1 <= kMaxPartsU;
+  return attention_mma_eligible(p) && p.kv_dtype == JPT_INT8 && R <= 8;
 }
 
 int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStream_t st, const NewTokenArgs* nt_in) {
@@ -1451,12 +1396,6 @@ int launch_attention_umma(const jpt_attn_params& p, const AttnArgs& a, cudaStrea
 }
 
 }  // namespace jpt
-
-#ifdef JPT_UMMA_PHASES
-extern "C" int jpt_debug_umma_phases(unsigned long long* out_host, int n_ctas) {
-  return (int)cudaMemcpyFromSymbol(out_host, jpt::g_umma_phase, sizeof(unsigned long long) * 32 * n_ctas);
-}
-#endif
 
 #ifdef JPT_UMMA_SPANS
 extern "C" int jpt_debug_umma_spans(unsigned long long* out_host, int n_ctas) {
