@@ -557,6 +557,43 @@ def extra_insert_burst(dev, peak, reps, nl=32):
           "inserts_per_s": n_ins / (ms * 1e-3)}
 
 
+def extra_w8a16_linear(dev, peak, reps, eager=False):
+  """The weight stream of a decode step: the weight-only int8 linear layer at the
+  bench model's projection shapes (Llama-2-70B, batch 96), each over rotating
+  weight sets larger than L2, replayed as one CUDA graph."""
+  from jetstream_pytorch_b200.layers import WeightOnlyPerChannelQuantizedLinear
+
+  out = {}
+  gen = torch.Generator(device=dev).manual_seed(1006)
+  shapes = (("wo_8192x8192", 8192, 8192), ("w_up_8192x28672", 8192, 28672), ("w_down_28672x8192", 28672, 8192))
+  for name, k, n in shapes[:1] if eager else shapes:  # (eager: the command line for profiler captures, one shape)
+    sets = max(3, int(300e6 // (k * n)) + 1)
+    layers = []
+    for _ in range(sets):
+      lin = WeightOnlyPerChannelQuantizedLinear(k, n, device=dev)
+      lin._load_quantized_weights(torch.randint(-127, 128, (n, k), generator=gen, dtype=torch.int8, device=dev),
+                                  torch.rand(n, generator=gen, device=dev) * 0.01)
+      layers.append(lin)
+    x = torch.randn((B, k), generator=gen, device=dev).to(torch.bfloat16)
+
+    def run_all():
+      for lin in layers:
+        lin(x)
+
+    if eager:
+      run_all()
+      us = time_replays(run_all, reps) * 1e3 / sets
+    else:
+      us = time_replays(graph_of(run_all).replay, reps) * 1e3 / sets
+    status = max(lin.kernel_status() for lin in layers)
+    nbytes = n * k + B * k * 2 + B * n * 2 + n * 2  # int8 weights, bf16 activations in and out, bf16 scales
+    out[name] = kernel_entry(us, nbytes, peak, kernel_status=status, rotating_weight_sets=sets)
+    del layers
+    torch.cuda.empty_cache()
+  out["workload"] = "y = bf16(bf16(x W^T) * scale), x bf16 [96, K], W int8 [N, K]: level split + tcgen05 GEMM launches"
+  return out
+
+
 # ---------------------------------------------------------------------------
 # CUDA arm
 # ---------------------------------------------------------------------------
@@ -591,6 +628,9 @@ def run_cuda(args):
     return
   if args.only == "peer-insert":
     print(json.dumps({"only": "peer-insert", **peer_insert(args.steps, nl=min(32, nl))}), flush=True)
+    return
+  if args.only == "linear":
+    print(json.dumps({"only": "linear", **extra_w8a16_linear(dev, peak, args.steps, eager=True)}), flush=True)
     return
 
   # ---- device-resident state: every layer owns its cache (>> L2 in total).  Layer 0 comes from
@@ -980,6 +1020,8 @@ def run_cuda(args):
       torch.cuda.empty_cache()
       kernels["prefill_insert_burst"] = extra_insert_burst(dev, peak, max(2, xreps // 2))
       torch.cuda.empty_cache()
+      kernels["w8a16_linear"] = extra_w8a16_linear(dev, peak, xreps)
+      torch.cuda.empty_cache()
     except Exception as e:  # pylint: disable=broad-except
       kernels["error"] = f"{type(e).__name__}: {e}"
       torch.cuda.synchronize()
@@ -1016,7 +1058,7 @@ def main():
   ap.add_argument("--no-extras", action="store_true", help="skip the other workloads' kernels (N = 1 runs them by default)")
   ap.add_argument("--amax-exchange", choices=["peers", "nccl"], default="peers",
                   help="N > 1: how the per-token amax is max-reduced over the ranks")
-  ap.add_argument("--only", choices=["attention", "append", "insert", "peer-insert"], default=None,
+  ap.add_argument("--only", choices=["attention", "append", "insert", "peer-insert", "linear"], default=None,
                   help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
   ap.add_argument("--kv", choices=["int8", "bf16"], default="int8", help="with --only attention: cache dtype")
   ap.add_argument("--attn-kernel", choices=["auto", "mma"], default="auto",

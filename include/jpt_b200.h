@@ -443,6 +443,28 @@ int jpt_merge_partials(const void* o1, const float* m1, const float* l1,
                        int in_dtype, void* o, int out_dtype, int64_t rows, int D,
                        void* stream);
 
+/*
+ * Weight-only int8 linear layer for decode batches (next to the KV path in a
+ * decode step: the weights are the other stream of bytes).  Replaces
+ * WeightOnlyPerChannelQuantizedLinear.forward with symmetric weights and
+ * without activation quantisation, jetstream_pt/layers.py:141-166:
+ *   y = bf16(bf16(x @ W^T) * w_scale)
+ *   x        [M, K] bf16, 1 <= M <= 128, K a multiple of 128, 16-byte aligned
+ *   w        [N, K] int8 (one row per output channel), 16-byte aligned
+ *   w_scale  [N] bf16
+ *   y        [M, N] bf16 out
+ *   workspace  jpt_w8a16_linear_workspace_bytes(M, N, K) bytes, 256-byte
+ *            aligned; its first int is 0 after the call, or 1 if a bounded wait
+ *            inside the kernel gave up (the output is then invalid)
+ * The int8 weights go to the tensor core as they are (tcgen05 integer MMAs);
+ * the bf16 activations are split into two int8 levels (exact to 2^-16 of a
+ * row's amax), so the sums are exact integers.
+ */
+size_t jpt_w8a16_linear_workspace_bytes(int M, int N, int K);
+int jpt_w8a16_linear(const void* x, const void* w, const void* w_scale, void* y,
+                     int M, int N, int K, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

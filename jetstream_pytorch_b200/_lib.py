@@ -91,6 +91,8 @@ _SIGNATURES = {
     "jpt_prefill_insert_paged": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                          c_void_p, c_void_p] + [c_int] * 7 + [c_i64] * 5 + [c_void_p]),
     "jpt_enable_peer_access": (c_int, [c_int, c_int]),
+    "jpt_w8a16_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "jpt_w8a16_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jpt_quantize_tokens": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "jpt_flash_decode": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
     "jpt_flash_decode_static": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),

@@ -18,6 +18,7 @@ SOURCES = [
     "attention_generic.cu",
     "attention_mma.cu",
     "attention_umma.cu",
+    "w8a16_linear.cu",
 ]
 
 NVCC_FLAGS = [

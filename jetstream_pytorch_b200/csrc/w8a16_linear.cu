@@ -1,0 +1,490 @@
+// Weight-only int8 linear layer for decode batches: y[m, n] = (sum_k x[m, k] W[n, k]) * scale[n]
+// with x bf16 [M <= 128, K], W int8 [N, K] (one scale per output channel), y bf16 [M, N]
+// (WeightOnlyPerChannelQuantizedLinear.forward, symmetric weights, no activation quantisation:
+// jetstream_pt/layers.py:141-166).
+//
+// A decode step streams every weight byte once, so the kernel is bound by the HBM read of W.  The
+// int8 weights go from HBM to shared memory by the copy engine and from there straight into the
+// tensor core: the contraction runs as tcgen05 integer MMAs with the weights as the M = 128 operand
+// and the activations as the N operand.  The bf16 activations become 8-bit without losing their
+// precision by the same two-level split the attention kernel uses for its queries: a row x of the
+// batch is s (h + l / 254) with s = amax|x| / 127 and h, l signed bytes (error 2^-16 of the row's
+// amax), so the N operand holds 2 M rows (all h rows, then all l rows) and
+//   y[m, n] = scale[n] * s_m * (S_h[n, m] + S_l[n, m] / 254)
+// with exact int32 sums S_h, S_l in tensor memory.  Nothing is converted in registers.
+//
+// Launches: (1) split of the activations into levels (one CTA per row of x), (2) the GEMM: one CTA
+// per 256 output channels and K split; the CTAs of a tile's K splits form a thread-block cluster.
+// 128 threads: thread 0 requests the tiles of a 3-stage ring of 128-byte-swizzled [256 x 128 B] weight
+// and [2 M x 128 B] activation tiles, thread 32 issues the MMAs, two per K step of 32 bytes, one for
+// each half of the channels, so that an activation tile read from L2 serves 256 channels, and frees
+// the stages through tcgen05.commit.  Epilogue: all four warps read the accumulators out of tensor
+// memory; the rows of the batch are dealt out to the CTAs of the cluster in groups of eight, every
+// CTA stores its partial sums of a group into the shared memory of the group's owner (the ring is
+// free by then), and the owner adds the partials in the order of the splits, rounds to bf16,
+// multiplies by the channel's scale and rounds again, as the reference's two bf16 operations do.
+// No partial result goes through global memory.  Every wait on data is bounded; a CTA that gives up
+// raises the status word, still meets its cluster at the two cluster barriers, and returns.
+#include <cuda.h>
+#include <string.h>
+
+#include <mutex>
+#include <type_traits>
+#include <vector>
+
+#include "common.cuh"
+
+namespace jpt {
+namespace {
+
+constexpr int kTileN = 256;      // output channels per CTA: two accumulators of 128 TMEM lanes
+constexpr int kTileK = 128;      // int8 elements per stage and row: one 128-byte swizzle atom
+constexpr int kStages = 3;
+constexpr int kMaxM = 128;       // rows of x: the N operand holds 2 * M rows (<= 256)
+constexpr int kTmemColsL = 512;  // two accumulators [128 lanes x 2 M columns]
+constexpr int kThreadsL = 128;
+constexpr int kMaxSplit = 8;     // K splits of a tile = CTAs of a cluster (the portable limit)
+constexpr long long kWaitCyclesL = 1000000000ll;
+
+struct __align__(1024) SmemL {
+  uint8_t w[kStages][kTileN * kTileK];        // weight tiles, swizzled
+  uint8_t x[kStages][2 * kMaxM * kTileK];     // activation level tiles (only 2 M rows are filled)
+  uint64_t full[kStages], empty[kStages], done;
+  float xs[kMaxM];  // s_m / 254 of the rows of x
+  uint32_t tmem_base;
+};
+
+struct LinearMaps {
+  CUtensorMap w, x;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait for the phase with the given parity; false when it gave up.
+__device__ __noinline__ bool mbar_wait_l(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {
+      if (mbar_try(bar, parity)) return true;
+    }
+    if (clock64() - t0 > kWaitCyclesL) return false;
+  }
+}
+__device__ __forceinline__ uint64_t desc_k_major_128b(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);  // start address
+  d |= (uint64_t)(1024 >> 4) << 16;       // leading byte offset (one swizzle atom)
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                 // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Thread-block cluster: barrier over all its threads (with release / acquire of shared-memory stores),
+// the address of a shared-memory location in the CTA of another rank, a store there.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t remote_smem(uint32_t local_addr, int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  // (no memory clobber: the cluster barriers order these stores, and the loads around them must stay free to move)
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v));
+}
+
+// 32 consecutive accumulator columns of this thread's lane
+__device__ __forceinline__ void tmem_ld_32(uint32_t addr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(addr));
+}
+
+// ---------------------------------------------------------------- (1) activation levels
+// x [M, K] bf16 -> levels [2 Mp, K] int8 (rows 0 .. M-1: h, rows Mp .. Mp+M-1: l, the others zero)
+// and xs[m] = s_m / 254.
+__global__ void __launch_bounds__(256) x_levels_kernel(const __nv_bfloat16* x, int8_t* lev, float* xs, int* status, int M,
+                                                       int Mp, int K) {
+  __shared__ float red[33];
+  const int m = blockIdx.x, tid = threadIdx.x;  // one CTA per row of the padded batch
+  grid_dependency_trigger();
+  if (m == 0 && tid == 0) *status = 0;
+  uint2* hrow = reinterpret_cast<uint2*>(lev + (int64_t)m * K);
+  uint2* lrow = reinterpret_cast<uint2*>(lev + (int64_t)(Mp + m) * K);
+  const int nvec = K / 8;  // eight elements per step: 16 bytes in, 8 + 8 bytes out
+  if (m >= M) {  // padding rows of the level matrix
+    for (int v = tid; v < nvec; v += 256) hrow[v] = lrow[v] = make_uint2(0u, 0u);
+    return;
+  }
+  const uint4* row = reinterpret_cast<const uint4*>(x + (int64_t)m * K);
+  constexpr int kHeld = 8;  // steps of a thread kept in registers between the two passes (rows of up to 16384 elements)
+  uint4 held[kHeld];
+  __nv_bfloat162 mx = __float2bfloat162_rn(0.f);
+  auto fold = [&](const uint4& r) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mx = __hmax2(mx, __habs2(h2[j]));
+  };
+#pragma unroll
+  for (int i = 0; i < kHeld; ++i) {
+    const int v = tid + 256 * i;
+    held[i] = v < nvec ? __ldg(row + v) : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int i = 0; i < kHeld; ++i) fold(held[i]);
+  for (int v = tid + 256 * kHeld; v < nvec; v += 256) fold(__ldg(row + v));
+  const float amax = block_max(fmaxf(__low2float(mx), __high2float(mx)), red);
+  const float inv = amax > 0.f ? 127.f / amax : 0.f;
+  auto split_levels = [&](const uint4& r, int v) {
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&r);
+    uint32_t hb[2] = {0u, 0u}, lb[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float t = __bfloat162float(e[j]) * inv;
+      const float h = rintf(t);
+      const float l = rintf((t - h) * 254.f);
+      hb[j >> 2] |= ((uint32_t)(int)h & 0xffu) << (8 * (j & 3));
+      lb[j >> 2] |= ((uint32_t)(int)l & 0xffu) << (8 * (j & 3));
+    }
+    hrow[v] = make_uint2(hb[0], hb[1]);
+    lrow[v] = make_uint2(lb[0], lb[1]);
+  };
+#pragma unroll
+  for (int i = 0; i < kHeld; ++i) {
+    const int v = tid + 256 * i;
+    if (v < nvec) split_levels(held[i], v);
+  }
+  for (int v = tid + 256 * kHeld; v < nvec; v += 256) split_levels(__ldg(row + v), v);
+  if (tid == 0) xs[m] = amax * (1.f / 127.f) * (1.f / 254.f);
+}
+
+// ---------------------------------------------------------------- (2) the GEMM
+// grid (ceil(N / 256), ksplit), clusters of (1, ksplit): the rank of a CTA in its cluster is its K split.
+__global__ void __launch_bounds__(kThreadsL, 1)
+    w8a16_gemm_kernel(const __grid_constant__ LinearMaps maps, const float* xs, const __nv_bfloat16* scale, __nv_bfloat16* y,
+                      int M, int Mp, int N, int K, int k_per_split, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  SmemL& sm = *reinterpret_cast<SmemL*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if ((smem_addr(smem_raw) & 1023u) != 0u) {
+    grid_dependency_wait();  // (the launch before this one clears the status word)
+    if (tid == 0) atomicExch(status, 2);
+    return;
+  }
+  const int n0 = blockIdx.x * kTileN, split = blockIdx.y;
+  const int k_begin = split * k_per_split, iters = k_per_split / kTileK;
+  const int n_mma = 2 * Mp;  // columns of the accumulator (a multiple of 16)
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&sm.full[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&sm.empty[s])));
+    }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&sm.done)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.x)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sm.tmem_base)),
+                 "r"((uint32_t)kTmemColsL)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  sm.xs[tid] = tid < M ? xs[tid] : 0.f;
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = sm.tmem_base;
+  bool dead = false;
+
+  if (tid == 0) {
+    // ---- producer: tiles of stage s are requested when the MMAs that read its previous contents are done
+    // Every CTA of a K split reads the same activation tiles: each starts at another K step (the sums are
+    // exact integers, their order is free), so that the CTAs do not ask the same L2 lines at the same time.
+    const int rot = (int)(blockIdx.x % (unsigned)iters);
+    const uint32_t bytes = (uint32_t)(kTileN * kTileK + n_mma * kTileK);
+    for (int it = 0; it < iters && !dead; ++it) {
+      const int s = it % kStages;
+      if (it >= kStages && !mbar_wait_l(smem_addr(&sm.empty[s]), (uint32_t)((it / kStages) - 1) & 1u)) dead = true;
+      if (dead) break;
+      const uint32_t bar = smem_addr(&sm.full[s]);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+      const int kt = it + rot < iters ? it + rot : it + rot - iters;
+      tma_load_2d(smem_addr(&sm.w[s][0]), &maps.w, k_begin + kt * kTileK, n0, bar);
+      tma_load_2d(smem_addr(&sm.x[s][0]), &maps.x, k_begin + kt * kTileK, 0, bar);
+    }
+  } else if (tid == 32) {
+    // ---- MMA issue: D_half[128 n x 2 Mp] += W_tile[half][128 x 128 B] . Xl_tile^T, four K steps of 32 bytes per stage
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)n_mma >> 3) << 17) | ((128u >> 4) << 24);
+    for (int it = 0; it < iters && !dead; ++it) {
+      const int s = it % kStages;
+      if (!mbar_wait_l(smem_addr(&sm.full[s]), (uint32_t)(it / kStages) & 1u)) {
+        dead = true;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t wa = smem_addr(&sm.w[s][0]), xa = smem_addr(&sm.x[s][0]);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint64_t bd = desc_k_major_128b(xa + 32 * ks);
+        const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint64_t ad = desc_k_major_128b(wa + half * (128 * kTileK) + 32 * ks);
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem + (uint32_t)(half * n_mma)),
+              "l"(ad), "l"(bd), "r"(idesc), "r"(acc)
+              : "memory");
+        }
+      }
+      // the stage is free again when these MMAs have read it
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&sm.empty[s]))
+                   : "memory");
+    }
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&sm.done))
+                 : "memory");
+  }
+  __syncwarp();
+  // ---- epilogue: lane n of accumulator `half` belongs to thread n (output channel n0 + 128 half + n)
+  const int csize = (int)gridDim.y;  // CTAs in the cluster = K splits
+  const int groups = Mp / 8;         // groups of eight rows of the batch; group j belongs to rank j % csize
+  const int owned = (groups + csize - 1) / csize;
+  // landing area in the ring: [source rank][owned group][half][row of the group][thread] fp32
+  float* land = reinterpret_cast<float*>(smem_raw);
+  const bool ok = mbar_wait_l(smem_addr(&sm.done), 0u);
+  const bool bad = __syncthreads_or(dead || !ok) != 0;
+  if (bad && tid == 0) atomicExch(status, 1);  // (only if the copy engine or the tensor core stopped answering)
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  cluster_sync();  // every ring of the cluster has been read to the end: the landing areas are free
+  if (!bad) {
+    for (int m0 = 0; m0 < Mp; m0 += 32) {
+      uint32_t h[2][32], l[2][32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(half * n_mma);
+        tmem_ld_32(lane_addr + (uint32_t)m0, h[half]);
+        tmem_ld_32(lane_addr + (uint32_t)(Mp + m0), l[half]);
+      }
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      float xr[32];  // (all loads before the stores: the compiler cannot move them across)
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) xr[jj] = sm.xs[(m0 + jj) & (kMaxM - 1)];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = m0 / 8 + c;
+        if (j < groups) {
+          const int owner = j % csize, q = j / csize;
+          const uint32_t base = remote_smem(smem_addr(land + ((((int64_t)split * owned + q) * 2) * 8) * kThreadsL + tid), owner);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              const int jj = 8 * c + r;
+              const float v = fmaf((float)(int)h[half][jj], 254.f, (float)(int)l[half][jj]) * xr[jj];
+              st_cluster_f32(base + (uint32_t)((half * 8 + r) * kThreadsL * 4), v);
+            }
+          }
+        }
+      }
+    }
+  }
+  float sc[2];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int n = n0 + half * 128 + tid;
+    sc[half] = n < N ? __bfloat162float(scale[n]) : 0.f;
+  }
+  cluster_sync();  // all partial sums have landed
+  if (!bad) {
+    auto reduce = [&](auto cs_tag) {
+      constexpr int kCs = decltype(cs_tag)::value;
+      for (int q = 0; q < owned; ++q) {
+        const int j = q * kCs + split;
+        if (j >= groups) break;
+        float acc[2][8];  // (sixteen independent chains; all loads before the stores)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int r = 0; r < 8; ++r) acc[half][r] = land[(((0 * owned + q) * 2 + half) * 8 + r) * kThreadsL + tid];
+        }
+#pragma unroll
+        for (int src = 1; src < kCs; ++src) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) acc[half][r] += land[(((src * owned + q) * 2 + half) * 8 + r) * kThreadsL + tid];
+          }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int n = n0 + half * 128 + tid;
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int m = 8 * j + r;
+            const float dot = __bfloat162float(__float2bfloat16_rn(acc[half][r]));            // F.linear's bf16 result
+            if (m < M && n < N) y[(int64_t)m * N + n] = __float2bfloat16_rn(dot * sc[half]);  // * weight_scaler
+          }
+        }
+      }
+    };
+    switch (csize) {
+      case 1: reduce(std::integral_constant<int, 1>{}); break;
+      case 2: reduce(std::integral_constant<int, 2>{}); break;
+      case 4: reduce(std::integral_constant<int, 4>{}); break;
+      default: reduce(std::integral_constant<int, 8>{}); break;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemColsL) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+// rows x K bytes, row-major; boxes of box_rows x 128 bytes with the 128-byte swizzle
+bool encode_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t str[1] = {(cuuint64_t)K};
+  const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, str, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int split_for(int N, int K) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  const int tiles = (N + kTileN - 1) / kTileN, k_tiles = K / kTileK;
+  // The K splits of a tile are the CTAs of one cluster (1, 2, 4 or 8).  The split with the shortest
+  // estimated run is taken: CTAs run in waves of one per SM; a CTA costs about 8 us of set-up, first
+  // fetch and epilogue plus 0.6 us per K step (measured on B200 for 96 rows).
+  int split = 1;
+  float best = 0.f;
+  for (int c = 1; c <= kMaxSplit && c <= k_tiles; c *= 2) {
+    if (k_tiles % c) break;
+    const int waves = (tiles * c + sms - 1) / sms;
+    const float cost = (float)waves * (8.f + 0.6f * (float)(k_tiles / c));
+    if (c == 1 || cost < best) best = cost, split = c;
+  }
+  return split;
+}
+
+}  // namespace
+}  // namespace jpt
+
+using namespace jpt;
+
+extern "C" size_t jpt_w8a16_linear_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int Mp = (M + 7) / 8 * 8;
+  const size_t levels = ((size_t)2 * Mp * K + 255) / 256 * 256;
+  const size_t xs = 1024;
+  (void)N;
+  return 256 + levels + xs;
+}
+
+extern "C" int jpt_w8a16_linear(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  JPT_REQUIRE(x && w && w_scale && y, JPT_EINVAL, "w8a16_linear: null tensor");
+  JPT_REQUIRE(M >= 1 && M <= kMaxM, JPT_EINVAL, "w8a16_linear: M = %d rows, the kernel takes 1 .. %d (decode batches)", M, kMaxM);
+  JPT_REQUIRE(N >= 1 && K >= kTileK && K % kTileK == 0, JPT_EINVAL, "w8a16_linear: K = %d must be a multiple of %d", K, kTileK);
+  JPT_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 2), JPT_EALIGN, "w8a16_linear: x and w must be 16-byte aligned");
+  const size_t need = jpt_w8a16_linear_workspace_bytes(M, N, K);
+  JPT_REQUIRE(workspace && workspace_bytes >= need, JPT_EWORKSPACE, "w8a16_linear: workspace of %zu bytes needed, %zu given", need,
+              workspace_bytes);
+  JPT_REQUIRE(aligned(workspace, 256), JPT_EALIGN, "w8a16_linear: workspace must be 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Mp = (M + 7) / 8 * 8;
+  char* ws = static_cast<char*>(workspace);
+  int* status = reinterpret_cast<int*>(ws);  // first word: 0, or the code of a CTA that gave up
+  int8_t* lev = reinterpret_cast<int8_t*>(ws + 256);
+  const size_t levels = ((size_t)2 * Mp * K + 255) / 256 * 256;
+  float* xs = reinterpret_cast<float*>(ws + 256 + levels);
+  const int ksplit = split_for(N, K);
+
+  static std::mutex mu;
+  LinearMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    JPT_REQUIRE(encode_2d(&maps.w, w, N, K, kTileN) && encode_2d(&maps.x, lev, 2 * Mp, K, 2 * Mp), JPT_EINVAL,
+                "w8a16_linear: the tensors cannot be described by a tensor map");
+  }
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    const cudaError_t e = cudaFuncSetAttribute(w8a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmemL));
+    if (e != cudaSuccess) return fail((int)e, "w8a16_linear: configuring the kernel: %s", cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  // (the level kernel also clears the status word and the padding rows of the level matrix; the two launches after it
+  // may start while their predecessor drains and wait for its results on the device)
+  x_levels_kernel<<<Mp, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), lev, xs, status, M, Mp, K);
+  if (int rc = check_launch("x_levels_kernel")) return rc;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((N + kTileN - 1) / kTileN, ksplit);
+  cfg.blockDim = dim3(kThreadsL);
+  cfg.dynamicSmemBytes = sizeof(SmemL);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = ksplit;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) capturing = cudaStreamCaptureStatusNone;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl_enabled() && capturing == cudaStreamCaptureStatusNone) ? 2 : 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, w8a16_gemm_kernel, maps, static_cast<const float*>(xs),
+                                           static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(y), M, Mp, N, K,
+                                           K / ksplit, status);
+  if (e != cudaSuccess) return fail((int)e, "w8a16_gemm_kernel: %s", cudaGetErrorString(e));
+  return 0;
+}

@@ -14,10 +14,17 @@ import torch
 
 @dataclasses.dataclass
 class QuantizationConfig:
-  """jetstream_pt/environment.py:31-40 (only the KV flag matters here)."""
+  """jetstream_pt/environment.py:31-40."""
 
   enable_weight_quantization: bool = False
+  num_bits_weight: int = 8
+  is_blockwise_weight: bool = False
+  block_size_weight: int = 128
+  is_symmetric_weight: bool = True
+
+  enable_activation_quantization: bool = False
   enable_kv_quantization: bool = False
+  exclude_layers: object = None
 
 
 @dataclasses.dataclass

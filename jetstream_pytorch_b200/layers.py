@@ -2,13 +2,18 @@
 the branch structure, call order and return shapes of the reference's
 `AttentionKernel` and `Int8KVAttentionKernel` (jetstream_pt/layers.py:382-550,
 553-718).  They exist so the cache objects and attention entry points can be
-exercised exactly the way the reference's model code drives them; projections,
-RoPE and the rest of `layers.Attention` stay outside this package.
+exercised exactly the way the reference's model code drives them; RoPE and the
+rest of `layers.Attention` stay outside this package.
+
+`WeightOnlyPerChannelQuantizedLinear` (jetstream_pt/layers.py:69-166) is the
+other byte stream of a decode step: the int8 weights of the projections.
 """
 
 import torch
 
+from jetstream_pytorch_b200 import _lib
 from jetstream_pytorch_b200 import attention_kernel as ak
+from jetstream_pytorch_b200.environment import QuantizationConfig
 
 
 class _AttentionKernelBase:
@@ -120,3 +125,80 @@ class Int8KVAttentionKernel(_AttentionKernelBase):
     new_output, (new_max, new_denom) = self._attend(xq, new_key, new_value, new_k_scaler, new_v_scaler, None,
                                                     *args)
     return self._merge(existing_output, existing_max, existing_denom, new_output, new_max, new_denom)
+
+
+class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
+  """layers.py:69-166 for decode batches: int8 weights [out, in] with one bf16
+  scale per output channel, bf16 activations, result
+  bf16(bf16(inputs @ weight^T) * weight_scaler).
+
+  Built: 8-bit symmetric weights, no activation quantisation, up to 128 rows of
+  activations per call (a decode batch) and `in_features` a multiple of 128.
+  Anything else raises; there is no eager path."""
+
+  MAX_ROWS = 128
+
+  def __init__(self, in_features, out_features, bias=False, device=None, quant_config=None):
+    super().__init__()
+    quant_config = QuantizationConfig() if quant_config is None else quant_config
+    assert not bias, "Quantized Linear doesn't support bias."
+    if not getattr(quant_config, "is_symmetric_weight", True):
+      raise NotImplementedError("asymmetric weights are not provided")
+    if getattr(quant_config, "enable_activation_quantization", False):
+      raise NotImplementedError("activation quantisation is not provided")
+    if getattr(quant_config, "num_bits_weight", 8) != 8:
+      raise NotImplementedError("only 8-bit weights are provided")
+    if in_features % 128:
+      raise NotImplementedError(f"in_features = {in_features} must be a multiple of 128")
+    self.in_features = in_features
+    self.out_features = out_features
+    self.register_buffer("weight", torch.ones((out_features, in_features), dtype=torch.int8, device=device))
+    self.register_buffer("weight_scaler", torch.ones((out_features,), dtype=torch.bfloat16, device=device))
+    self.register_buffer("zero_point", None)
+    self.is_symmetric_weight = True
+    self.n_bit = 8
+    self.quantize_activation = False
+    self._workspace = None
+
+  def _load_quantized_weights(self, w_q, scale, zp=None):
+    """layers.py:114-120 with `load_q_weight_helper` (quantize.py:86-93)."""
+    if zp is not None:
+      raise NotImplementedError("asymmetric weights are not provided")
+    dev = self.weight.device
+    self.weight = w_q.to(torch.int8).to(dev).contiguous()
+    self.weight_scaler = scale.reshape(self.out_features).to(torch.bfloat16).to(dev).contiguous()
+
+  def quantize_weight_from_nn_linear(self, weight):
+    """layers.py:122-133: per-channel symmetric quantisation of a float weight
+    (quantize.py:58-76).  Offline work, plain torch."""
+    assert weight.dim() == 2, "Expect 2D weight from torch.nn.Linear."
+    assert weight.shape == (self.out_features, self.in_features), (
+        f"Got unexpected weight of shape {weight.shape}, expected weight shape "
+        f"({self.out_features}, {self.in_features}).")
+    max_val = weight.abs().amax(dim=1, keepdim=True).clamp(min=1e-5)
+    scales = max_val / 127
+    w_q = torch.clamp(torch.round(weight * (1.0 / scales)), -128, 127).to(torch.int8)
+    self._load_quantized_weights(w_q, scales.squeeze(-1))
+
+  def kernel_status(self):
+    """0, or 1 if a bounded wait inside the last launch gave up (synchronises)."""
+    return 0 if self._workspace is None else int(self._workspace[:4].view(torch.int32).item())
+
+  def forward(self, inputs):
+    if inputs.dtype != torch.bfloat16:
+      raise NotImplementedError(f"activations must be bfloat16, got {inputs.dtype}")
+    k, n = self.in_features, self.out_features
+    x = inputs.reshape(-1, k)
+    m = x.shape[0]
+    if not 1 <= m <= self.MAX_ROWS:
+      raise NotImplementedError(f"{m} rows of activations: the kernel takes 1 .. {self.MAX_ROWS} (decode batches)")
+    if not x.is_contiguous():
+      x = x.contiguous()
+    lib = _lib.lib()
+    need = lib.jpt_w8a16_linear_workspace_bytes(m, n, k)
+    if self._workspace is None or self._workspace.numel() < need or self._workspace.device != x.device:
+      self._workspace = torch.empty((need,), dtype=torch.uint8, device=x.device)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.jpt_w8a16_linear(_lib.ptr(x), _lib.ptr(self.weight), _lib.ptr(self.weight_scaler), _lib.ptr(y), m, n,
+                                    k, _lib.ptr(self._workspace), self._workspace.numel(), _lib.stream()))
+    return y.reshape(*inputs.shape[:-1], n)

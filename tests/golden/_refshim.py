@@ -523,3 +523,37 @@ def import_reference_engine(reference_root):
         setattr(sys.modules[parent], child, sys.modules[name])
   sys.modules["flax"].struct = types.SimpleNamespace(dataclass=dataclasses.dataclass)
   return importlib.import_module("jetstream_pt.engine")
+
+
+def import_reference_layers(reference_root):
+  """Returns the reference's `jetstream_pt.layers` module (for its quantised
+  linear layer).  `jetstream_pt.environment` cannot be imported under Python
+  3.12 (a dataclass field with an unhashable dataclass default), so the one name
+  layers.py takes from it, the `QuantizationConfig` record, is provided here with
+  the same fields and defaults (environment.py:31-40); absl and model_base are
+  placeholders."""
+  import dataclasses
+  import importlib
+
+  import_reference(reference_root)
+  for name in ("absl", "absl.flags", "jetstream_pt.model_base"):
+    if name not in sys.modules:
+      sys.modules[name] = _AnyModule(name)
+
+  @dataclasses.dataclass(frozen=True)
+  class QuantizationConfig:
+    enable_weight_quantization: bool = False
+    num_bits_weight: int = 8
+    is_blockwise_weight: bool = False
+    block_size_weight: int = 128
+    is_symmetric_weight: bool = True
+    enable_activation_quantization: bool = False
+    enable_kv_quantization: bool = False
+    exclude_layers: object = None
+
+  env = sys.modules.get("jetstream_pt.environment")
+  if env is None or isinstance(env, _AnyModule):
+    env = types.ModuleType("jetstream_pt.environment")
+    sys.modules["jetstream_pt.environment"] = env
+  env.QuantizationConfig = QuantizationConfig
+  return importlib.import_module("jetstream_pt.layers")

@@ -456,6 +456,41 @@ def gen_engine_step(eng):
   save("engine_step", out)
 
 
+def gen_linear(layers):
+  """`WeightOnlyPerChannelQuantizedLinear` (layers.py:69-166): the reference's
+  own weight quantiser and forward.  Its `F.linear(bf16, int8)` exists only under
+  torch_xla2, where the int8 weight is promoted to bfloat16 (jax type promotion);
+  on CPU torch that one call is given the promoted weight, everything else runs
+  as written."""
+  real_linear = layers.F.linear
+
+  def promoted_linear(inputs, weight, bias=None):
+    return real_linear(inputs, weight.to(inputs.dtype) if weight.dtype == torch.int8 else weight, bias)
+
+  g = torch.Generator().manual_seed(11)
+  out = {}
+  for tag, (m, k, n) in (("small", (5, 256, 192)), ("batch", (96, 1024, 320))):
+    lin = layers.WeightOnlyPerChannelQuantizedLinear(k, n)
+    w = torch.randn(n, k, generator=g) * 0.05
+    w[3] = 0  # an all-zero channel: the EPS clamp of the scale
+    w[7] *= 1e-4
+    lin.quantize_weight_from_nn_linear(w)
+    x = randn(g, 1, m, k)
+    x[0, 1] = 0
+    x[0, 2] *= 37.0
+    layers.F.linear = promoted_linear
+    try:
+      y = lin(x)
+    finally:
+      layers.F.linear = real_linear
+    assert y.dtype == torch.bfloat16 and lin.weight.dtype == torch.int8 and lin.weight_scaler.dtype == torch.bfloat16
+    if tag == "small":
+      out[f"{tag}_w"] = w  # (the float weight only where the quantiser is pinned: it is the bulk of the file)
+    out.update({f"{tag}_x": x, f"{tag}_weight": lin.weight, f"{tag}_weight_scaler": lin.weight_scaler,
+                f"{tag}_y": y})
+  save("linear", out)
+
+
 def functools_partial(fn, first):
   return lambda *a: fn(first, *a)
 
@@ -474,6 +509,7 @@ def main():
   eng = _refshim.import_reference_engine(ref)
   gen_engine_insert(eng, pam)
   gen_engine_step(eng)
+  gen_linear(_refshim.import_reference_layers(ref))
   print("golden fixtures written")
 
 

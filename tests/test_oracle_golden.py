@@ -301,3 +301,32 @@ def test_insert_restatements():
   assert not c3[0].any() and not c3[2].any()
   m = oi.insert_mask_row(8, 6, 2, wrap=True)
   assert m.tolist() == [0, 0] + [float("-inf")] * 4 + [0, 0]
+
+
+def test_w8a16_linear_against_the_reference_layer():
+  """`linear.npz`: the reference's own `quantize_weight_from_nn_linear` (bit for
+  bit) and `forward` (within `w8a16_tolerance`, more than 99 % of the outputs
+  identical: the oracle rounds the exact dot product, the reference a float32
+  accumulation)."""
+  from oracle import linear as ol
+
+  g = load("linear")
+  codes, scale = ol.quantize_weight(g["small_w"])
+  assert torch.equal(codes, g["small_weight"])
+  assert torch.equal(scale, g["small_weight_scaler"])
+  assert (g["small_weight"][3] == 0).all()  # the all-zero channel keeps the clamped scale
+  # the package's module quantises a float weight the same way (offline work in plain torch)
+  from jetstream_pytorch_b200.layers import WeightOnlyPerChannelQuantizedLinear
+
+  lin = WeightOnlyPerChannelQuantizedLinear(g["small_w"].shape[1], g["small_w"].shape[0])
+  lin.quantize_weight_from_nn_linear(g["small_w"])
+  assert torch.equal(lin.weight, g["small_weight"]) and torch.equal(lin.weight_scaler, g["small_weight_scaler"])
+  for tag in ("small", "batch"):
+    x, w, s, want = g[f"{tag}_x"], g[f"{tag}_weight"], g[f"{tag}_weight_scaler"], g[f"{tag}_y"]
+    got = ol.w8a16_linear(x, w, s)
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    same = (got.view(torch.int16) == want.view(torch.int16)).float().mean().item()
+    assert same > 0.99, same
+    # (the outputs that differ are sums that cancel to almost nothing, where the reference's float32
+    # accumulation error shows; they stay far inside the absolute term of the tolerance)
+    assert ((got.float() - want.float()).abs().double() <= ol.w8a16_tolerance(x, w, s)).all()
