@@ -207,6 +207,16 @@ __global__ void __launch_bounds__(kThreadsL, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.w)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&maps.x)) : "memory");
+    // The weights do not depend on the launch before this one (only the activation levels do): the weight
+    // tiles of the first stages are requested before the wait on that launch.  Their bytes are announced to
+    // the stage's barrier without an arrival; the arrival comes with the activation tile's request.
+    const int rot0 = (int)(blockIdx.x % (unsigned)iters);
+    for (int it = 0; it < kStages && it < iters; ++it) {
+      const int kt = it + rot0 < iters ? it + rot0 : it + rot0 - iters;
+      const uint32_t bar = smem_addr(&sm.full[it]);
+      asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"((uint32_t)(kTileN * kTileK)) : "memory");
+      tma_load_2d(smem_addr(&sm.w[it][0]), &maps.w, k_begin + kt * kTileK, n0, bar);
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sm.tmem_base)),
@@ -228,15 +238,19 @@ __global__ void __launch_bounds__(kThreadsL, 1)
     // Every CTA of a K split reads the same activation tiles: each starts at another K step (the sums are
     // exact integers, their order is free), so that the CTAs do not ask the same L2 lines at the same time.
     const int rot = (int)(blockIdx.x % (unsigned)iters);
-    const uint32_t bytes = (uint32_t)(kTileN * kTileK + n_mma * kTileK);
+    const uint32_t w_bytes = (uint32_t)(kTileN * kTileK), x_bytes = (uint32_t)(n_mma * kTileK);
     for (int it = 0; it < iters && !dead; ++it) {
       const int s = it % kStages;
       if (it >= kStages && !mbar_wait_l(smem_addr(&sm.empty[s]), (uint32_t)((it / kStages) - 1) & 1u)) dead = true;
       if (dead) break;
       const uint32_t bar = smem_addr(&sm.full[s]);
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
       const int kt = it + rot < iters ? it + rot : it + rot - iters;
-      tma_load_2d(smem_addr(&sm.w[s][0]), &maps.w, k_begin + kt * kTileK, n0, bar);
+      if (it >= kStages) {  // (the weight tiles of the first stages are on their way already)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(w_bytes + x_bytes) : "memory");
+        tma_load_2d(smem_addr(&sm.w[s][0]), &maps.w, k_begin + kt * kTileK, n0, bar);
+      } else {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(x_bytes) : "memory");
+      }
       tma_load_2d(smem_addr(&sm.x[s][0]), &maps.x, k_begin + kt * kTileK, 0, bar);
     }
   } else if (tid == 32) {
@@ -478,10 +492,8 @@ extern "C" int jpt_w8a16_linear(const void* x, const void* w, const void* w_scal
   attr[0].val.clusterDim.z = 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) capturing = cudaStreamCaptureStatusNone;
   cfg.attrs = attr;
-  cfg.numAttrs = (pdl_enabled() && capturing == cudaStreamCaptureStatusNone) ? 2 : 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;  // (also inside a graph capture: the weight tiles stream in under the level kernel)
   const cudaError_t e = cudaLaunchKernelEx(&cfg, w8a16_gemm_kernel, maps, static_cast<const float*>(xs),
                                            static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(y), M, Mp, N, K,
                                            K / ksplit, status);
