@@ -449,7 +449,9 @@ int jpt_merge_partials(const void* o1, const float* m1, const float* l1,
  * WeightOnlyPerChannelQuantizedLinear.forward with symmetric weights and
  * without activation quantisation, jetstream_pt/layers.py:141-166:
  *   y = bf16(bf16(x @ W^T) * w_scale)
- *   x        [M, K] bf16, 1 <= M <= 128, K a multiple of 128, 16-byte aligned
+ *   x        [M, K] bf16, K a multiple of 128, 16-byte aligned; made for decode
+ *            batches: up to 128 rows stream the weights once, more rows are
+ *            taken in blocks of 128 (each block streams the weights again)
  *   w        [N, K] int8 (one row per output channel), 16-byte aligned
  *   w_scale  [N] bf16
  *   y        [M, N] bf16 out

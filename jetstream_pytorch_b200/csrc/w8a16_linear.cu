@@ -28,6 +28,7 @@
 #include <cuda.h>
 #include <string.h>
 
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 #include <vector>
@@ -127,11 +128,11 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t addr, uint32_t (&v)[32]) {
 // x [M, K] bf16 -> levels [2 Mp, K] int8 (rows 0 .. M-1: h, rows Mp .. Mp+M-1: l, the others zero)
 // and xs[m] = s_m / 254.
 __global__ void __launch_bounds__(256) x_levels_kernel(const __nv_bfloat16* x, int8_t* lev, float* xs, int* status, int M,
-                                                       int Mp, int K) {
+                                                       int Mp, int K, int clear_status) {
   __shared__ float red[33];
   const int m = blockIdx.x, tid = threadIdx.x;  // one CTA per row of the padded batch
   grid_dependency_trigger();
-  if (m == 0 && tid == 0) *status = 0;
+  if (m == 0 && tid == 0 && clear_status) *status = 0;
   uint2* hrow = reinterpret_cast<uint2*>(lev + (int64_t)m * K);
   uint2* lrow = reinterpret_cast<uint2*>(lev + (int64_t)(Mp + m) * K);
   const int nvec = K / 8;  // eight elements per step: 16 bytes in, 8 + 8 bytes out
@@ -434,24 +435,18 @@ using namespace jpt;
 
 extern "C" size_t jpt_w8a16_linear_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  const int Mp = (M + 7) / 8 * 8;
+  const int Mp = (std::min(M, kMaxM) + 7) / 8 * 8;  // (more rows are taken in blocks of 128, one after the other)
   const size_t levels = ((size_t)2 * Mp * K + 255) / 256 * 256;
   const size_t xs = 1024;
   (void)N;
   return 256 + levels + xs;
 }
 
-extern "C" int jpt_w8a16_linear(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K,
-                                void* workspace, size_t workspace_bytes, void* stream) {
-  JPT_REQUIRE(x && w && w_scale && y, JPT_EINVAL, "w8a16_linear: null tensor");
-  JPT_REQUIRE(M >= 1 && M <= kMaxM, JPT_EINVAL, "w8a16_linear: M = %d rows, the kernel takes 1 .. %d (decode batches)", M, kMaxM);
-  JPT_REQUIRE(N >= 1 && K >= kTileK && K % kTileK == 0, JPT_EINVAL, "w8a16_linear: K = %d must be a multiple of %d", K, kTileK);
-  JPT_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 2), JPT_EALIGN, "w8a16_linear: x and w must be 16-byte aligned");
-  const size_t need = jpt_w8a16_linear_workspace_bytes(M, N, K);
-  JPT_REQUIRE(workspace && workspace_bytes >= need, JPT_EWORKSPACE, "w8a16_linear: workspace of %zu bytes needed, %zu given", need,
-              workspace_bytes);
-  JPT_REQUIRE(aligned(workspace, 256), JPT_EALIGN, "w8a16_linear: workspace must be 256-byte aligned");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+namespace jpt {
+namespace {
+// up to 128 rows: the level kernel, then the GEMM
+int linear_rows(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K, void* workspace, cudaStream_t st,
+                bool clear_status) {
   const int Mp = (M + 7) / 8 * 8;
   char* ws = static_cast<char*>(workspace);
   int* status = reinterpret_cast<int*>(ws);  // first word: 0, or the code of a CTA that gave up
@@ -478,7 +473,7 @@ extern "C" int jpt_w8a16_linear(const void* x, const void* w, const void* w_scal
   }
   // (the level kernel also clears the status word and the padding rows of the level matrix; the two launches after it
   // may start while their predecessor drains and wait for its results on the device)
-  x_levels_kernel<<<Mp, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), lev, xs, status, M, Mp, K);
+  x_levels_kernel<<<Mp, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), lev, xs, status, M, Mp, K, clear_status ? 1 : 0);
   if (int rc = check_launch("x_levels_kernel")) return rc;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((N + kTileN - 1) / kTileN, ksplit);
@@ -498,5 +493,29 @@ extern "C" int jpt_w8a16_linear(const void* x, const void* w, const void* w_scal
                                            static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(y), M, Mp, N, K,
                                            K / ksplit, status);
   if (e != cudaSuccess) return fail((int)e, "w8a16_gemm_kernel: %s", cudaGetErrorString(e));
+  return 0;
+}
+}  // namespace
+}  // namespace jpt
+
+extern "C" int jpt_w8a16_linear(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  JPT_REQUIRE(x && w && w_scale && y, JPT_EINVAL, "w8a16_linear: null tensor");
+  JPT_REQUIRE(M >= 1, JPT_EINVAL, "w8a16_linear: M = %d rows", M);
+  JPT_REQUIRE(N >= 1 && K >= kTileK && K % kTileK == 0, JPT_EINVAL, "w8a16_linear: K = %d must be a multiple of %d", K, kTileK);
+  JPT_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 2), JPT_EALIGN, "w8a16_linear: x and w must be 16-byte aligned");
+  const size_t need = jpt_w8a16_linear_workspace_bytes(M, N, K);
+  JPT_REQUIRE(workspace && workspace_bytes >= need, JPT_EWORKSPACE, "w8a16_linear: workspace of %zu bytes needed, %zu given", need,
+              workspace_bytes);
+  JPT_REQUIRE(aligned(workspace, 256), JPT_EALIGN, "w8a16_linear: workspace must be 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // More than 128 rows (prefill shapes) go through in blocks of 128 that reuse the workspace in stream order;
+  // every block streams the weights again, which is the wrong trade for a compute-bound shape but a correct one.
+  for (int m0 = 0; m0 < M; m0 += kMaxM) {
+    const int rows = std::min(kMaxM, M - m0);
+    const int rc = linear_rows(static_cast<const char*>(x) + (size_t)m0 * K * 2, w, w_scale, static_cast<char*>(y) + (size_t)m0 * N * 2,
+                               rows, N, K, workspace, st, m0 == 0);
+    if (rc) return rc;
+  }
   return 0;
 }

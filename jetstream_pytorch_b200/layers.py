@@ -132,11 +132,10 @@ class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
   scale per output channel, bf16 activations, result
   bf16(bf16(inputs @ weight^T) * weight_scaler).
 
-  Built: 8-bit symmetric weights, no activation quantisation, up to 128 rows of
-  activations per call (a decode batch) and `in_features` a multiple of 128.
+  Built: 8-bit symmetric weights, no activation quantisation, `in_features` a
+  multiple of 128.  The kernel is made for decode batches (up to 128 rows of
+  activations stream the weights once); more rows go through in blocks of 128.
   Anything else raises; there is no eager path."""
-
-  MAX_ROWS = 128
 
   def __init__(self, in_features, out_features, bias=False, device=None, quant_config=None):
     super().__init__()
@@ -190,8 +189,8 @@ class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
     k, n = self.in_features, self.out_features
     x = inputs.reshape(-1, k)
     m = x.shape[0]
-    if not 1 <= m <= self.MAX_ROWS:
-      raise NotImplementedError(f"{m} rows of activations: the kernel takes 1 .. {self.MAX_ROWS} (decode batches)")
+    if m < 1:
+      return inputs.new_empty((*inputs.shape[:-1], n))
     if not x.is_contiguous():
       x = x.contiguous()
     lib = _lib.lib()
