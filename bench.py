@@ -591,6 +591,34 @@ def extra_w8a16_linear(dev, peak, reps, eager=False):
     del layers
     torch.cuda.empty_cache()
   out["workload"] = "y = bf16(bf16(x W^T) * scale), x bf16 [96, K], W int8 [N, K]: level split + tcgen05 GEMM launches"
+  if not eager:
+    # the feed-forward block behind its norm: RMSNorm (writes the levels of its result), w1 and w3 on those
+    # levels, the gate (writes the levels of its result), w2: five launches, 705 MB of weights
+    from jetstream_pytorch_b200.layers import FeedForward, RMSNorm
+
+    dim, hidden, sets = 8192, 28672, 2
+    blocks = []
+    for _ in range(sets):
+      ff = FeedForward(dim, hidden, device=dev)
+      for lin in (ff.w1, ff.w2, ff.w3):
+        lin._load_quantized_weights(
+            torch.randint(-127, 128, (lin.out_features, lin.in_features), generator=gen, dtype=torch.int8, device=dev),
+            torch.rand(lin.out_features, generator=gen, device=dev) * 0.002)
+      blocks.append((RMSNorm(dim, eps=1e-5, device=dev), ff))
+    x = torch.randn((B, dim), generator=gen, device=dev).to(torch.bfloat16)
+
+    def run_blocks():
+      for norm, ff in blocks:
+        y, lv = norm(x, with_levels=True)
+        ff(y, levels=lv)
+
+    us = time_replays(graph_of(run_blocks).replay, reps) * 1e3 / sets
+    nbytes = 3 * dim * hidden + 3 * hidden * 2 + dim * 2 + B * 2 * (2 * dim + 3 * hidden + dim)
+    out["ffn_block_8192_28672"] = kernel_entry(
+        us, nbytes, peak, launches=5, kernel_status=max(ff.w2.kernel_status() for _, ff in blocks),
+        workload="RMSNorm -> w1, w3 -> silu-mul -> w2 at batch 96 (weights, scales, norm weight, activations in and out)")
+    del blocks
+    torch.cuda.empty_cache()
   return out
 
 

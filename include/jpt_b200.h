@@ -467,6 +467,38 @@ int jpt_w8a16_linear(const void* x, const void* w, const void* w_scale, void* y,
                      int M, int N, int K, void* workspace,
                      size_t workspace_bytes, void* stream);
 
+/*
+ * The same layer in two steps, for activations that feed several layers (wq /
+ * wk / wv after the attention norm, w1 / w3 after the ffn norm): the level
+ * split once into a workspace (M <= 128 rows), then one GEMM per layer on the
+ * levels it holds.  jpt_w8a16_linear(x, ...) equals jpt_w8a16_split_levels(x)
+ * followed by jpt_w8a16_linear_from_levels(...), bit for bit.
+ */
+int jpt_w8a16_split_levels(const void* x, int M, int K, void* workspace,
+                           size_t workspace_bytes, void* stream);
+int jpt_w8a16_linear_from_levels(void* workspace, size_t workspace_bytes,
+                                 const void* w, const void* w_scale, void* y,
+                                 int M, int N, int K, void* stream);
+
+/*
+ * The two element-wise producers of a linear layer's activations in a decoder
+ * block, each of which can leave the level split of its result in a workspace
+ * (levels_workspace non-NULL, M <= 128) so that the layers behind it start at
+ * their GEMM.  All tensors bf16, 16-byte aligned, K a multiple of 8 (of 128 with
+ * levels).
+ *   jpt_rmsnorm   RMSNorm.forward, jetstream_pt/layers.py:337-350, with a bf16
+ *                 weight: y = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * weight),
+ *                 x, y [M, K], weight [K]; the mean and the product in fp32
+ *   jpt_silu_mul  the gate of FeedForward.forward,
+ *                 third_party/llama/model_exportable.py:84-86:
+ *                 h = bf16(bf16(silu(a)) * b), a, b, h [M, K]
+ */
+int jpt_rmsnorm(const void* x, const void* weight, float eps, void* y, int M,
+                int K, void* levels_workspace, size_t workspace_bytes,
+                void* stream);
+int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K,
+                 void* levels_workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

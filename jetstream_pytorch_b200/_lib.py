@@ -93,6 +93,10 @@ _SIGNATURES = {
     "jpt_enable_peer_access": (c_int, [c_int, c_int]),
     "jpt_w8a16_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "jpt_w8a16_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "jpt_w8a16_split_levels": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "jpt_w8a16_linear_from_levels": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "jpt_rmsnorm": (c_int, [c_void_p, c_void_p, ctypes.c_float, c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "jpt_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jpt_quantize_tokens": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "jpt_flash_decode": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),
     "jpt_flash_decode_static": (c_int, [ctypes.POINTER(AttnParams), c_void_p]),

@@ -182,6 +182,184 @@ __global__ void __launch_bounds__(256) x_levels_kernel(const __nv_bfloat16* x, i
   if (tid == 0) xs[m] = amax * (1.f / 127.f) * (1.f / 254.f);
 }
 
+// ---------------------------------------------------------------- producers of the activations that split on the way
+// Eight bf16 values of a row -> their two level bytes each, stored at step v of the row's h and l rows.
+__device__ __forceinline__ void split_levels8(const __nv_bfloat16 (&e)[8], float inv, uint2* hrow, uint2* lrow, int v) {
+  uint32_t hb[2] = {0u, 0u}, lb[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float t = __bfloat162float(e[j]) * inv;
+    const float h = rintf(t);
+    const float l = rintf((t - h) * 254.f);
+    hb[j >> 2] |= ((uint32_t)(int)h & 0xffu) << (8 * (j & 3));
+    lb[j >> 2] |= ((uint32_t)(int)l & 0xffu) << (8 * (j & 3));
+  }
+  hrow[v] = make_uint2(hb[0], hb[1]);
+  lrow[v] = make_uint2(lb[0], lb[1]);
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int sh = 16; sh > 0; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float x = lane < (int)((blockDim.x + 31) >> 5) ? red[lane] : 0.f;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) x += __shfl_xor_sync(0xffffffffu, x, sh);
+    if (lane == 0) red[32] = x;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+constexpr int kRowThreads = 1024;  // threads of a CTA of the element-wise producers
+// The CTAs of a cluster (gridDim.x of them, rank blockIdx.x) share a row: a value of every CTA combined in the
+// order of the ranks.  Every CTA stores its value into slot `rank` of every CTA's `slots`; one cluster barrier later
+// all slots are there.  (`slots` must not be reused for another reduction: a fast CTA could overwrite a slot
+// that a slow one has not read yet.)
+template <typename Op>
+__device__ __forceinline__ float cluster_combine(float v, float* slots, Op op) {
+  const int csize = (int)gridDim.x, rank = (int)blockIdx.x;
+  if (csize == 1) return v;
+  if ((int)threadIdx.x < csize) st_cluster_f32(remote_smem(smem_addr(&slots[rank]), (int)threadIdx.x), v);
+  cluster_sync();
+  float r = slots[0];
+  for (int c = 1; c < csize; ++c) r = op(r, slots[c]);
+  return r;
+}
+
+// A row of results, eight at a time from `compute(step, out)`: written to `dst`, and with `levels` split into the
+// row's level bytes once the row's amax is known.  The first steps of a thread stay in registers between the two
+// passes (1024 threads x 4 steps x 8: rows of up to 32768 elements); longer rows compute their tail twice.
+template <typename Compute>
+__device__ __forceinline__ void write_row_and_levels(Compute& compute, uint4* dst, int v_lo, int nvec, bool levels, uint2* hrow,
+                                                     uint2* lrow, float* xs, int m, float* red, float* slots) {
+  constexpr int kHeldOut = 4;
+  const int tid = threadIdx.x + v_lo;  // (this CTA's steps are v_lo .. nvec - 1)
+  uint4 held[kHeldOut];
+  float amax = 0.f;
+  auto fold = [&](const __nv_bfloat16 (&o)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(o[j])));
+  };
+#pragma unroll
+  for (int i = 0; i < kHeldOut; ++i) {
+    const int v = tid + kRowThreads * i;
+    if (v < nvec) {
+      __nv_bfloat16 o[8];
+      compute(v, o);
+      fold(o);
+      held[i] = *reinterpret_cast<const uint4*>(o);
+      dst[v] = held[i];
+    }
+  }
+  for (int v = tid + kRowThreads * kHeldOut; v < nvec; v += kRowThreads) {
+    __nv_bfloat16 o[8];
+    compute(v, o);
+    fold(o);
+    dst[v] = *reinterpret_cast<const uint4*>(o);
+  }
+  if (!levels) return;
+  amax = cluster_combine(block_max(amax, red), slots, [](float p, float q) { return fmaxf(p, q); });
+  const float inv = amax > 0.f ? 127.f / amax : 0.f;
+#pragma unroll
+  for (int i = 0; i < kHeldOut; ++i) {
+    const int v = tid + kRowThreads * i;
+    if (v < nvec) split_levels8(*reinterpret_cast<const __nv_bfloat16(*)[8]>(&held[i]), inv, hrow, lrow, v);
+  }
+  for (int v = tid + kRowThreads * kHeldOut; v < nvec; v += kRowThreads) {
+    __nv_bfloat16 o[8];
+    compute(v, o);
+    split_levels8(o, inv, hrow, lrow, v);
+  }
+  if (threadIdx.x == 0 && blockIdx.x == 0) xs[m] = amax * (1.f / 127.f) * (1.f / 254.f);
+}
+
+// RMSNorm (jetstream_pt/layers.py:337-350 with a bf16 weight): n = bf16(x * rsqrt(mean(x^2) + eps)) in fp32,
+// y = bf16(n * weight).  With `lev` the row's levels are written too (the rows M .. Mp-1 of the level matrix as zeros),
+// so that the linear layers that read y start at their GEMM.  One CTA per row.
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_levels_kernel(const __nv_bfloat16* x, const __nv_bfloat16* weight, float eps,
+                                                             __nv_bfloat16* y, int8_t* lev, float* xs, int* status, int M, int Mp,
+                                                             int K) {
+  __shared__ float red[33], slots_ss[8], slots_amax[8];
+  // row m = blockIdx.y; the CTAs of the row's cluster (blockIdx.x) take equal parts of its steps of eight elements
+  const int m = blockIdx.y, tid = threadIdx.x, per = K / 8 / (int)gridDim.x;
+  const int v_lo = (int)blockIdx.x * per, nvec = v_lo + per;
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  if (m == 0 && blockIdx.x == 0 && tid == 0 && status) *status = 0;
+  uint2* hrow = lev ? reinterpret_cast<uint2*>(lev + (int64_t)m * K) : nullptr;
+  uint2* lrow = lev ? reinterpret_cast<uint2*>(lev + (int64_t)(Mp + m) * K) : nullptr;
+  if (m >= M) {  // (a padding row: the whole cluster is here, nobody waits for it)
+    for (int v = v_lo + tid; v < nvec; v += kRowThreads) hrow[v] = lrow[v] = make_uint2(0u, 0u);
+    return;
+  }
+  const uint4* row = reinterpret_cast<const uint4*>(x + (int64_t)m * K);
+  const uint4* wrow = reinterpret_cast<const uint4*>(weight);
+  float ss = 0.f;
+  for (int v = v_lo + tid; v < nvec; v += kRowThreads) {
+    const uint4 r = __ldg(row + v);
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = __bfloat162float(e[j]);
+      ss = fmaf(f, f, ss);
+    }
+  }
+  ss = cluster_combine(block_sum(ss, red), slots_ss, [](float p, float q) { return p + q; });
+  const float rs = 1.f / sqrtf(ss / (float)K + eps);
+  auto normed = [&](int v, __nv_bfloat16 (&o)[8]) {
+    const uint4 r = __ldg(row + v), wv = __ldg(wrow + v);
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&r);
+    const __nv_bfloat16* we = reinterpret_cast<const __nv_bfloat16*>(&wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float n = __bfloat162float(__float2bfloat16_rn(__bfloat162float(e[j]) * rs));
+      o[j] = __float2bfloat16_rn(n * __bfloat162float(we[j]));
+    }
+  };
+  write_row_and_levels(normed, reinterpret_cast<uint4*>(y + (int64_t)m * K), v_lo, nvec, lev != nullptr, hrow, lrow, xs, m, red,
+                       slots_amax);
+  if (gridDim.x > 1) cluster_sync();  // (no CTA leaves while a peer may still store into its slots)
+}
+
+// The feed-forward block's gate (third_party/llama/model_exportable.py:84-86): h = bf16(bf16(silu(a)) * b), and with
+// `lev` the levels of h for the down projection.
+__global__ void __launch_bounds__(kRowThreads) silu_mul_levels_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* h,
+                                                              int8_t* lev, float* xs, int* status, int M, int Mp, int K) {
+  __shared__ float red[33], slots_amax[8];
+  const int m = blockIdx.y, tid = threadIdx.x, per = K / 8 / (int)gridDim.x;
+  const int v_lo = (int)blockIdx.x * per, nvec = v_lo + per;
+  grid_dependency_wait();
+  grid_dependency_trigger();
+  if (m == 0 && blockIdx.x == 0 && tid == 0 && status) *status = 0;
+  uint2* hrow = lev ? reinterpret_cast<uint2*>(lev + (int64_t)m * K) : nullptr;
+  uint2* lrow = lev ? reinterpret_cast<uint2*>(lev + (int64_t)(Mp + m) * K) : nullptr;
+  if (m >= M) {
+    for (int v = v_lo + tid; v < nvec; v += kRowThreads) hrow[v] = lrow[v] = make_uint2(0u, 0u);
+    return;
+  }
+  const uint4* arow = reinterpret_cast<const uint4*>(a + (int64_t)m * K);
+  const uint4* brow = reinterpret_cast<const uint4*>(b + (int64_t)m * K);
+  auto gated = [&](int v, __nv_bfloat16 (&o)[8]) {
+    const uint4 ra = __ldg(arow + v), rb = __ldg(brow + v);
+    const __nv_bfloat16* ea = reinterpret_cast<const __nv_bfloat16*>(&ra);
+    const __nv_bfloat16* eb = reinterpret_cast<const __nv_bfloat16*>(&rb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = __bfloat162float(ea[j]);
+      // (fast exponential and division: the quotient is rounded to bf16, and the exact forms are subroutines)
+      const float s = __bfloat162float(__float2bfloat16_rn(__fdividef(f, 1.f + __expf(-f))));
+      o[j] = __float2bfloat16_rn(s * __bfloat162float(eb[j]));
+    }
+  };
+  write_row_and_levels(gated, reinterpret_cast<uint4*>(h + (int64_t)m * K), v_lo, nvec, lev != nullptr, hrow, lrow, xs, m, red,
+                       slots_amax);
+  if (gridDim.x > 1) cluster_sync();  // (no CTA leaves while a peer may still store into its slots)
+}
+
 // ---------------------------------------------------------------- (2) the GEMM
 // grid (ceil(N / 256), ksplit), clusters of (1, ksplit): the rank of a CTA in its cluster is its K split.
 __global__ void __launch_bounds__(kThreadsL, 1)
@@ -444,23 +622,34 @@ extern "C" size_t jpt_w8a16_linear_workspace_bytes(int M, int N, int K) {
 
 namespace jpt {
 namespace {
-// up to 128 rows: the level kernel, then the GEMM
-int linear_rows(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K, void* workspace, cudaStream_t st,
-                bool clear_status) {
-  const int Mp = (M + 7) / 8 * 8;
+// The workspace of up to 128 rows: status word, level matrix [2 Mp, K], row scales.
+struct LevelsView {
+  int* status;  // 0, or the code of a CTA that gave up
+  int8_t* lev;
+  float* xs;
+  int Mp;
+};
+LevelsView levels_view(void* workspace, int M, int K) {
+  LevelsView v;
+  v.Mp = (M + 7) / 8 * 8;
   char* ws = static_cast<char*>(workspace);
-  int* status = reinterpret_cast<int*>(ws);  // first word: 0, or the code of a CTA that gave up
-  int8_t* lev = reinterpret_cast<int8_t*>(ws + 256);
-  const size_t levels = ((size_t)2 * Mp * K + 255) / 256 * 256;
-  float* xs = reinterpret_cast<float*>(ws + 256 + levels);
-  const int ksplit = split_for(N, K);
+  v.status = reinterpret_cast<int*>(ws);
+  v.lev = reinterpret_cast<int8_t*>(ws + 256);
+  const size_t levels = ((size_t)2 * v.Mp * K + 255) / 256 * 256;
+  v.xs = reinterpret_cast<float*>(ws + 256 + levels);
+  return v;
+}
 
+// The GEMM on levels that a launch before this one in the stream wrote.  The launch may start while that one
+// drains (it requests its first weight tiles at once) and waits for its results on the device.
+int launch_gemm(const LevelsView& lv, const void* w, const void* w_scale, void* y, int M, int N, int K, cudaStream_t st) {
+  const int ksplit = split_for(N, K);
   static std::mutex mu;
   LinearMaps maps;
   memset(&maps, 0, sizeof(maps));
   {
     std::lock_guard<std::mutex> lock(mu);
-    JPT_REQUIRE(encode_2d(&maps.w, w, N, K, kTileN) && encode_2d(&maps.x, lev, 2 * Mp, K, 2 * Mp), JPT_EINVAL,
+    JPT_REQUIRE(encode_2d(&maps.w, w, N, K, kTileN) && encode_2d(&maps.x, lv.lev, 2 * lv.Mp, K, 2 * lv.Mp), JPT_EINVAL,
                 "w8a16_linear: the tensors cannot be described by a tensor map");
   }
   static bool configured[64];
@@ -471,10 +660,6 @@ int linear_rows(const void* x, const void* w, const void* w_scale, void* y, int 
     if (e != cudaSuccess) return fail((int)e, "w8a16_linear: configuring the kernel: %s", cudaGetErrorString(e));
     configured[dev] = true;
   }
-  // (the level kernel also clears the status word and the padding rows of the level matrix; the two launches after it
-  // may start while their predecessor drains and wait for its results on the device)
-  x_levels_kernel<<<Mp, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), lev, xs, status, M, Mp, K, clear_status ? 1 : 0);
-  if (int rc = check_launch("x_levels_kernel")) return rc;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((N + kTileN - 1) / kTileN, ksplit);
   cfg.blockDim = dim3(kThreadsL);
@@ -489,10 +674,54 @@ int linear_rows(const void* x, const void* w, const void* w_scale, void* y, int 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;  // (also inside a graph capture: the weight tiles stream in under the level kernel)
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, w8a16_gemm_kernel, maps, static_cast<const float*>(xs),
-                                           static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(y), M, Mp, N, K,
-                                           K / ksplit, status);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, w8a16_gemm_kernel, maps, static_cast<const float*>(lv.xs),
+                                           static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(y), M, lv.Mp, N, K,
+                                           K / ksplit, lv.status);
   if (e != cudaSuccess) return fail((int)e, "w8a16_gemm_kernel: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+// (the level kernel also clears the status word and the padding rows of the level matrix)
+int launch_levels(const void* x, const LevelsView& lv, int M, int K, cudaStream_t st, bool clear_status) {
+  x_levels_kernel<<<lv.Mp, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), lv.lev, lv.xs, lv.status, M, lv.Mp, K,
+                                         clear_status ? 1 : 0);
+  return check_launch("x_levels_kernel");
+}
+
+// CTAs per row of the element-wise producers (a cluster along x): enough of them to fill the GPU
+int row_parts(int rows, int K) {
+  const int steps = K / 8;
+  int c = 1;
+  // (one CTA of 1024 threads per row measured faster than a row split over a cluster: 3.7 against 9.8 us for
+  // RMSNorm of [96, 8192]; the split stays available for single rows of long vectors)
+  while (c < 8 && rows * c < 8 && steps % (c * 2) == 0 && steps / (c * 2) >= kRowThreads) c *= 2;
+  return c;
+}
+template <typename... KArgs, typename... Args>
+int launch_rows(const char* name, void (*kernel)(KArgs...), int rows, int parts, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(parts, rows);
+  cfg.blockDim = dim3(kRowThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = parts;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess) return fail((int)e, "%s: %s", name, cudaGetErrorString(e));
+  return 0;
+}
+
+int check_levels_args(const char* who, int M, int K, const void* workspace, size_t workspace_bytes) {
+  JPT_REQUIRE(M >= 1 && M <= kMaxM, JPT_EINVAL, "%s: M = %d rows, activation levels are kept for 1 .. %d rows", who, M, kMaxM);
+  JPT_REQUIRE(K >= kTileK && K % kTileK == 0, JPT_EINVAL, "%s: K = %d must be a multiple of %d", who, K, kTileK);
+  const size_t need = jpt_w8a16_linear_workspace_bytes(M, 1, K);
+  JPT_REQUIRE(workspace && workspace_bytes >= need, JPT_EWORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need,
+              workspace_bytes);
+  JPT_REQUIRE(aligned(workspace, 256), JPT_EALIGN, "%s: workspace must be 256-byte aligned", who);
   return 0;
 }
 }  // namespace
@@ -513,9 +742,57 @@ extern "C" int jpt_w8a16_linear(const void* x, const void* w, const void* w_scal
   // every block streams the weights again, which is the wrong trade for a compute-bound shape but a correct one.
   for (int m0 = 0; m0 < M; m0 += kMaxM) {
     const int rows = std::min(kMaxM, M - m0);
-    const int rc = linear_rows(static_cast<const char*>(x) + (size_t)m0 * K * 2, w, w_scale, static_cast<char*>(y) + (size_t)m0 * N * 2,
-                               rows, N, K, workspace, st, m0 == 0);
-    if (rc) return rc;
+    const LevelsView lv = levels_view(workspace, rows, K);
+    if (int rc = launch_levels(static_cast<const char*>(x) + (size_t)m0 * K * 2, lv, rows, K, st, m0 == 0)) return rc;
+    if (int rc = launch_gemm(lv, w, w_scale, static_cast<char*>(y) + (size_t)m0 * N * 2, rows, N, K, st)) return rc;
   }
   return 0;
+}
+
+extern "C" int jpt_w8a16_split_levels(const void* x, int M, int K, void* workspace, size_t workspace_bytes, void* stream) {
+  JPT_REQUIRE(x && aligned(x, 16), JPT_EALIGN, "w8a16_split_levels: x must be 16-byte aligned");
+  if (int rc = check_levels_args("w8a16_split_levels", M, K, workspace, workspace_bytes)) return rc;
+  return launch_levels(x, levels_view(workspace, M, K), M, K, static_cast<cudaStream_t>(stream), true);
+}
+
+extern "C" int jpt_w8a16_linear_from_levels(void* workspace, size_t workspace_bytes, const void* w, const void* w_scale, void* y,
+                                            int M, int N, int K, void* stream) {
+  JPT_REQUIRE(w && w_scale && y && N >= 1, JPT_EINVAL, "w8a16_linear_from_levels: null tensor");
+  JPT_REQUIRE(aligned(w, 16), JPT_EALIGN, "w8a16_linear_from_levels: w must be 16-byte aligned");
+  if (int rc = check_levels_args("w8a16_linear_from_levels", M, K, workspace, workspace_bytes)) return rc;
+  return launch_gemm(levels_view(workspace, M, K), w, w_scale, y, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int jpt_rmsnorm(const void* x, const void* weight, float eps, void* y, int M, int K, void* levels_workspace,
+                           size_t workspace_bytes, void* stream) {
+  JPT_REQUIRE(x && weight && y && M >= 1 && K >= 8 && K % 8 == 0, JPT_EINVAL, "rmsnorm: M = %d, K = %d (K must be a multiple of 8)", M, K);
+  JPT_REQUIRE(aligned(x, 16) && aligned(weight, 16) && aligned(y, 16), JPT_EALIGN, "rmsnorm: tensors must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(weight);
+  if (!levels_workspace) {
+    return launch_rows("rmsnorm_levels_kernel", rmsnorm_levels_kernel, M, row_parts(M, K), st, xp, wp, eps, static_cast<__nv_bfloat16*>(y),
+                       nullptr, nullptr, nullptr, M, M, K);
+  }
+  if (int rc = check_levels_args("rmsnorm", M, K, levels_workspace, workspace_bytes)) return rc;
+  const LevelsView lv = levels_view(levels_workspace, M, K);
+  return launch_rows("rmsnorm_levels_kernel", rmsnorm_levels_kernel, lv.Mp, row_parts(lv.Mp, K), st, xp, wp, eps,
+                     static_cast<__nv_bfloat16*>(y), lv.lev, lv.xs, lv.status, M, lv.Mp, K);
+}
+
+extern "C" int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K, void* levels_workspace, size_t workspace_bytes,
+                            void* stream) {
+  JPT_REQUIRE(a && b && h && M >= 1 && K >= 8 && K % 8 == 0, JPT_EINVAL, "silu_mul: M = %d, K = %d (K must be a multiple of 8)", M, K);
+  JPT_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(h, 16), JPT_EALIGN, "silu_mul: tensors must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(a);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(b);
+  if (!levels_workspace) {
+    return launch_rows("silu_mul_levels_kernel", silu_mul_levels_kernel, M, row_parts(M, K), st, ap, bp, static_cast<__nv_bfloat16*>(h),
+                       nullptr, nullptr, nullptr, M, M, K);
+  }
+  if (int rc = check_levels_args("silu_mul", M, K, levels_workspace, workspace_bytes)) return rc;
+  const LevelsView lv = levels_view(levels_workspace, M, K);
+  return launch_rows("silu_mul_levels_kernel", silu_mul_levels_kernel, lv.Mp, row_parts(lv.Mp, K), st, ap, bp,
+                     static_cast<__nv_bfloat16*>(h), lv.lev, lv.xs, lv.status, M, lv.Mp, K);
 }

@@ -7,6 +7,10 @@ rest of `layers.Attention` stay outside this package.
 
 `WeightOnlyPerChannelQuantizedLinear` (jetstream_pt/layers.py:69-166) is the
 other byte stream of a decode step: the int8 weights of the projections.
+`RMSNorm` (layers.py:337-350) and `FeedForward`
+(third_party/llama/model_exportable.py:32-86) are the producers and consumers of
+its activations in a decoder block; for decode batches they hand the int8 level
+split of their results (`ActivationLevels`) to the linear layers behind them.
 """
 
 import torch
@@ -183,7 +187,9 @@ class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
     """0, or 1 if a bounded wait inside the last launch gave up (synchronises)."""
     return 0 if self._workspace is None else int(self._workspace[:4].view(torch.int32).item())
 
-  def forward(self, inputs):
+  def forward(self, inputs, levels=None):
+    """`levels` (an `ActivationLevels` of `inputs`, from `RMSNorm`, `FeedForward`
+    or `ActivationLevels.of`): the layer starts at its GEMM."""
     if inputs.dtype != torch.bfloat16:
       raise NotImplementedError(f"activations must be bfloat16, got {inputs.dtype}")
     k, n = self.in_features, self.out_features
@@ -191,6 +197,15 @@ class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
     m = x.shape[0]
     if m < 1:
       return inputs.new_empty((*inputs.shape[:-1], n))
+    if levels is not None:
+      if (levels.rows, levels.features) != (m, k):
+        raise ValueError(f"levels of a [{levels.rows}, {levels.features}] activation given for [{m}, {k}]")
+      y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+      ws = levels.workspace
+      _lib.check(_lib.lib().jpt_w8a16_linear_from_levels(_lib.ptr(ws), ws.numel(), _lib.ptr(self.weight),
+                                                         _lib.ptr(self.weight_scaler), _lib.ptr(y), m, n, k, _lib.stream()))
+      self._workspace = ws  # (kernel_status reads the status word of the workspace last used)
+      return y.reshape(*inputs.shape[:-1], n)
     if not x.is_contiguous():
       x = x.contiguous()
     lib = _lib.lib()
@@ -201,3 +216,92 @@ class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
     _lib.check(lib.jpt_w8a16_linear(_lib.ptr(x), _lib.ptr(self.weight), _lib.ptr(self.weight_scaler), _lib.ptr(y), m, n,
                                     k, _lib.ptr(self._workspace), self._workspace.numel(), _lib.stream()))
     return y.reshape(*inputs.shape[:-1], n)
+
+
+class ActivationLevels:
+  """The int8 level split of a [rows, features] bf16 activation (rows <= 128), as
+  the weight-only linear layers' GEMM reads it: x = s (h + l / 254) per row with
+  signed bytes h, l.  One split serves every layer that reads the activation."""
+
+  MAX_ROWS = 128
+
+  def __init__(self, rows, features, device):
+    if not 1 <= rows <= self.MAX_ROWS or features % 128:
+      raise NotImplementedError(f"levels are kept for 1 .. {self.MAX_ROWS} rows of a multiple of 128 features, "
+                                f"got [{rows}, {features}]")
+    self.rows, self.features = rows, features
+    need = _lib.lib().jpt_w8a16_linear_workspace_bytes(rows, 1, features)
+    self.workspace = torch.empty((need,), dtype=torch.uint8, device=device)
+
+  @classmethod
+  def fits(cls, x):
+    return x.is_cuda and x.dtype == torch.bfloat16 and 1 <= x.numel() // x.shape[-1] <= cls.MAX_ROWS and x.shape[-1] % 128 == 0
+
+  @classmethod
+  def of(cls, x):
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    lv = cls(x2.shape[0], x2.shape[1], x.device)
+    _lib.check(_lib.lib().jpt_w8a16_split_levels(_lib.ptr(x2), lv.rows, lv.features, _lib.ptr(lv.workspace),
+                                                 lv.workspace.numel(), _lib.stream()))
+    return lv
+
+
+class RMSNorm(torch.nn.Module):
+  """layers.py:337-350 with a bf16 weight:
+  bf16(bf16(x * rsqrt(mean(x^2) + eps)) * weight), the mean in fp32."""
+
+  def __init__(self, dim: int, eps: float = 1e-6, device=None):
+    super().__init__()
+    self.eps = eps
+    self.weight = torch.nn.Parameter(torch.ones(dim, dtype=torch.bfloat16, device=device), requires_grad=False)
+
+  def forward(self, x, with_levels=False):
+    """Returns y, or (y, ActivationLevels of y) with `with_levels`."""
+    if x.dtype != torch.bfloat16 or self.weight.dtype != torch.bfloat16:
+      raise NotImplementedError("RMSNorm is provided for bfloat16 activations and weights")
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k).contiguous()
+    m = x2.shape[0]
+    y = torch.empty_like(x2)
+    lv = ActivationLevels(m, k, x.device) if with_levels else None
+    _lib.check(_lib.lib().jpt_rmsnorm(_lib.ptr(x2), _lib.ptr(self.weight), float(self.eps), _lib.ptr(y), m, k,
+                                      _lib.ptr(lv.workspace) if lv else None, lv.workspace.numel() if lv else 0,
+                                      _lib.stream()))
+    y = y.reshape(x.shape)
+    return (y, lv) if with_levels else y
+
+
+def silu_mul(a, b, with_levels=False):
+  """bf16(bf16(silu(a)) * b); with `with_levels` also the level split of the result."""
+  if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.shape != b.shape:
+    raise NotImplementedError("silu_mul takes two bfloat16 tensors of one shape")
+  k = a.shape[-1]
+  a2, b2 = a.reshape(-1, k).contiguous(), b.reshape(-1, k).contiguous()
+  m = a2.shape[0]
+  h = torch.empty_like(a2)
+  lv = ActivationLevels(m, k, a.device) if with_levels else None
+  _lib.check(_lib.lib().jpt_silu_mul(_lib.ptr(a2), _lib.ptr(b2), _lib.ptr(h), m, k, _lib.ptr(lv.workspace) if lv else None,
+                                     lv.workspace.numel() if lv else 0, _lib.stream()))
+  h = h.reshape(a.shape)
+  return (h, lv) if with_levels else h
+
+
+class FeedForward(torch.nn.Module):
+  """third_party/llama/model_exportable.py:32-86 with weight-only int8 linear
+  layers: w2(silu(w1(x)) * w3(x)).  For a decode batch the level split of x is
+  made once for w1 and w3 (or taken from the norm in front: `levels`), and the
+  gate writes the split of its result for w2: five launches in all."""
+
+  def __init__(self, dim, hidden_dim, device=None, quant_config=None):
+    super().__init__()
+    self.w1 = WeightOnlyPerChannelQuantizedLinear(dim, hidden_dim, device=device, quant_config=quant_config)
+    self.w2 = WeightOnlyPerChannelQuantizedLinear(hidden_dim, dim, device=device, quant_config=quant_config)
+    self.w3 = WeightOnlyPerChannelQuantizedLinear(dim, hidden_dim, device=device, quant_config=quant_config)
+
+  def forward(self, x, levels=None):
+    if not ActivationLevels.fits(x):
+      return self.w2(silu_mul(self.w1(x), self.w3(x)))
+    if levels is None:
+      levels = ActivationLevels.of(x)
+    h, h_levels = silu_mul(self.w1(x, levels=levels), self.w3(x, levels=levels), with_levels=True)
+    return self.w2(h, levels=h_levels)

@@ -56,3 +56,24 @@ def w8a16_tolerance(x: torch.Tensor, w_q: torch.Tensor, scale: torch.Tensor):
   amax = x.to(torch.float64).abs().amax(dim=-1, keepdim=True)
   wsum = w_q.to(torch.float64).abs().sum(dim=1) * scale.to(torch.float64).abs()
   return exact.abs() * 2.0 ** -6 + amax * wsum * 2.0 ** -15
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float):
+  """`RMSNorm.forward`, jetstream_pt/layers.py:345-350, for bf16 x and a bf16
+  weight: the norm in fp32 (`x.float()`), rounded to x's dtype (`type_as`), times
+  the weight (bf16 product).  Pinned bit for bit against the reference's own class
+  (tests/golden/linear.npz)."""
+  xf = x.float()
+  normed = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).type_as(x)
+  return normed * weight
+
+
+def silu_mul(a: torch.Tensor, b: torch.Tensor):
+  """The gate of `FeedForward.forward`, third_party/llama/model_exportable.py:85:
+  `F.silu(a) * b` on bf16 tensors (each op rounds to bf16)."""
+  return torch.nn.functional.silu(a) * b
+
+
+def feed_forward(x, w1, s1, w2, s2, w3, s3):
+  """model_exportable.py:84-86 with the weight-only int8 layers."""
+  return w8a16_linear(silu_mul(w8a16_linear(x, w1, s1), w8a16_linear(x, w3, s3)), w2, s2)

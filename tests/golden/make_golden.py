@@ -488,6 +488,15 @@ def gen_linear(layers):
       out[f"{tag}_w"] = w  # (the float weight only where the quantiser is pinned: it is the bulk of the file)
     out.update({f"{tag}_x": x, f"{tag}_weight": lin.weight, f"{tag}_weight_scaler": lin.weight_scaler,
                 f"{tag}_y": y})
+  # RMSNorm (layers.py:337-350) as the model runs it in bf16: the weight converted like the other parameters
+  norm = layers.RMSNorm(512, eps=1e-5, device="cpu")
+  norm.weight = torch.nn.Parameter((1 + 0.1 * torch.randn(512, generator=g)).to(torch.bfloat16), requires_grad=False)
+  xn = randn(g, 2, 9, 512)
+  xn[0, 1] = 0
+  xn[0, 2] *= 50.0
+  yn = norm(xn)
+  assert yn.dtype == torch.bfloat16
+  out.update({"norm_x": xn, "norm_weight": norm.weight.data, "norm_eps": np.float32(1e-5), "norm_y": yn})
   save("linear", out)
 
 

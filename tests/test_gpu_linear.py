@@ -102,3 +102,86 @@ def test_linear_rejects_what_it_does_not_take():
     lin(torch.zeros(4, 256, dtype=torch.float32, device=DEV))
   with pytest.raises(NotImplementedError):
     WeightOnlyPerChannelQuantizedLinear(200, 128, device=DEV)
+
+
+def ulp_close(got, want, min_same):
+  """bf16 results of the same formula evaluated with another fp32 library (sum
+  order, rsqrt, exp): all but a few identical, none further than the
+  neighbouring bf16 value."""
+  gi, wi = got.view(torch.int16).int(), want.view(torch.int16).int()
+  same = (gi == wi).float().mean().item()
+  assert same >= min_same, same
+  assert (gi - wi).abs().max().item() <= 1
+
+
+def test_rmsnorm_against_the_reference_class():
+  from jetstream_pytorch_b200.layers import RMSNorm
+
+  g = load("linear")
+  x, w, eps, want = g["norm_x"], g["norm_weight"], float(g["norm_eps"]), g["norm_y"]
+  norm = RMSNorm(x.shape[-1], eps=eps, device=DEV)
+  norm.weight.data.copy_(w)
+  y = norm(x.to(DEV)).cpu()
+  assert y.shape == want.shape
+  ulp_close(y, want, 0.999)
+  assert not y[0, 1].any()
+  y2, lv = norm(x.to(DEV), with_levels=True)
+  assert torch.equal(y2.cpu(), y)
+  assert lv.rows == 18 and lv.features == 512
+
+
+@pytest.mark.parametrize("m,k", [(1, 128), (96, 8192), (37, 28672), (128, 1024)])
+def test_rmsnorm_and_silu_mul_shapes(m, k):
+  from jetstream_pytorch_b200.layers import RMSNorm, silu_mul
+
+  g = torch.Generator().manual_seed(k + m)
+  x = (torch.randn(m, k, generator=g) * 3).to(torch.bfloat16)
+  w = (1 + 0.2 * torch.randn(k, generator=g)).to(torch.bfloat16)
+  norm = RMSNorm(k, eps=1e-5, device=DEV)
+  norm.weight.data.copy_(w)
+  ulp_close(norm(x.to(DEV)).cpu(), ol.rmsnorm(x, w, 1e-5), 0.999)
+  b = torch.randn(m, k, generator=g).to(torch.bfloat16)
+  ulp_close(silu_mul(x.to(DEV), b.to(DEV)).cpu(), ol.silu_mul(x, b), 0.999)
+  # more rows than levels are kept for: the plain kernels take any number
+  if m == 1:
+    xx = x.repeat(300, 1)
+    assert torch.equal(norm(xx.to(DEV)).cpu(), norm(x.to(DEV)).cpu().repeat(300, 1))
+
+
+def test_levels_from_the_producers_equal_the_layer_s_own_split():
+  """A linear layer fed with the levels that RMSNorm, the gate or
+  `ActivationLevels.of` left behind returns what it returns on the bf16 tensor
+  itself, bit for bit; the feed-forward block equals its three layers and the gate
+  called one by one, and the oracle within the layers' tolerance."""
+  from jetstream_pytorch_b200.layers import ActivationLevels, FeedForward, RMSNorm, silu_mul
+
+  g = torch.Generator().manual_seed(77)
+  m, dim, hidden = 96, 1024, 2816
+  ff = FeedForward(dim, hidden, device=DEV)
+  ws = {}
+  for name, (n, k) in (("w1", (hidden, dim)), ("w2", (dim, hidden)), ("w3", (hidden, dim))):
+    wq, sc = ol.quantize_weight(torch.randn(n, k, generator=g) * 0.03)
+    getattr(ff, name)._load_quantized_weights(wq, sc)
+    ws[name] = (wq, sc)
+  x = torch.randn(3, 32, dim, generator=g).to(torch.bfloat16)
+  norm = RMSNorm(dim, eps=1e-5, device=DEV)
+  norm.weight.data.copy_((1 + 0.1 * torch.randn(dim, generator=g)).to(torch.bfloat16))
+  xd = x.to(DEV)
+  y, lv = norm(xd, with_levels=True)
+  assert torch.equal(ff.w1(y, levels=lv), ff.w1(y))
+  assert torch.equal(ff.w3(y, levels=ActivationLevels.of(y)), ff.w3(y))
+  a, b = ff.w1(y), ff.w3(y)
+  h, hl = silu_mul(a, b, with_levels=True)
+  assert torch.equal(h, silu_mul(a, b))
+  assert torch.equal(ff.w2(h, levels=hl), ff.w2(h))
+  out = ff(y, levels=lv)
+  assert torch.equal(out, ff.w2(h)) and torch.equal(out, ff(y))
+  assert out.shape == (3, 32, dim)
+  torch.cuda.synchronize()
+  assert ff.w1.kernel_status() == 0 and ff.w2.kernel_status() == 0
+  # each step against the oracle on the step's own inputs
+  yc, ac, bc, hc = y.cpu().reshape(m, dim), a.cpu().reshape(m, hidden), b.cpu().reshape(m, hidden), h.cpu().reshape(m, hidden)
+  for got, xin, (wq, sc) in ((ac, yc, ws["w1"]), (bc, yc, ws["w3"]), (out.cpu().reshape(m, dim), hc, ws["w2"])):
+    err = (got.float() - ol.w8a16_linear(xin, wq, sc).float()).abs().double()
+    assert (err <= ol.w8a16_tolerance(xin, wq, sc)).all()
+  ulp_close(hc, ol.silu_mul(ac, bc), 0.999)

@@ -330,3 +330,13 @@ def test_w8a16_linear_against_the_reference_layer():
     # (the outputs that differ are sums that cancel to almost nothing, where the reference's float32
     # accumulation error shows; they stay far inside the absolute term of the tolerance)
     assert ((got.float() - want.float()).abs().double() <= ol.w8a16_tolerance(x, w, s)).all()
+
+
+def test_rmsnorm_against_the_reference_class():
+  """`linear.npz`: the reference's own `RMSNorm` on bf16 inputs with a bf16 weight, bit for bit."""
+  from oracle import linear as ol
+
+  g = load("linear")
+  y = ol.rmsnorm(g["norm_x"], g["norm_weight"], float(g["norm_eps"]))
+  assert y.dtype == torch.bfloat16 and torch.equal(y, g["norm_y"])
+  assert not g["norm_y"][0, 1].any()
