@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(kRowThreads) silu_mul_levels_kernel(const __nv
 // grid (ceil(N / 256), ksplit), clusters of (1, ksplit): the rank of a CTA in its cluster is its K split.
 __global__ void __launch_bounds__(kThreadsL, 1)
     w8a16_gemm_kernel(const __grid_constant__ LinearMaps maps, const float* xs, const __nv_bfloat16* scale, __nv_bfloat16* y,
-                      int M, int Mp, int N, int K, int k_per_split, int* status) {
+                      int M, int Mp, int N, int K, int k_tiles, int* status) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   SmemL& sm = *reinterpret_cast<SmemL*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -374,7 +374,9 @@ __global__ void __launch_bounds__(kThreadsL, 1)
     return;
   }
   const int n0 = blockIdx.x * kTileN, split = blockIdx.y;
-  const int k_begin = split * k_per_split, iters = k_per_split / kTileK;
+  // K steps of this split: the k_tiles steps dealt out as evenly as whole steps allow (the first splits one more)
+  const int nsplit = (int)gridDim.y, k_lo = split * (k_tiles / nsplit) + min(split, k_tiles % nsplit);
+  const int iters = k_tiles / nsplit + (split < k_tiles % nsplit ? 1 : 0), k_begin = k_lo * kTileK;
   const int n_mma = 2 * Mp;  // columns of the accumulator (a multiple of 16)
 
   if (tid == 0) {
@@ -550,7 +552,11 @@ __global__ void __launch_bounds__(kThreadsL, 1)
     switch (csize) {
       case 1: reduce(std::integral_constant<int, 1>{}); break;
       case 2: reduce(std::integral_constant<int, 2>{}); break;
+      case 3: reduce(std::integral_constant<int, 3>{}); break;
       case 4: reduce(std::integral_constant<int, 4>{}); break;
+      case 5: reduce(std::integral_constant<int, 5>{}); break;
+      case 6: reduce(std::integral_constant<int, 6>{}); break;
+      case 7: reduce(std::integral_constant<int, 7>{}); break;
       default: reduce(std::integral_constant<int, 8>{}); break;
     }
   }
@@ -592,15 +598,14 @@ int split_for(int N, int K) {
   cudaGetDevice(&dev);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   const int tiles = (N + kTileN - 1) / kTileN, k_tiles = K / kTileK;
-  // The K splits of a tile are the CTAs of one cluster (1, 2, 4 or 8).  The split with the shortest
-  // estimated run is taken: CTAs run in waves of one per SM; a CTA costs about 8 us of set-up, first
+  // The K splits of a tile are the CTAs of one cluster (1 .. 8; the K steps are dealt out evenly).  The split with
+  // the shortest estimated run is taken: CTAs run in waves of one per SM; a CTA costs about 8 us of set-up, first
   // fetch and epilogue plus 0.6 us per K step (measured on B200 for 96 rows).
   int split = 1;
   float best = 0.f;
-  for (int c = 1; c <= kMaxSplit && c <= k_tiles; c *= 2) {
-    if (k_tiles % c) break;
+  for (int c = 1; c <= kMaxSplit && c <= k_tiles; ++c) {
     const int waves = (tiles * c + sms - 1) / sms;
-    const float cost = (float)waves * (8.f + 0.6f * (float)(k_tiles / c));
+    const float cost = (float)waves * (8.f + 0.6f * (float)((k_tiles + c - 1) / c));
     if (c == 1 || cost < best) best = cost, split = c;
   }
   return split;
@@ -676,7 +681,7 @@ int launch_gemm(const LevelsView& lv, const void* w, const void* w_scale, void* 
   cfg.numAttrs = pdl_enabled() ? 2 : 1;  // (also inside a graph capture: the weight tiles stream in under the level kernel)
   const cudaError_t e = cudaLaunchKernelEx(&cfg, w8a16_gemm_kernel, maps, static_cast<const float*>(lv.xs),
                                            static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(y), M, lv.Mp, N, K,
-                                           K / ksplit, lv.status);
+                                           K / kTileK, lv.status);
   if (e != cudaSuccess) return fail((int)e, "w8a16_gemm_kernel: %s", cudaGetErrorString(e));
   return 0;
 }

@@ -49,11 +49,13 @@ def test_linear_against_the_reference_layer(tag):
 
 
 @pytest.mark.parametrize("m,k,n", [(1, 128, 128), (3, 256, 100), (8, 512, 384), (17, 1024, 1000), (96, 2048, 512),
-                                   (128, 1024, 256), (33, 8192, 640), (300, 512, 384)])
+                                   (128, 1024, 256), (33, 8192, 640), (300, 512, 384), (9, 384, 300), (9, 640, 300),
+                                   (96, 768, 520), (128, 896, 256), (96, 8192, 10240)])
 def test_linear_shapes(m, k, n):
   """Ragged batch sizes (padded to eight level rows), output channels that are
-  not a multiple of the 256-channel tile, K split over the CTAs of a cluster,
-  more than 128 rows (taken in blocks)."""
+  not a multiple of the 256-channel tile, K split over clusters of 1 to 8 CTAs
+  (3, 5, 6 and 7 K steps give clusters of that size; 10240 channels one of 3 with
+  uneven shares), more than 128 rows (taken in blocks)."""
   g = torch.Generator().manual_seed(m * 131 + n)
   w = torch.randn(n, k, generator=g) * 0.03
   w_q, scale = ol.quantize_weight(w)
