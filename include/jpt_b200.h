@@ -499,6 +499,37 @@ int jpt_rmsnorm(const void* x, const void* weight, float eps, void* y, int M,
 int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K,
                  void* levels_workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * The row-parallel form of the layer over the GPUs of one box: the input
+ * features are sharded (rank r holds x[:, K_r] and w[:, K_r], as `wo` and `w2`
+ * are in jetstream_pt/default_shardings/llama.yaml:10,20), and what GSPMD
+ * inserts behind the reference's matmul, an all-reduce of the partial results,
+ * happens inside the GEMM's epilogue: every CTA stores the fp32 sums of its
+ * rows into all ranks' receive buffers over NVLink (plain peer stores),
+ * announces them with the launch number, waits (bounded) for the same CTA of
+ * the other ranks and adds the partials in the order of the ranks; then the
+ * two bf16 roundings and the channel scale, as on one GPU.  Every rank gets the
+ * whole y.  M <= 128.  All ranks make the same sequence of calls with the same
+ * shapes; the calls are numbered on the device (a captured graph of them can be
+ * replayed), and two consecutive calls use the two halves of the buffers.
+ * Setting up: every rank allocates jpt_w8a16_tp_buffer_bytes(N_max, world)
+ * zero-filled bytes (jpt_peer_exchange_alloc), exports the handle and imports
+ * the others' (jpt_peer_exchange_export / _import), as for jpt_peer_exchange.
+ * jpt_w8a16_tp_status: 0, or 1 after a launch gave up on a peer (its y is then
+ * the sum of what had arrived).
+ */
+typedef struct jpt_tp_sum {
+  int rank, world;       /* 1 <= world <= 8 */
+  void* buffers[8];      /* buffers[rank] = own */
+  size_t buffer_bytes;   /* size of each */
+  long long wait_cycles; /* 0 = the default (about half a second) */
+} jpt_tp_sum;
+size_t jpt_w8a16_tp_buffer_bytes(int N, int world);
+int jpt_w8a16_linear_tp(const void* x, const void* w, const void* w_scale, void* y,
+                        int M, int N, int K, void* workspace, size_t workspace_bytes,
+                        const jpt_tp_sum* tp, void* stream);
+int jpt_w8a16_tp_status(const jpt_tp_sum* tp, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,6 +33,12 @@ class PeerExchangeStruct(ctypes.Structure):
               ("wait_cycles", ctypes.c_longlong)]
 
 
+class TpSumStruct(ctypes.Structure):
+  """Mirror of `struct jpt_tp_sum`."""
+  _fields_ = [("rank", c_int), ("world", c_int), ("buffers", c_void_p * 8), ("buffer_bytes", c_size_t),
+              ("wait_cycles", ctypes.c_longlong)]
+
+
 class AttnParams(ctypes.Structure):
   """Mirror of `struct jpt_attn_params`."""
 
@@ -95,6 +101,10 @@ _SIGNATURES = {
     "jpt_w8a16_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jpt_w8a16_split_levels": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jpt_w8a16_linear_from_levels": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "jpt_w8a16_tp_buffer_bytes": (c_size_t, [c_int, c_int]),
+    "jpt_w8a16_linear_tp": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t,
+                                    ctypes.POINTER(TpSumStruct), c_void_p]),
+    "jpt_w8a16_tp_status": (c_int, [ctypes.POINTER(TpSumStruct), c_void_p]),
     "jpt_rmsnorm": (c_int, [c_void_p, c_void_p, ctypes.c_float, c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jpt_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "jpt_quantize_tokens": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

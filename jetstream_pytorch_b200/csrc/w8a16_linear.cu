@@ -59,6 +59,31 @@ struct LinearMaps {
   CUtensorMap w, x;
 };
 
+// Row-parallel layer over the GPUs of one box (the input features are sharded: every rank holds x[:, K_r] and
+// W[:, K_r], the result is the sum over the ranks).  buffers[r] is rank r's receive buffer (own or an IPC
+// mapping): launch numbers [2 (launch parity)][8 (source rank)][1024 (tile)][8 (K split)] u32, a status word,
+// then fp32 partial sums [2][world][128][N].  world = 1: a layer of one GPU.
+struct TpArgs {
+  int world, rank;
+  // number of this launch (the same on every rank): counted on the device by the level kernel in front of the GEMM,
+  // so that a captured graph can be replayed
+  unsigned* launch_counter;
+  long long wait_cycles;
+  char* buffers[8];
+  int* status;  // in the rank's own buffer: raised when a wait for a peer ran out
+};
+constexpr int kTpMaxTiles = 1024;
+constexpr size_t kTpFlagBytes = (size_t)2 * 8 * kTpMaxTiles * 8 * sizeof(unsigned);
+constexpr size_t kTpDataOffset = kTpFlagBytes + 256;
+__device__ __forceinline__ void st_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -128,11 +153,12 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t addr, uint32_t (&v)[32]) {
 // x [M, K] bf16 -> levels [2 Mp, K] int8 (rows 0 .. M-1: h, rows Mp .. Mp+M-1: l, the others zero)
 // and xs[m] = s_m / 254.
 __global__ void __launch_bounds__(256) x_levels_kernel(const __nv_bfloat16* x, int8_t* lev, float* xs, int* status, int M,
-                                                       int Mp, int K, int clear_status) {
+                                                       int Mp, int K, int clear_status, unsigned* launch_counter) {
   __shared__ float red[33];
   const int m = blockIdx.x, tid = threadIdx.x;  // one CTA per row of the padded batch
   grid_dependency_trigger();
   if (m == 0 && tid == 0 && clear_status) *status = 0;
+  if (m == 0 && tid == 0 && launch_counter) *launch_counter += 1u;  // (one thread, launches in stream order)
   uint2* hrow = reinterpret_cast<uint2*>(lev + (int64_t)m * K);
   uint2* lrow = reinterpret_cast<uint2*>(lev + (int64_t)(Mp + m) * K);
   const int nvec = K / 8;  // eight elements per step: 16 bytes in, 8 + 8 bytes out
@@ -364,7 +390,7 @@ __global__ void __launch_bounds__(kRowThreads) silu_mul_levels_kernel(const __nv
 // grid (ceil(N / 256), ksplit), clusters of (1, ksplit): the rank of a CTA in its cluster is its K split.
 __global__ void __launch_bounds__(kThreadsL, 1)
     w8a16_gemm_kernel(const __grid_constant__ LinearMaps maps, const float* xs, const __nv_bfloat16* scale, __nv_bfloat16* y,
-                      int M, int Mp, int N, int K, int k_tiles, int* status) {
+                      int M, int Mp, int N, int K, int k_tiles, int* status, const __grid_constant__ TpArgs tp) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   SmemL& sm = *reinterpret_cast<SmemL*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -408,6 +434,7 @@ __global__ void __launch_bounds__(kThreadsL, 1)
   }
   grid_dependency_wait();
   grid_dependency_trigger();
+  const unsigned tp_epoch = tp.world > 1 ? *reinterpret_cast<volatile unsigned*>(tp.launch_counter) : 0u;
   sm.xs[tid] = tid < M ? xs[tid] : 0.f;
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -537,6 +564,24 @@ __global__ void __launch_bounds__(kThreadsL, 1)
             for (int r = 0; r < 8; ++r) acc[half][r] += land[(((src * owned + q) * 2 + half) * 8 + r) * kThreadsL + tid];
           }
         }
+        if (tp.world > 1) {
+          // this rank's sums of the group go to every rank's receive buffer (its own included); the roundings follow
+          // below, on the sum over the ranks
+          const int64_t src_rows = ((int64_t)(tp_epoch & 1u) * tp.world + tp.rank) * kMaxM;
+          for (int d = 0; d < tp.world; ++d) {
+            float* dst = reinterpret_cast<float*>(tp.buffers[d] + kTpDataOffset);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int n = n0 + half * 128 + tid;
+#pragma unroll
+              for (int r = 0; r < 8; ++r) {
+                const int m = 8 * j + r;
+                if (m < M && n < N) __stcg(&dst[(src_rows + m) * N + n], acc[half][r]);
+              }
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int n = n0 + half * 128 + tid;
@@ -558,6 +603,59 @@ __global__ void __launch_bounds__(kThreadsL, 1)
       case 6: reduce(std::integral_constant<int, 6>{}); break;
       case 7: reduce(std::integral_constant<int, 7>{}); break;
       default: reduce(std::integral_constant<int, 8>{}); break;
+    }
+    if (tp.world > 1 && split < groups) {  // (a CTA without a group of rows has nothing to send or to wait for)
+      // ---- sum over the ranks: tell every rank that this CTA's groups are in its buffer, wait for the same CTA of
+      // every rank, add the partial sums in the order of the ranks
+      const int par = (int)(tp_epoch & 1u);
+      auto flag_of = [&](int owner, int src) {
+        return reinterpret_cast<unsigned*>(tp.buffers[owner]) + (((size_t)par * 8 + src) * kTpMaxTiles + blockIdx.x) * 8 + split;
+      };
+      __syncthreads();  // every thread's stores are issued ...
+      if (tid < tp.world) {
+        __threadfence_system();  // ... and ordered before the launch number that announces them
+        st_sys_u32(flag_of(tid, tp.rank), tp_epoch);
+      }
+      if (tid < tp.world) {
+        const long long t0c = clock64();
+        while (ld_sys_u32(flag_of(tp.rank, tid)) != tp_epoch) {
+          if (clock64() - t0c > tp.wait_cycles) {  // a rank never came: report, go on with what is there
+            atomicExch(tp.status, 1);
+            break;
+          }
+        }
+        __threadfence_system();
+      }
+      __syncthreads();
+      const float* mine = reinterpret_cast<const float*>(tp.buffers[tp.rank] + kTpDataOffset) + (int64_t)par * tp.world * kMaxM * N;
+      for (int q = 0; q < owned; ++q) {
+        const int j = q * csize + split;
+        if (j >= groups) break;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int n = n0 + half * 128 + tid;
+          if (n >= N) continue;
+          float sum[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int m = min(8 * j + r, M - 1);
+            sum[r] = __ldcg(&mine[(int64_t)m * N + n]);
+          }
+          for (int src = 1; src < tp.world; ++src) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              const int m = min(8 * j + r, M - 1);
+              sum[r] += __ldcg(&mine[((int64_t)src * kMaxM + m) * N + n]);
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const int m = 8 * j + r;
+            const float dot = __bfloat162float(__float2bfloat16_rn(sum[r]));
+            if (m < M) y[(int64_t)m * N + n] = __float2bfloat16_rn(dot * sc[half]);
+          }
+        }
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -647,8 +745,13 @@ LevelsView levels_view(void* workspace, int M, int K) {
 
 // The GEMM on levels that a launch before this one in the stream wrote.  The launch may start while that one
 // drains (it requests its first weight tiles at once) and waits for its results on the device.
-int launch_gemm(const LevelsView& lv, const void* w, const void* w_scale, void* y, int M, int N, int K, cudaStream_t st) {
+int launch_gemm(const LevelsView& lv, const void* w, const void* w_scale, void* y, int M, int N, int K, cudaStream_t st,
+                const TpArgs* tp_in = nullptr) {
   const int ksplit = split_for(N, K);
+  TpArgs tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.world = 1;
+  if (tp_in) tp = *tp_in;
   static std::mutex mu;
   LinearMaps maps;
   memset(&maps, 0, sizeof(maps));
@@ -681,15 +784,16 @@ int launch_gemm(const LevelsView& lv, const void* w, const void* w_scale, void* 
   cfg.numAttrs = pdl_enabled() ? 2 : 1;  // (also inside a graph capture: the weight tiles stream in under the level kernel)
   const cudaError_t e = cudaLaunchKernelEx(&cfg, w8a16_gemm_kernel, maps, static_cast<const float*>(lv.xs),
                                            static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(y), M, lv.Mp, N, K,
-                                           K / kTileK, lv.status);
+                                           K / kTileK, lv.status, tp);
   if (e != cudaSuccess) return fail((int)e, "w8a16_gemm_kernel: %s", cudaGetErrorString(e));
   return 0;
 }
 
 // (the level kernel also clears the status word and the padding rows of the level matrix)
-int launch_levels(const void* x, const LevelsView& lv, int M, int K, cudaStream_t st, bool clear_status) {
+int launch_levels(const void* x, const LevelsView& lv, int M, int K, cudaStream_t st, bool clear_status,
+                  unsigned* launch_counter = nullptr) {
   x_levels_kernel<<<lv.Mp, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), lv.lev, lv.xs, lv.status, M, lv.Mp, K,
-                                         clear_status ? 1 : 0);
+                                         clear_status ? 1 : 0, launch_counter);
   return check_launch("x_levels_kernel");
 }
 
@@ -800,4 +904,45 @@ extern "C" int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K,
   const LevelsView lv = levels_view(levels_workspace, M, K);
   return launch_rows("silu_mul_levels_kernel", silu_mul_levels_kernel, lv.Mp, row_parts(lv.Mp, K), st, ap, bp,
                      static_cast<__nv_bfloat16*>(h), lv.lev, lv.xs, lv.status, M, lv.Mp, K);
+}
+
+extern "C" size_t jpt_w8a16_tp_buffer_bytes(int N, int world) {
+  if (N < 1 || world < 1 || world > 8 || (N + kTileN - 1) / kTileN > kTpMaxTiles) return 0;
+  return kTpDataOffset + (size_t)2 * world * kMaxM * N * sizeof(float);
+}
+
+extern "C" int jpt_w8a16_linear_tp(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K, void* workspace,
+                                   size_t workspace_bytes, const jpt_tp_sum* tp, void* stream) {
+  JPT_REQUIRE(x && w && w_scale && y && tp, JPT_EINVAL, "w8a16_linear_tp: null argument");
+  JPT_REQUIRE(N >= 1 && aligned(x, 16) && aligned(w, 16), JPT_EALIGN, "w8a16_linear_tp: x and w must be 16-byte aligned");
+  JPT_REQUIRE(tp->world >= 1 && tp->world <= 8 && tp->rank >= 0 && tp->rank < tp->world, JPT_EINVAL,
+              "w8a16_linear_tp: rank %d of %d", tp->rank, tp->world);
+  JPT_REQUIRE(tp->buffer_bytes >= jpt_w8a16_tp_buffer_bytes(N, tp->world) && jpt_w8a16_tp_buffer_bytes(N, tp->world) > 0, JPT_EWORKSPACE,
+              "w8a16_linear_tp: receive buffers of %zu bytes are too small for N = %d on %d ranks", tp->buffer_bytes, N, tp->world);
+  if (int rc = check_levels_args("w8a16_linear_tp", M, K, workspace, workspace_bytes)) return rc;
+  TpArgs t;
+  memset(&t, 0, sizeof(t));
+  t.world = tp->world;
+  t.rank = tp->rank;
+  t.wait_cycles = tp->wait_cycles > 0 ? tp->wait_cycles : kWaitCyclesL;
+  for (int r = 0; r < tp->world; ++r) {
+    JPT_REQUIRE(tp->buffers[r], JPT_EINVAL, "w8a16_linear_tp: no buffer for rank %d", r);
+    t.buffers[r] = static_cast<char*>(tp->buffers[r]);
+  }
+  t.status = reinterpret_cast<int*>(t.buffers[t.rank] + kTpFlagBytes);
+  t.launch_counter = reinterpret_cast<unsigned*>(t.buffers[t.rank] + kTpFlagBytes + 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const LevelsView lv = levels_view(workspace, M, K);
+  if (int rc = launch_levels(x, lv, M, K, st, true, t.launch_counter)) return rc;
+  return launch_gemm(lv, w, w_scale, y, M, N, K, st, &t);
+}
+
+extern "C" int jpt_w8a16_tp_status(const jpt_tp_sum* tp, void* stream) {
+  JPT_REQUIRE(tp && tp->buffers[tp->rank], JPT_EINVAL, "w8a16_tp_status: null buffer");
+  int v = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&v, static_cast<const char*>(tp->buffers[tp->rank]) + kTpFlagBytes, sizeof(v), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail((int)e, "w8a16_tp_status: %s", cudaGetErrorString(e));
+  return v;
 }

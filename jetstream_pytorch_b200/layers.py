@@ -13,6 +13,8 @@ its activations in a decoder block; for decode batches they hand the int8 level
 split of their results (`ActivationLevels`) to the linear layers behind them.
 """
 
+import ctypes
+
 import torch
 
 from jetstream_pytorch_b200 import _lib
@@ -187,9 +189,14 @@ class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
     """0, or 1 if a bounded wait inside the last launch gave up (synchronises)."""
     return 0 if self._workspace is None else int(self._workspace[:4].view(torch.int32).item())
 
-  def forward(self, inputs, levels=None):
+  def forward(self, inputs, levels=None, tp=None):
     """`levels` (an `ActivationLevels` of `inputs`, from `RMSNorm`, `FeedForward`
-    or `ActivationLevels.of`): the layer starts at its GEMM."""
+    or `ActivationLevels.of`): the layer starts at its GEMM.
+    `tp` (a `TensorParallelSum`): this rank holds a slice of the input features
+    (`weight` [out, in / world], `inputs` [..., in / world]); the partial results
+    of the ranks are added inside the kernel and every rank gets the whole
+    output (the all-reduce behind `wo` and `w2` of the reference's sharding,
+    default_shardings/llama.yaml:10,20)."""
     if inputs.dtype != torch.bfloat16:
       raise NotImplementedError(f"activations must be bfloat16, got {inputs.dtype}")
     k, n = self.in_features, self.out_features
@@ -197,6 +204,19 @@ class WeightOnlyPerChannelQuantizedLinear(torch.nn.Module):
     m = x.shape[0]
     if m < 1:
       return inputs.new_empty((*inputs.shape[:-1], n))
+    if tp is not None:
+      if levels is not None or m > ActivationLevels.MAX_ROWS:
+        raise NotImplementedError("the row-parallel form takes up to 128 rows of bf16 activations")
+      x = x.contiguous()
+      lib = _lib.lib()
+      need = lib.jpt_w8a16_linear_workspace_bytes(m, n, k)
+      if self._workspace is None or self._workspace.numel() < need or self._workspace.device != x.device:
+        self._workspace = torch.empty((need,), dtype=torch.uint8, device=x.device)
+      y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+      _lib.check(lib.jpt_w8a16_linear_tp(_lib.ptr(x), _lib.ptr(self.weight), _lib.ptr(self.weight_scaler), _lib.ptr(y), m, n, k,
+                                         _lib.ptr(self._workspace), self._workspace.numel(), ctypes.byref(tp.struct),
+                                         _lib.stream()))
+      return y.reshape(*inputs.shape[:-1], n)
     if levels is not None:
       if (levels.rows, levels.features) != (m, k):
         raise ValueError(f"levels of a [{levels.rows}, {levels.features}] activation given for [{m}, {k}]")
@@ -305,3 +325,66 @@ class FeedForward(torch.nn.Module):
       levels = ActivationLevels.of(x)
     h, h_levels = silu_mul(self.w1(x, levels=levels), self.w3(x, levels=levels), with_levels=True)
     return self.w2(h, levels=h_levels)
+
+
+class TensorParallelSum:
+  """Receive buffers for the sum of the row-parallel linear layers' partial
+  results over the GPUs of one box (`WeightOnlyPerChannelQuantizedLinear.forward(
+  ..., tp=...)`): every rank allocates one buffer, exports its CUDA IPC handle and
+  opens the others'.  `handles_all_gather(handle) -> [handle of rank 0, ...]` is
+  any host-side all-gather of 64-byte strings.  All ranks must then make the same
+  sequence of calls with the same shapes; one object serves every layer whose
+  output has at most `max_out_features` channels."""
+
+  def __init__(self, max_out_features, rank, world_size, handles_all_gather, wait_cycles=0):
+    lib = _lib.lib()
+    nbytes = lib.jpt_w8a16_tp_buffer_bytes(max_out_features, world_size)
+    if nbytes == 0:
+      raise ValueError(f"no row-parallel sum for {max_out_features} channels on {world_size} ranks (1..8 ranks)")
+    own = ctypes.c_void_p()
+    _lib.check(lib.jpt_peer_exchange_alloc(nbytes, ctypes.byref(own)))
+    self._own = own
+    handle = ctypes.create_string_buffer(64)
+    _lib.check(lib.jpt_peer_exchange_export(own, handle))
+    handles = handles_all_gather(handle.raw)
+    self.struct = _lib.TpSumStruct()
+    self.struct.rank, self.struct.world = rank, world_size
+    self.struct.buffer_bytes = nbytes
+    self.struct.wait_cycles = int(wait_cycles)
+    self._opened = []
+    for r in range(world_size):
+      if r == rank:
+        self.struct.buffers[r] = own.value
+      else:
+        peer = ctypes.c_void_p()
+        _lib.check(lib.jpt_peer_exchange_import(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(peer)))
+        self._opened.append(peer)
+        self.struct.buffers[r] = peer.value
+
+  @classmethod
+  def with_torch_distributed(cls, max_out_features, wait_cycles=0):
+    import torch.distributed as dist
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+
+    def gather(h):
+      out = [None] * world
+      dist.all_gather_object(out, h)
+      return out
+
+    tp = cls(max_out_features, rank, world, gather, wait_cycles)
+    dist.barrier()  # every rank has opened every buffer before anybody launches
+    return tp
+
+  def status(self):
+    """0 while every wait of every launch was satisfied; 1 after a launch gave up on a peer."""
+    return _lib.lib().jpt_w8a16_tp_status(ctypes.byref(self.struct), _lib.stream())
+
+  def close(self):
+    lib = _lib.lib()
+    for p in self._opened:
+      lib.jpt_peer_exchange_release(p)
+    self._opened = []
+    if self._own is not None:
+      lib.jpt_peer_exchange_free(self._own)
+      self._own = None
