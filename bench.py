@@ -622,6 +622,74 @@ def extra_w8a16_linear(dev, peak, reps, eager=False):
   return out
 
 
+def linear_tp(dev, peak, reps, rank, world):
+  """The row-parallel projections of the bench model (`wo` 8192 -> 8192, `w2`
+  28672 -> 8192) at batch 96 with their input features sharded over the ranks:
+  the sum over the ranks inside the GEMM's epilogue (peer stores over NVLink)
+  against the same GEMM followed by an NCCL all-reduce of its bf16 result.
+  Times are the maximum over the ranks; bytes are one rank's."""
+  import torch.distributed as dist
+
+  from jetstream_pytorch_b200.layers import TensorParallelSum, WeightOnlyPerChannelQuantizedLinear
+
+  out = {}
+  tp = TensorParallelSum.with_torch_distributed(8192) if world > 1 else TensorParallelSum(8192, 0, 1, lambda h: [h])
+  gen = torch.Generator(device=dev).manual_seed(1007 + rank)
+
+  def max_over_ranks(ms):
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+  for name, k_all, n in (("wo_8192x8192", 8192, 8192), ("w_down_28672x8192", 28672, 8192)):
+    k = k_all // world
+    sets = max(3, int(300e6 // (k * n)) + 1)
+    layers = []
+    for _ in range(sets):
+      lin = WeightOnlyPerChannelQuantizedLinear(k, n, device=dev)
+      lin._load_quantized_weights(torch.randint(-127, 128, (n, k), generator=gen, dtype=torch.int8, device=dev),
+                                  torch.full((n,), 0.002, device=dev))
+      layers.append(lin)
+    x = torch.randn((B, k), generator=gen, device=dev).to(torch.bfloat16)
+
+    def fused():
+      for lin in layers:
+        lin(x, tp=tp)
+
+    def with_nccl():
+      for lin in layers:
+        y = lin(x)
+        if world > 1:
+          dist.all_reduce(y)
+
+    entry = {}
+    for label, fn in (("sum_in_kernel", fused), ("gemm_then_nccl_all_reduce", with_nccl)):
+      if world > 1:
+        dist.barrier()
+      try:
+        ms = time_replays(graph_of(fn).replay, reps)
+        how = "graph"
+      except Exception as e:  # pylint: disable=broad-except
+        torch.cuda.synchronize()
+        fn()
+        ms = time_replays(fn, reps)
+        how = f"eager ({type(e).__name__})"
+      entry[label] = {"us_per_layer": max_over_ranks(ms) * 1e3 / sets, "launches": how}
+    nbytes = n * k + B * k * 2 + B * n * 2 + n * 2
+    us = entry["sum_in_kernel"]["us_per_layer"]
+    entry.update(algorithmic_bytes_per_rank=int(nbytes), achieved_gbs_per_rank=nbytes / us / 1e3, frac=nbytes / us / 1e3 / peak,
+                 nvlink_bytes_out_per_rank=int((world - 1) * B * n * 4), rotating_weight_sets=sets,
+                 kernel_status=max(lin.kernel_status() for lin in layers), tp_status=tp.status())
+    out[name] = entry
+    del layers
+    torch.cuda.empty_cache()
+  if world > 1:
+    dist.barrier()
+  tp.close()
+  return out
+
+
 # ---------------------------------------------------------------------------
 # CUDA arm
 # ---------------------------------------------------------------------------
@@ -656,6 +724,14 @@ def run_cuda(args):
     return
   if args.only == "peer-insert":
     print(json.dumps({"only": "peer-insert", **peer_insert(args.steps, nl=min(32, nl))}), flush=True)
+    return
+  if args.only == "linear-tp":
+    res = linear_tp(dev, peak, args.steps, rank, world)
+    if rank == 0:
+      print(json.dumps({"only": "linear-tp", "n_gpus": world, **res}), flush=True)
+    if world > 1:
+      dist.barrier()
+      dist.destroy_process_group()
     return
   if args.only == "linear":
     print(json.dumps({"only": "linear", **extra_w8a16_linear(dev, peak, args.steps, eager=True)}), flush=True)
@@ -1086,7 +1162,7 @@ def main():
   ap.add_argument("--no-extras", action="store_true", help="skip the other workloads' kernels (N = 1 runs them by default)")
   ap.add_argument("--amax-exchange", choices=["peers", "nccl"], default="peers",
                   help="N > 1: how the per-token amax is max-reduced over the ranks")
-  ap.add_argument("--only", choices=["attention", "append", "insert", "peer-insert", "linear"], default=None,
+  ap.add_argument("--only", choices=["attention", "append", "insert", "peer-insert", "linear", "linear-tp"], default=None,
                   help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
   ap.add_argument("--kv", choices=["int8", "bf16"], default="int8", help="with --only attention: cache dtype")
   ap.add_argument("--attn-kernel", choices=["auto", "mma"], default="auto",
