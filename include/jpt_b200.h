@@ -505,9 +505,11 @@ int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K,
  * are in jetstream_pt/default_shardings/llama.yaml:10,20), and what GSPMD
  * inserts behind the reference's matmul, an all-reduce of the partial results,
  * happens inside the GEMM's epilogue: every CTA stores the fp32 sums of its
- * rows into all ranks' receive buffers over NVLink (plain peer stores),
- * announces them with the launch number, waits (bounded) for the same CTA of
- * the other ranks and adds the partials in the order of the ranks; then the
+ * rows into all ranks' receive buffers over NVLink (plain peer stores of
+ * 8-byte words: the value and the number of the launch, so that a word that
+ * shows this launch's number is complete and needs no fence or flag), reads
+ * the words of the other ranks for the same rows (bounded wait for those that
+ * have not arrived) and adds the partials in the order of the ranks; then the
  * two bf16 roundings and the channel scale, as on one GPU.  Every rank gets the
  * whole y.  M <= 128.  All ranks make the same sequence of calls with the same
  * shapes; the calls are numbered on the device (a captured graph of them can be

@@ -61,8 +61,10 @@ struct LinearMaps {
 
 // Row-parallel layer over the GPUs of one box (the input features are sharded: every rank holds x[:, K_r] and
 // W[:, K_r], the result is the sum over the ranks).  buffers[r] is rank r's receive buffer (own or an IPC
-// mapping): launch numbers [2 (launch parity)][8 (source rank)][1024 (tile)][8 (K split)] u32, a status word,
-// then fp32 partial sums [2][world][128][N].  world = 1: a layer of one GPU.
+// mapping): a status word and the launch counter, then [2 (launch parity)][world (source rank)][128][N] words of
+// eight bytes, each an fp32 partial sum with the number of the launch that wrote it.  A word travels as one
+// 8-byte store, so a reader that sees the launch number has the value: no fence and no separate flag lie between
+// a rank's sums and their use on another rank.  world = 1: a layer of one GPU.
 struct TpArgs {
   int world, rank;
   // number of this launch (the same on every rank): counted on the device by the level kernel in front of the GEMM,
@@ -72,15 +74,13 @@ struct TpArgs {
   char* buffers[8];
   int* status;  // in the rank's own buffer: raised when a wait for a peer ran out
 };
-constexpr int kTpMaxTiles = 1024;
-constexpr size_t kTpFlagBytes = (size_t)2 * 8 * kTpMaxTiles * 8 * sizeof(unsigned);
-constexpr size_t kTpDataOffset = kTpFlagBytes + 256;
-__device__ __forceinline__ void st_sys_u32(unsigned* p, unsigned v) {
-  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+constexpr size_t kTpDataOffset = 256;
+__device__ __forceinline__ void st_sys_word(uint2* p, float v, unsigned launch) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(launch) : "memory");
 }
-__device__ __forceinline__ unsigned ld_sys_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_sys_word(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
 
@@ -569,14 +569,14 @@ __global__ void __launch_bounds__(kThreadsL, 1)
           // below, on the sum over the ranks
           const int64_t src_rows = ((int64_t)(tp_epoch & 1u) * tp.world + tp.rank) * kMaxM;
           for (int d = 0; d < tp.world; ++d) {
-            float* dst = reinterpret_cast<float*>(tp.buffers[d] + kTpDataOffset);
+            uint2* dst = reinterpret_cast<uint2*>(tp.buffers[d] + kTpDataOffset);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               const int n = n0 + half * 128 + tid;
 #pragma unroll
               for (int r = 0; r < 8; ++r) {
                 const int m = 8 * j + r;
-                if (m < M && n < N) __stcg(&dst[(src_rows + m) * N + n], acc[half][r]);
+                if (m < M && n < N) st_sys_word(&dst[(src_rows + m) * N + n], acc[half][r], tp_epoch);
               }
             }
           }
@@ -605,29 +605,11 @@ __global__ void __launch_bounds__(kThreadsL, 1)
       default: reduce(std::integral_constant<int, 8>{}); break;
     }
     if (tp.world > 1 && split < groups) {  // (a CTA without a group of rows has nothing to send or to wait for)
-      // ---- sum over the ranks: tell every rank that this CTA's groups are in its buffer, wait for the same CTA of
-      // every rank, add the partial sums in the order of the ranks
+      // ---- sum over the ranks: every thread reads the words of its own elements from every rank (a word whose
+      // launch number is not this launch's has not arrived yet: bounded wait) and adds them in the order of the ranks
       const int par = (int)(tp_epoch & 1u);
-      auto flag_of = [&](int owner, int src) {
-        return reinterpret_cast<unsigned*>(tp.buffers[owner]) + (((size_t)par * 8 + src) * kTpMaxTiles + blockIdx.x) * 8 + split;
-      };
-      __syncthreads();  // every thread's stores are issued ...
-      if (tid < tp.world) {
-        __threadfence_system();  // ... and ordered before the launch number that announces them
-        st_sys_u32(flag_of(tid, tp.rank), tp_epoch);
-      }
-      if (tid < tp.world) {
-        const long long t0c = clock64();
-        while (ld_sys_u32(flag_of(tp.rank, tid)) != tp_epoch) {
-          if (clock64() - t0c > tp.wait_cycles) {  // a rank never came: report, go on with what is there
-            atomicExch(tp.status, 1);
-            break;
-          }
-        }
-        __threadfence_system();
-      }
-      __syncthreads();
-      const float* mine = reinterpret_cast<const float*>(tp.buffers[tp.rank] + kTpDataOffset) + (int64_t)par * tp.world * kMaxM * N;
+      const uint2* mine = reinterpret_cast<const uint2*>(tp.buffers[tp.rank] + kTpDataOffset) + (int64_t)par * tp.world * kMaxM * N;
+      bool gave_up = false;
       for (int q = 0; q < owned; ++q) {
         const int j = q * csize + split;
         if (j >= groups) break;
@@ -637,15 +619,28 @@ __global__ void __launch_bounds__(kThreadsL, 1)
           if (n >= N) continue;
           float sum[8];
 #pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const int m = min(8 * j + r, M - 1);
-            sum[r] = __ldcg(&mine[(int64_t)m * N + n]);
-          }
-          for (int src = 1; src < tp.world; ++src) {
+          for (int r = 0; r < 8; ++r) sum[r] = 0.f;
+          for (int src = 0; src < tp.world; ++src) {
+            uint2 wv[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
               const int m = min(8 * j + r, M - 1);
-              sum[r] += __ldcg(&mine[((int64_t)src * kMaxM + m) * N + n]);
+              wv[r] = ld_sys_word(&mine[((int64_t)src * kMaxM + m) * N + n]);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (wv[r].y != tp_epoch && !gave_up) {  // not there yet
+                const int m = min(8 * j + r, M - 1);
+                const long long t0c = clock64();
+                do {
+                  wv[r] = ld_sys_word(&mine[((int64_t)src * kMaxM + m) * N + n]);
+                  if (clock64() - t0c > tp.wait_cycles) {  // a rank never came: report, go on with what is there
+                    gave_up = true;
+                    break;
+                  }
+                } while (wv[r].y != tp_epoch);
+              }
+              sum[r] += wv[r].y == tp_epoch ? __uint_as_float(wv[r].x) : 0.f;
             }
           }
 #pragma unroll
@@ -656,6 +651,7 @@ __global__ void __launch_bounds__(kThreadsL, 1)
           }
         }
       }
+      if (gave_up) atomicExch(tp.status, 1);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -907,8 +903,8 @@ extern "C" int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K,
 }
 
 extern "C" size_t jpt_w8a16_tp_buffer_bytes(int N, int world) {
-  if (N < 1 || world < 1 || world > 8 || (N + kTileN - 1) / kTileN > kTpMaxTiles) return 0;
-  return kTpDataOffset + (size_t)2 * world * kMaxM * N * sizeof(float);
+  if (N < 1 || world < 1 || world > 8) return 0;
+  return kTpDataOffset + (size_t)2 * world * kMaxM * N * sizeof(uint2);
 }
 
 extern "C" int jpt_w8a16_linear_tp(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K, void* workspace,
@@ -929,8 +925,8 @@ extern "C" int jpt_w8a16_linear_tp(const void* x, const void* w, const void* w_s
     JPT_REQUIRE(tp->buffers[r], JPT_EINVAL, "w8a16_linear_tp: no buffer for rank %d", r);
     t.buffers[r] = static_cast<char*>(tp->buffers[r]);
   }
-  t.status = reinterpret_cast<int*>(t.buffers[t.rank] + kTpFlagBytes);
-  t.launch_counter = reinterpret_cast<unsigned*>(t.buffers[t.rank] + kTpFlagBytes + 8);
+  t.status = reinterpret_cast<int*>(t.buffers[t.rank]);
+  t.launch_counter = reinterpret_cast<unsigned*>(t.buffers[t.rank] + 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const LevelsView lv = levels_view(workspace, M, K);
   if (int rc = launch_levels(x, lv, M, K, st, true, t.launch_counter)) return rc;
@@ -941,7 +937,7 @@ extern "C" int jpt_w8a16_tp_status(const jpt_tp_sum* tp, void* stream) {
   JPT_REQUIRE(tp && tp->buffers[tp->rank], JPT_EINVAL, "w8a16_tp_status: null buffer");
   int v = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemcpyAsync(&v, static_cast<const char*>(tp->buffers[tp->rank]) + kTpFlagBytes, sizeof(v), cudaMemcpyDeviceToHost, st);
+  cudaError_t e = cudaMemcpyAsync(&v, static_cast<const char*>(tp->buffers[tp->rank]), sizeof(v), cudaMemcpyDeviceToHost, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return fail((int)e, "w8a16_tp_status: %s", cudaGetErrorString(e));
   return v;

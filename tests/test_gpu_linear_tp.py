@@ -91,11 +91,13 @@ def _worker(rank, world, port, out_path):
   dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_sum_inside_the_kernel(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_sum_inside_the_kernel(tmp_path, world):
+  """Two ranks exchange their partial sums; with four a tile's owner adds them and returns the result."""
   import torch.multiprocessing as mp
 
-  world = 2
+  if torch.cuda.device_count() < world:
+    pytest.skip(f"needs {world} GPUs")
   out = str(tmp_path / "rank")
   mp.spawn(_worker, args=(world, 29900 + os.getpid() % 300, out), nprocs=world, join=True)
   res = [torch.load(f"{out}.{rank}") for rank in range(world)]
@@ -103,8 +105,9 @@ def test_two_ranks_sum_inside_the_kernel(tmp_path):
     assert r["status"] == 0
     _check(r["outs"])
   # every rank adds the same partial sums in the same order: the same bits everywhere
-  for a, b in zip(res[0]["outs"], res[1]["outs"]):
-    assert torch.equal(a, b)
+  for other in res[1:]:
+    for a, b in zip(res[0]["outs"], other["outs"]):
+      assert torch.equal(a, b)
 
 
 def test_a_peer_that_never_comes_is_reported():
