@@ -505,12 +505,12 @@ int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K,
  * are in jetstream_pt/default_shardings/llama.yaml:10,20), and what GSPMD
  * inserts behind the reference's matmul, an all-reduce of the partial results,
  * happens inside the GEMM's epilogue: every CTA stores the fp32 sums of its
- * rows into all ranks' receive buffers over NVLink (plain peer stores of
- * 8-byte words: the value and the number of the launch, so that a word that
- * shows this launch's number is complete and needs no fence or flag), reads
- * the words of the other ranks for the same rows (bounded wait for those that
- * have not arrived) and adds the partials in the order of the ranks; then the
- * two bf16 roundings and the channel scale, as on one GPU.  Every rank gets the
+ * rows into its rank's own buffer, tells the other ranks with the number of
+ * the launch (a small peer store behind a system-scope fence), waits (bounded)
+ * for the same CTA of the other ranks, fetches their sums over NVLink (plain
+ * 16-byte peer loads) and adds the partials in the order of the ranks; then the
+ * two bf16 roundings and the channel scale, as on one GPU.  N must be a
+ * multiple of 4.  Every rank gets the
  * whole y.  M <= 128.  All ranks make the same sequence of calls with the same
  * shapes; the calls are numbered on the device (a captured graph of them can be
  * replayed), and two consecutive calls use the two halves of the buffers.

@@ -61,10 +61,11 @@ struct LinearMaps {
 
 // Row-parallel layer over the GPUs of one box (the input features are sharded: every rank holds x[:, K_r] and
 // W[:, K_r], the result is the sum over the ranks).  buffers[r] is rank r's receive buffer (own or an IPC
-// mapping): a status word and the launch counter, then [2 (launch parity)][world (source rank)][128][N] words of
-// eight bytes, each an fp32 partial sum with the number of the launch that wrote it.  A word travels as one
-// 8-byte store, so a reader that sees the launch number has the value: no fence and no separate flag lie between
-// a rank's sums and their use on another rank.  world = 1: a layer of one GPU.
+// mapping): a status word and the launch counter, launch numbers [2 (launch parity)][8 (source rank)][1024 (tile)]
+// [8 (K split)] u32, then the rank's OWN fp32 partial sums [2][128][N].  A rank writes its sums into its own buffer,
+// tells the others with the launch number (one small peer store per CTA and rank, behind a system-scope fence) and
+// reads theirs with 16-byte peer loads, twelve of a thread in flight at a time: loads cross NVLink at about
+// twice the rate of narrow peer stores.  world = 1: a layer of one GPU.
 struct TpArgs {
   int world, rank;
   // number of this launch (the same on every rank): counted on the device by the level kernel in front of the GEMM,
@@ -74,13 +75,23 @@ struct TpArgs {
   char* buffers[8];
   int* status;  // in the rank's own buffer: raised when a wait for a peer ran out
 };
-constexpr size_t kTpDataOffset = 256;
-__device__ __forceinline__ void st_sys_word(uint2* p, float v, unsigned launch) {
-  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(launch) : "memory");
+constexpr int kTpMaxTiles = 1024;
+constexpr size_t kTpFlagOffset = 256;
+constexpr size_t kTpFlagBytes = (size_t)2 * 8 * kTpMaxTiles * 8 * sizeof(unsigned);
+constexpr size_t kTpDataOffset = kTpFlagOffset + kTpFlagBytes;
+__device__ __forceinline__ void st_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint2 ld_sys_word(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned ld_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// (no memory clobber: the loads of a batch must be free to go out together; the flag's wait, fence and barrier
+// stand before them)
+__device__ __forceinline__ float4 ld_sys_f32x4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
   return v;
 }
 
@@ -565,19 +576,16 @@ __global__ void __launch_bounds__(kThreadsL, 1)
           }
         }
         if (tp.world > 1) {
-          // this rank's sums of the group go to every rank's receive buffer (its own included); the roundings follow
-          // below, on the sum over the ranks
-          const int64_t src_rows = ((int64_t)(tp_epoch & 1u) * tp.world + tp.rank) * kMaxM;
-          for (int d = 0; d < tp.world; ++d) {
-            uint2* dst = reinterpret_cast<uint2*>(tp.buffers[d] + kTpDataOffset);
+          // this rank's sums of the group go into its own buffer, where the other ranks read them; the roundings
+          // follow below, on the sum over the ranks
+          float* dst = reinterpret_cast<float*>(tp.buffers[tp.rank] + kTpDataOffset) + (int64_t)(tp_epoch & 1u) * kMaxM * N;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              const int n = n0 + half * 128 + tid;
+          for (int half = 0; half < 2; ++half) {
+            const int n = n0 + half * 128 + tid;
 #pragma unroll
-              for (int r = 0; r < 8; ++r) {
-                const int m = 8 * j + r;
-                if (m < M && n < N) st_sys_word(&dst[(src_rows + m) * N + n], acc[half][r], tp_epoch);
-              }
+            for (int r = 0; r < 8; ++r) {
+              const int m = 8 * j + r;
+              if (m < M && n < N) __stcg(&dst[(int64_t)m * N + n], acc[half][r]);
             }
           }
           continue;
@@ -605,53 +613,69 @@ __global__ void __launch_bounds__(kThreadsL, 1)
       default: reduce(std::integral_constant<int, 8>{}); break;
     }
     if (tp.world > 1 && split < groups) {  // (a CTA without a group of rows has nothing to send or to wait for)
-      // ---- sum over the ranks: every thread reads the words of its own elements from every rank (a word whose
-      // launch number is not this launch's has not arrived yet: bounded wait) and adds them in the order of the ranks
+      // ---- sum over the ranks: tell every rank that this CTA's groups are in this rank's buffer, wait (bounded) for
+      // the same CTA of every rank, read their sums and add them in the order of the ranks
       const int par = (int)(tp_epoch & 1u);
-      const uint2* mine = reinterpret_cast<const uint2*>(tp.buffers[tp.rank] + kTpDataOffset) + (int64_t)par * tp.world * kMaxM * N;
-      bool gave_up = false;
-      for (int q = 0; q < owned; ++q) {
-        const int j = q * csize + split;
-        if (j >= groups) break;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int n = n0 + half * 128 + tid;
-          if (n >= N) continue;
-          float sum[8];
-#pragma unroll
-          for (int r = 0; r < 8; ++r) sum[r] = 0.f;
-          for (int src = 0; src < tp.world; ++src) {
-            uint2 wv[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              const int m = min(8 * j + r, M - 1);
-              wv[r] = ld_sys_word(&mine[((int64_t)src * kMaxM + m) * N + n]);
-            }
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-              if (wv[r].y != tp_epoch && !gave_up) {  // not there yet
-                const int m = min(8 * j + r, M - 1);
-                const long long t0c = clock64();
-                do {
-                  wv[r] = ld_sys_word(&mine[((int64_t)src * kMaxM + m) * N + n]);
-                  if (clock64() - t0c > tp.wait_cycles) {  // a rank never came: report, go on with what is there
-                    gave_up = true;
-                    break;
-                  }
-                } while (wv[r].y != tp_epoch);
-              }
-              sum[r] += wv[r].y == tp_epoch ? __uint_as_float(wv[r].x) : 0.f;
-            }
-          }
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const int m = 8 * j + r;
-            const float dot = __bfloat162float(__float2bfloat16_rn(sum[r]));
-            if (m < M) y[(int64_t)m * N + n] = __float2bfloat16_rn(dot * sc[half]);
+      auto flag_of = [&](int buffer_of, int src) {  // the sums of rank `src` are ready, as told to rank `buffer_of`
+        return reinterpret_cast<unsigned*>(tp.buffers[buffer_of] + kTpFlagOffset) +
+               (((size_t)par * 8 + src) * kTpMaxTiles + blockIdx.x) * 8 + split;
+      };
+      __syncthreads();  // every thread's stores are issued ...
+      if (tid < tp.world && tid != tp.rank) {
+        __threadfence_system();  // ... and ordered before the launch number that announces them
+        st_sys_u32(flag_of(tid, tp.rank), tp_epoch);
+        const long long t0c = clock64();
+        while (ld_sys_u32(flag_of(tp.rank, tid)) != tp_epoch) {
+          if (clock64() - t0c > tp.wait_cycles) {  // a rank never came: report, go on with what is there
+            atomicExch(tp.status, 1);
+            break;
           }
         }
+        __threadfence_system();
       }
-      if (gave_up) atomicExch(tp.status, 1);
+      __syncthreads();
+      asm volatile("" ::: "memory");  // (the peer loads below carry no memory clobber of their own)
+      const size_t part_off = kTpDataOffset + (size_t)par * kMaxM * N * sizeof(float);
+      // A group is eight rows x 256 channels: 512 pieces of four channels (16 bytes), four per thread.  A thread
+      // has the pieces of up to three groups (twelve loads per rank) in flight at a time.
+      constexpr int kBatch = 12;
+      const int my_groups = (groups - split + csize - 1) / csize;
+      for (int base = 0; base < 4 * my_groups; base += kBatch) {
+        float4 sum[kBatch];
+        int64_t at[kBatch];  // element offset of the piece, -1: none
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          const int idx = base + b, item = (idx & 3) * kThreadsL + tid;
+          const int m = 8 * ((idx >> 2) * csize + split) + (item >> 6), n = n0 + 4 * (item & 63);
+          at[b] = (idx < 4 * my_groups && m < M && n < N) ? (int64_t)m * N + n : -1;
+          sum[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int src = 0; src < tp.world; ++src) {
+          const float* part = reinterpret_cast<const float*>(tp.buffers[src] + part_off);
+          float4 v[kBatch];
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) {
+            v[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (at[b] >= 0) v[b] = src == tp.rank ? __ldcg(reinterpret_cast<const float4*>(part + at[b])) : ld_sys_f32x4(part + at[b]);
+          }
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) sum[b].x += v[b].x, sum[b].y += v[b].y, sum[b].z += v[b].z, sum[b].w += v[b].w;
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          if (at[b] < 0) continue;
+          const int n = (int)(at[b] % N);
+          const uint2 sraw = __ldg(reinterpret_cast<const uint2*>(scale + n));
+          const __nv_bfloat16* sb = reinterpret_cast<const __nv_bfloat16*>(&sraw);
+          const float a4[4] = {sum[b].x, sum[b].y, sum[b].z, sum[b].w};
+          uint2 o;
+          __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            ob[e] = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(a4[e])) * __bfloat162float(sb[e]));
+          *reinterpret_cast<uint2*>(y + at[b]) = o;
+        }
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -903,14 +927,16 @@ extern "C" int jpt_silu_mul(const void* a, const void* b, void* h, int M, int K,
 }
 
 extern "C" size_t jpt_w8a16_tp_buffer_bytes(int N, int world) {
-  if (N < 1 || world < 1 || world > 8) return 0;
-  return kTpDataOffset + (size_t)2 * world * kMaxM * N * sizeof(uint2);
+  if (N < 4 || N % 4 || world < 1 || world > 8 || (N + kTileN - 1) / kTileN > kTpMaxTiles) return 0;
+  return kTpDataOffset + (size_t)2 * kMaxM * N * sizeof(float);
 }
 
 extern "C" int jpt_w8a16_linear_tp(const void* x, const void* w, const void* w_scale, void* y, int M, int N, int K, void* workspace,
                                    size_t workspace_bytes, const jpt_tp_sum* tp, void* stream) {
   JPT_REQUIRE(x && w && w_scale && y && tp, JPT_EINVAL, "w8a16_linear_tp: null argument");
-  JPT_REQUIRE(N >= 1 && aligned(x, 16) && aligned(w, 16), JPT_EALIGN, "w8a16_linear_tp: x and w must be 16-byte aligned");
+  JPT_REQUIRE(N >= 4 && N % 4 == 0, JPT_EINVAL, "w8a16_linear_tp: N = %d must be a multiple of 4", N);
+  JPT_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 8) && aligned(w_scale, 8), JPT_EALIGN,
+              "w8a16_linear_tp: x and w must be 16-byte aligned, y and the scales 8-byte aligned");
   JPT_REQUIRE(tp->world >= 1 && tp->world <= 8 && tp->rank >= 0 && tp->rank < tp->world, JPT_EINVAL,
               "w8a16_linear_tp: rank %d of %d", tp->rank, tp->world);
   JPT_REQUIRE(tp->buffer_bytes >= jpt_w8a16_tp_buffer_bytes(N, tp->world) && jpt_w8a16_tp_buffer_bytes(N, tp->world) > 0, JPT_EWORKSPACE,
