@@ -60,3 +60,38 @@ def test_head_sharded_quantise_and_attention_match_unsharded():
     out = mgr.dict()
     mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
     assert dict(out) == {0: True, 1: True}
+
+
+def _linear_worker(rank, world, port, out):
+  """Row-parallel weight-only int8 layer: each rank multiplies its slice of the input features; the fp32 partial
+  results are summed over the ranks (what the device kernel does over NVLink, here a gloo all-reduce), then come
+  the two bf16 roundings and the channel scale."""
+  from oracle import linear as ol
+
+  os.environ["MASTER_ADDR"] = "127.0.0.1"
+  os.environ["MASTER_PORT"] = str(port)
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  try:
+    g = torch.Generator().manual_seed(9)
+    m, k, n = 24, 512, 96
+    wq, sc = ol.quantize_weight(torch.randn(n, k, generator=g) * 0.05)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    ks = slice(rank * k // world, (rank + 1) * k // world)
+    partial = (x[:, ks].double() @ wq[:, ks].double().t()).float()  # this rank's sums, as the GEMM leaves them
+    dist.all_reduce(partial, op=dist.ReduceOp.SUM)
+    y = (partial.to(torch.bfloat16).float() * sc.float()).to(torch.bfloat16)
+    want = ol.w8a16_linear(x, wq, sc)
+    err = (y.float() - want.float()).abs().double()
+    same = (y.view(torch.int16) == want.view(torch.int16)).float().mean().item()
+    out[rank] = bool((err <= ol.w8a16_tolerance(x, wq, sc)).all()) and same > 0.99
+  finally:
+    dist.destroy_process_group()
+
+
+def test_row_parallel_linear_sums_to_the_unsharded_layer():
+  world = 2
+  port = _free_port()
+  with mp.Manager() as mgr:
+    out = mgr.dict()
+    mp.spawn(_linear_worker, args=(world, port, out), nprocs=world, join=True)
+    assert all(out[r] for r in range(world)), dict(out)
