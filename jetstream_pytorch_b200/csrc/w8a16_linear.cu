@@ -25,6 +25,11 @@
 // multiplies by the channel's scale and rounds again, as the reference's two bf16 operations do.
 // No partial result goes through global memory.  Every wait on data is bounded; a CTA that gives up
 // raises the status word, still meets its cluster at the two cluster barriers, and returns.
+//
+// Also here, because they write the same level matrix: RMSNorm and the feed-forward gate (SiLU-mul) as
+// kernels that can leave the level split of their result behind, so that the layers after them start
+// at their GEMM; and the row-parallel form of the layer over the GPUs of one box, in which the owner
+// of a group of rows adds the partial sums of all ranks (fetched over NVLink) before it rounds.
 #include <cuda.h>
 #include <string.h>
 
