@@ -566,7 +566,7 @@ def extra_w8a16_linear(dev, peak, reps, eager=False):
   out = {}
   gen = torch.Generator(device=dev).manual_seed(1006)
   shapes = (("wo_8192x8192", 8192, 8192), ("w_up_8192x28672", 8192, 28672), ("w_down_28672x8192", 28672, 8192))
-  for name, k, n in shapes[:1] if eager else shapes:  # (eager: the command line for profiler captures, one shape)
+  for name, k, n in (shapes[:1] if eager is True else [] if eager else shapes):  # (eager: for profiler captures)
     sets = max(3, int(300e6 // (k * n)) + 1)
     layers = []
     for _ in range(sets):
@@ -591,7 +591,7 @@ def extra_w8a16_linear(dev, peak, reps, eager=False):
     del layers
     torch.cuda.empty_cache()
   out["workload"] = "y = bf16(bf16(x W^T) * scale), x bf16 [96, K], W int8 [N, K]: level split + tcgen05 GEMM launches"
-  if not eager:
+  if not eager or eager == "ffn":
     # the feed-forward block behind its norm: RMSNorm (writes the levels of its result), w1 and w3 on those
     # levels, the gate (writes the levels of its result), w2: five launches, 705 MB of weights
     from jetstream_pytorch_b200.layers import FeedForward, RMSNorm
@@ -612,7 +612,11 @@ def extra_w8a16_linear(dev, peak, reps, eager=False):
         y, lv = norm(x, with_levels=True)
         ff(y, levels=lv)
 
-    us = time_replays(graph_of(run_blocks).replay, reps) * 1e3 / sets
+    if eager:
+      run_blocks()
+      us = time_replays(run_blocks, reps) * 1e3 / sets
+    else:
+      us = time_replays(graph_of(run_blocks).replay, reps) * 1e3 / sets
     nbytes = 3 * dim * hidden + 3 * hidden * 2 + dim * 2 + B * 2 * (2 * dim + 3 * hidden + dim)
     out["ffn_block_8192_28672"] = kernel_entry(
         us, nbytes, peak, launches=5, kernel_status=max(ff.w2.kernel_status() for _, ff in blocks),
@@ -733,8 +737,9 @@ def run_cuda(args):
       dist.barrier()
       dist.destroy_process_group()
     return
-  if args.only == "linear":
-    print(json.dumps({"only": "linear", **extra_w8a16_linear(dev, peak, args.steps, eager=True)}), flush=True)
+  if args.only in ("linear", "ffn"):
+    print(json.dumps({"only": args.only,
+                      **extra_w8a16_linear(dev, peak, args.steps, eager=True if args.only == "linear" else "ffn")}), flush=True)
     return
 
   # ---- device-resident state: every layer owns its cache (>> L2 in total).  Layer 0 comes from
@@ -1162,7 +1167,7 @@ def main():
   ap.add_argument("--no-extras", action="store_true", help="skip the other workloads' kernels (N = 1 runs them by default)")
   ap.add_argument("--amax-exchange", choices=["peers", "nccl"], default="peers",
                   help="N > 1: how the per-token amax is max-reduced over the ranks")
-  ap.add_argument("--only", choices=["attention", "append", "insert", "peer-insert", "linear", "linear-tp"], default=None,
+  ap.add_argument("--only", choices=["attention", "append", "insert", "peer-insert", "linear", "ffn", "linear-tp"], default=None,
                   help="launch just this kernel (no graph, no end-to-end leg): for profiler captures")
   ap.add_argument("--kv", choices=["int8", "bf16"], default="int8", help="with --only attention: cache dtype")
   ap.add_argument("--attn-kernel", choices=["auto", "mma"], default="auto",
